@@ -1,0 +1,69 @@
+"""Builds libcrucible_attn.so (sm_100a) in-tree with nvcc, and the C oracle with gcc.
+
+    python -m crucible_strix_halo_b200.build [--force]
+"""
+import concurrent.futures
+import glob
+import os
+import subprocess
+import sys
+
+PKG = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(PKG)
+CSRC = os.path.join(PKG, "csrc")
+OBJ = os.path.join(PKG, "build")
+LIB = os.path.join(PKG, "libcrucible_attn.so")
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+              "-Xcompiler", "-fPIC", "--use_fast_math" if False else "-Xptxas", "-v" if False else "-O3"]
+
+
+def _newer(dst, srcs):
+    if not os.path.exists(dst):
+        return False
+    m = os.path.getmtime(dst)
+    return all(os.path.getmtime(s) <= m for s in srcs)
+
+
+def _run(cmd):
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("command failed: %s\n%s\n%s" % (" ".join(cmd), r.stdout, r.stderr))
+    return r.stdout + r.stderr
+
+
+def build_library(force=False, verbose=False):
+    os.makedirs(OBJ, exist_ok=True)
+    sources = sorted(glob.glob(os.path.join(CSRC, "*.cu")))
+    headers = glob.glob(os.path.join(CSRC, "*.cuh")) + glob.glob(os.path.join(ROOT, "include", "*.h"))
+    jobs = []
+    for src in sources:
+        obj = os.path.join(OBJ, os.path.basename(src)[:-3] + ".o")
+        if force or not _newer(obj, [src] + headers):
+            jobs.append(["nvcc", *NVCC_FLAGS, *(["-Xptxas", "-v"] if verbose else []), "-c", src, "-o", obj])
+    with concurrent.futures.ThreadPoolExecutor(max_workers=8) as ex:
+        for out in ex.map(_run, jobs):
+            if verbose:
+                print(out)
+    objs = [os.path.join(OBJ, os.path.basename(s)[:-3] + ".o") for s in sources]
+    if force or jobs or not os.path.exists(LIB):
+        _run(["nvcc", "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", LIB, *objs, "-lcudart"])
+    return LIB
+
+
+def build_oracle(force=False):
+    """The C restatement used as the timed CPU baseline (oracle/attn_oracle_c.c -> oracle/_ref/liboracle.so)."""
+    src = os.path.join(ROOT, "oracle", "attn_oracle_c.c")
+    if not os.path.exists(src):
+        return None
+    out_dir = os.path.join(ROOT, "oracle", "_ref")
+    os.makedirs(out_dir, exist_ok=True)
+    lib = os.path.join(out_dir, "liboracle.so")
+    if force or not _newer(lib, [src]):
+        _run(["gcc", "-O3", "-march=x86-64-v3", "-fopenmp", "-shared", "-fPIC", "-o", lib, src, "-lm"])
+    return lib
+
+
+if __name__ == "__main__":
+    force = "--force" in sys.argv
+    print(build_library(force, verbose="-v" in sys.argv))
+    print(build_oracle(force))

@@ -1,0 +1,113 @@
+// Shared device/host helpers of the sm_100a attention kernels.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+#include <cstdint>
+#include <cstdio>
+#include <cstdarg>
+#include "../../include/crucible_attn.h"
+
+namespace cr {
+
+constexpr float kEps = 1e-6f;                         // every norm epsilon
+constexpr float kInvSqrt128 = 0.08838834764831845f;   // 1/sqrt(128)
+constexpr float kHadNorm = 0.088388347648f;           // ExLlamaV3's 1/sqrt(128) constant
+constexpr int kMaxSpans = 32;                         // spans per launch (kernel-parameter budget)
+
+// ---- host-side error plumbing -------------------------------------------------------------------
+void set_error(const char* fmt, ...);
+cr_status cuda_fail(cudaError_t e, const char* what);
+void count_launch(const char* name);
+void use_stream(cudaStream_t stream);   // the stream the following launches go to (for stage timing)
+#define CR_CUDA(call)                                                          \
+  do {                                                                         \
+    cudaError_t e_ = (call);                                                   \
+    if (e_ != cudaSuccess) return ::cr::cuda_fail(e_, #call);                  \
+  } while (0)
+#define CR_REQUIRE(cond, ...)                                                  \
+  do {                                                                         \
+    if (!(cond)) { ::cr::set_error(__VA_ARGS__); return CR_ERR_INVALID; }      \
+  } while (0)
+#define CR_LAUNCH_CHECK(name)                                                  \
+  do {                                                                         \
+    cudaError_t e_ = cudaGetLastError();                                       \
+    if (e_ != cudaSuccess) return ::cr::cuda_fail(e_, name);                   \
+    ::cr::count_launch(name);                                                  \
+  } while (0)
+
+cr_status check_geometry(const cr_geometry* g);
+
+// ---- device math ---------------------------------------------------------------------------------
+__device__ __forceinline__ float round_h(float v) { return __half2float(__float2half_rn(v)); }
+__device__ __forceinline__ float sigmoidf_(float v) { return 1.f / (1.f + __expf(-v)); }
+__device__ __forceinline__ float siluf_(float v) { return v / (1.f + __expf(-v)); }
+__device__ __forceinline__ float bf16_bits_to_float(uint16_t u) { return __uint_as_float((uint32_t)u << 16); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int m = 16; m > 0; m >>= 1) v += __shfl_xor_sync(0xffffffffu, v, m);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int m = 16; m > 0; m >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, m));
+  return v;
+}
+
+// Sum over a block of NT threads; red holds NT/32 floats; every thread gets the same fixed-order result.
+template <int NT>
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float t = 0.f;
+#pragma unroll
+  for (int i = 0; i < NT / 32; ++i) t += red[i];
+  return t;
+}
+
+// In-warp natural-order Sylvester-Hadamard of 128 values, lane l holding elements 4l..4l+3; unnormalised.
+__device__ __forceinline__ void wht128(float v[4]) {
+  const int lane = threadIdx.x & 31;
+  const float a0 = v[0] + v[1], a1 = v[0] - v[1], a2 = v[2] + v[3], a3 = v[2] - v[3];
+  v[0] = a0 + a2; v[1] = a1 + a3; v[2] = a0 - a2; v[3] = a1 - a3;
+#pragma unroll
+  for (int m = 1; m < 32; m <<= 1) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float o = __shfl_xor_sync(0xffffffffu, v[i], m);
+      v[i] = (lane & m) ? (o - v[i]) : (v[i] + o);
+    }
+  }
+}
+
+// Out-projection input index: row-major [R][width], or (pack_rows > 0) the packed GEMM layout
+// [width/16][pack_rows][16] at row pack_off + r.
+__host__ __device__ __forceinline__ size_t out_index(int r, int c, int width, int pack_rows, int pack_off) {
+  return pack_rows ? ((size_t)(c >> 4) * pack_rows + pack_off + r) * 16 + (c & 15) : (size_t)r * width + c;
+}
+
+// Loads element i of a row buffer that is fp32 or bf16.
+template <bool BF16>
+__device__ __forceinline__ float load_in(const void* p, size_t i) {
+  if constexpr (BF16) return bf16_bits_to_float(reinterpret_cast<const uint16_t*>(p)[i]);
+  else return reinterpret_cast<const float*>(p)[i];
+}
+
+// Split-half partial RoPE angle terms for pair j (< 32) at position p with a 64-float table.
+__device__ __forceinline__ void rope_cs(const float* rope, int j, int p, float& c, float& s) {
+  const float ang = (float)p * rope[j], m = rope[32];
+  c = cosf(ang) * m;
+  s = sinf(ang) * m;
+}
+
+__host__ __device__ __forceinline__ size_t pool_offset(int b, int d) {
+  return (size_t)(b >> 5) * 4096 + (size_t)d * 32 + (b & 31);
+}
+__host__ __device__ __forceinline__ size_t raw_offset(int slots, int position, int dim) {
+  return (size_t)(slots ? position % slots : position) * 128 + dim;
+}
+
+}  // namespace cr

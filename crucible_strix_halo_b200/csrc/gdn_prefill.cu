@@ -1,0 +1,300 @@
+// Gated DeltaNet prefill for sm_100a: row preparation, the exact fp32 token-serial scan, the gated readout
+// and the raw-row ring.  The chunk-64 tensor-core scan lives in gdn_chunk.cu and shares prep/gate/ring.
+//
+// Pipeline of one call (rows pos0..pos0+R-1 of one layer, engine/layers/kernels/prefill_gdn.h:1206-1279):
+//   gdn_prep   conv(4)+SiLU on the raw projection, L2 norms of q/k per key head, g = -exp(A_log)softplus(a+dt),
+//              beta = sigmoid(b)                                   -> workspace (qn, kn, vn, glog, beta)
+//   scan       delta rule over the rows from the carried state     -> raw readout y, new state
+//   gdn_gate   y * rsqrt(mean y^2 + eps) * gamma * sigmoid(z), output transform
+//   gdn_ring   last 16 raw rows -> hist ring (GdnPrefillHistoryKernel, prefill_gdn.h:274-282)
+#include "common.cuh"
+#include "gdn_prefill.cuh"
+
+namespace cr {
+
+// ---- gdn_prep ----------------------------------------------------------------------------------------
+// grid (ceil(R/16), Hk + Hv/2 + 1), 256 threads.  Unit u < Hk: key head u (threads 0..127 the q channels,
+// 128..255 the k channels).  Hk <= u < Hk + Hv/2: value heads 2(u-Hk), 2(u-Hk)+1.  Last unit: g and beta.
+// Each thread slides a 4-row window down its channel over the 16 rows of the tile.
+template <bool BF16>
+__global__ void __launch_bounds__(256) gdn_prep_kernel(GdnPrefillParams P) {
+  const cr_gdn_args& a = P.a;
+  const int t = threadIdx.x, w = t >> 5, l = t & 31;
+  const int r0 = blockIdx.x * 16, u = blockIdx.y;
+  const int KW = P.Hk * 128, VW = P.Hv * 128, C = 2 * KW + VW;
+  const int rows = min(16, a.R - r0);
+  if (u == P.Hk + P.Hv / 2) {
+    // g / beta for rows r0.. and all value heads
+    for (int i = t; i < rows * P.Hv; i += 256) {
+      const int r = r0 + i / P.Hv, h = i % P.Hv;
+      const float av = load_in<BF16>(P.ab_logits, (size_t)r * 2 * P.Hv + h);
+      const float bv = load_in<BF16>(P.ab_logits, (size_t)r * 2 * P.Hv + P.Hv + h);
+      const float sp = av + a.dt_bias[h];
+      const float softplus = sp > 20.f ? sp : log1pf(expf(sp));
+      P.glog[(size_t)r * P.Hv + h] = -expf(a.A_log[h]) * softplus;
+      P.beta[(size_t)r * P.Hv + h] = sigmoidf_(bv);
+    }
+    return;
+  }
+  const bool is_qk = u < P.Hk;
+  const int ch = is_qk ? (t < 128 ? u * 128 + t : KW + u * 128 + (t - 128)) : 2 * KW + (u - P.Hk) * 256 + t;
+  const float4 wv = *reinterpret_cast<const float4*>(a.conv + (size_t)ch * 4);
+  auto raw = [&](int r) -> float {   // raw projection value of this channel at call row r (may be negative)
+    if (r >= 0) return load_in<BF16>(a.qkv, (size_t)r * C + ch);
+    const int p = a.pos0 + r;
+    return p < 0 ? 0.f : a.hist[(size_t)(p & 15) * C + ch];
+  };
+  float x0 = raw(r0 - 3), x1 = raw(r0 - 2), x2 = raw(r0 - 1);
+  float val[16];
+  __shared__ float red[16][8];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    float c = 0.f;
+    if (i < rows) {
+      const float x3 = raw(r0 + i);
+      c = wv.x * x0;
+      c = fmaf(wv.y, x1, c); c = fmaf(wv.z, x2, c); c = fmaf(wv.w, x3, c);
+      c = siluf_(c);
+      x0 = x1; x1 = x2; x2 = x3;
+    }
+    val[i] = c;
+    if (is_qk) {
+      const float s = warp_sum(c * c);
+      if (l == 0) red[i][w] = s;
+    }
+  }
+  if (is_qk) {
+    __syncthreads();
+    const int part = t >> 7, j = t & 127;
+    float* dst = part ? P.kn : P.qn;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      if (i >= rows) break;
+      const float ss = red[i][part * 4] + red[i][part * 4 + 1] + red[i][part * 4 + 2] + red[i][part * 4 + 3];
+      const float sc = rsqrtf(ss + kEps) * (part ? 1.f : kInvSqrt128);
+      dst[((size_t)(r0 + i) * P.Hk + u) * 128 + j] = val[i] * sc;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      if (i >= rows) break;
+      P.vn[(size_t)(r0 + i) * VW + (u - P.Hk) * 256 + t] = val[i];
+    }
+  }
+}
+
+// ---- exact fp32 serial scan --------------------------------------------------------------------------
+// grid Hv*4 CTAs x 256 threads.  CTA (h, slice) owns 32 value columns; warp w owns 4 of them; the 8 lanes
+// that share a column hold 16 key rows each in registers, so one token costs two 3-step shuffle reductions
+// and no block barrier.  Inputs of the next token are fetched while the current one is computed.
+__global__ void __launch_bounds__(256) gdn_scan_serial_kernel(GdnPrefillParams P) {
+  const cr_gdn_args& a = P.a;
+  const int t = threadIdx.x, w = t >> 5, l = t & 31;
+  const int h = blockIdx.x >> 2, slice = blockIdx.x & 3;
+  const int rep = P.Hv / P.Hk, kh = h / rep, VW = P.Hv * 128;
+  const int col = slice * 32 + w * 4 + (l >> 3), sub = l & 7;
+  float S[16];
+  float* st = a.state + (size_t)h * 16384 + col;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) S[i] = st[(size_t)(sub * 16 + i) * 128];
+
+  auto fetch = [&](int r, float4 (&k4)[4], float4 (&q4)[4], float& v, float& g, float& b) {
+    const float4* kp = reinterpret_cast<const float4*>(P.kn + ((size_t)r * P.Hk + kh) * 128 + sub * 16);
+    const float4* qp = reinterpret_cast<const float4*>(P.qn + ((size_t)r * P.Hk + kh) * 128 + sub * 16);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { k4[i] = kp[i]; q4[i] = qp[i]; }
+    v = P.vn[(size_t)r * VW + h * 128 + col];
+    g = P.glog[(size_t)r * P.Hv + h];
+    b = P.beta[(size_t)r * P.Hv + h];
+  };
+  float4 kc[4], qc[4], kn_[4], qn_[4];
+  float vc, gc, bc, vn_ = 0.f, gn_ = 0.f, bn_ = 0.f;
+  fetch(0, kc, qc, vc, gc, bc);
+  for (int r = 0; r < a.R; ++r) {
+    if (r + 1 < a.R) fetch(r + 1, kn_, qn_, vn_, gn_, bn_);
+    const float decay = expf(gc);
+    const float* k = reinterpret_cast<const float*>(kc);
+    const float* q = reinterpret_cast<const float*>(qc);
+    float m0 = 0.f, m1 = 0.f, m2 = 0.f, m3 = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; i += 4) {
+      m0 = fmaf(S[i], k[i], m0); m1 = fmaf(S[i + 1], k[i + 1], m1);
+      m2 = fmaf(S[i + 2], k[i + 2], m2); m3 = fmaf(S[i + 3], k[i + 3], m3);
+    }
+    float mem = (m0 + m1) + (m2 + m3);
+    mem += __shfl_xor_sync(0xffffffffu, mem, 1);
+    mem += __shfl_xor_sync(0xffffffffu, mem, 2);
+    mem += __shfl_xor_sync(0xffffffffu, mem, 4);
+    const float delta = bc * (vc - decay * mem);
+    float y0 = 0.f, y1 = 0.f, y2 = 0.f, y3 = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; i += 4) {
+      S[i] = fmaf(k[i], delta, decay * S[i]);             y0 = fmaf(S[i], q[i], y0);
+      S[i + 1] = fmaf(k[i + 1], delta, decay * S[i + 1]); y1 = fmaf(S[i + 1], q[i + 1], y1);
+      S[i + 2] = fmaf(k[i + 2], delta, decay * S[i + 2]); y2 = fmaf(S[i + 2], q[i + 2], y2);
+      S[i + 3] = fmaf(k[i + 3], delta, decay * S[i + 3]); y3 = fmaf(S[i + 3], q[i + 3], y3);
+    }
+    float y = (y0 + y1) + (y2 + y3);
+    y += __shfl_xor_sync(0xffffffffu, y, 1);
+    y += __shfl_xor_sync(0xffffffffu, y, 2);
+    y += __shfl_xor_sync(0xffffffffu, y, 4);
+    if (sub == 0) P.yraw[(size_t)r * VW + h * 128 + col] = y;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { kc[i] = kn_[i]; qc[i] = qn_[i]; }
+    vc = vn_; gc = gn_; bc = bn_;
+  }
+#pragma unroll
+  for (int i = 0; i < 16; ++i) st[(size_t)(sub * 16 + i) * 128] = S[i];
+}
+
+// ---- gated readout -----------------------------------------------------------------------------------
+// One warp per (row, head); lane l holds columns 4l..4l+3 (the WHT layout).
+template <bool BF16>
+__global__ void __launch_bounds__(256) gdn_gate_kernel(GdnPrefillParams P) {
+  const cr_gdn_args& a = P.a;
+  const int VW = P.Hv * 128;
+  const long long unit = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (unit >= (long long)a.R * P.Hv) return;
+  const int r = (int)(unit / P.Hv), h = (int)(unit % P.Hv), l = threadIdx.x & 31;
+  const size_t base = (size_t)r * VW + h * 128 + l * 4;
+  const float4 y4 = *reinterpret_cast<const float4*>(P.yraw + base);
+  const float y[4] = {y4.x, y4.y, y4.z, y4.w};
+  const float ss = warp_sum(y[0] * y[0] + y[1] * y[1] + y[2] * y[2] + y[3] * y[3]);
+  const float rs = rsqrtf(ss * (1.f / 128.f) + kEps);
+  float o[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) o[i] = y[i] * rs * a.gamma[l * 4 + i] * sigmoidf_(load_in<BF16>(a.z, base + i));
+  if (P.fmt == CR_OUT_RAW_F32) {
+    *reinterpret_cast<float4*>(reinterpret_cast<float*>(a.out) + base) = make_float4(o[0], o[1], o[2], o[3]);
+  } else if (P.fmt == CR_OUT_RAW_BF16) {
+    __nv_bfloat162* dst = reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<__nv_bfloat16*>(a.out) + base);
+    dst[0] = __floats2bfloat162_rn(o[0], o[1]);
+    dst[1] = __floats2bfloat162_rn(o[2], o[3]);
+  } else {
+    const __half* suh = reinterpret_cast<const __half*>(a.suh_out) + h * 128 + l * 4;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o[i] = round_h(round_h(o[i]) * __half2float(suh[i]));
+    wht128(o);
+    __half* dst = reinterpret_cast<__half*>(a.out);
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      dst[out_index(r, h * 128 + l * 4 + i, VW, a.pack_rows, a.pack_off)] = __float2half(o[i] * kHadNorm);
+  }
+}
+
+// ---- raw-row ring --------------------------------------------------------------------------------------
+template <bool BF16>
+__global__ void __launch_bounds__(256) gdn_ring_kernel(GdnPrefillParams P) {
+  const cr_gdn_args& a = P.a;
+  const int C = 2 * P.Hk * 128 + P.Hv * 128;
+  const int keep = min(a.R, 16);
+  const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+  if (i >= (long long)keep * C) return;
+  const int r = a.R - keep + (int)(i / C), ch = (int)(i % C);
+  a.hist[(size_t)((a.pos0 + r) & 15) * C + ch] = load_in<BF16>(a.qkv, (size_t)r * C + ch);
+}
+
+// ---- materialize -----------------------------------------------------------------------------------------
+struct GdnStates { float* layer[64]; int Hv; };
+__global__ void __launch_bounds__(1024) gdn_materialize_kernel(GdnStates s) {
+  float* const state = s.layer[blockIdx.y];
+  float* const slot = state + (size_t)s.Hv * 16384 + blockIdx.x;
+  const float c = *slot;
+  if (c == 0.f || c == 1.f) return;
+  float* const x = state + (size_t)blockIdx.x * 16384;
+  for (int i = threadIdx.x; i < 16384; i += blockDim.x) x[i] *= c;
+  __syncthreads();
+  if (threadIdx.x == 0) *slot = 1.f;
+}
+
+size_t gdn_workspace_layout(const cr_geometry* g, int rows, GdnPrefillParams* P, char* base) {
+  size_t off = 0;
+  auto take = [&](size_t bytes) { const size_t o = off; off += (bytes + 255) & ~(size_t)255; return o; };
+  const size_t R = (size_t)rows, Hk = g->gdn_kheads, Hv = g->gdn_vheads;
+  const size_t o_qn = take(R * Hk * 128 * 4), o_kn = take(R * Hk * 128 * 4), o_vn = take(R * Hv * 128 * 4);
+  const size_t o_g = take(R * Hv * 4), o_b = take(R * Hv * 4), o_y = take(R * Hv * 128 * 4);
+  const size_t o_chunk = take(gdn_chunk_workspace_bytes(g, rows));
+  if (P) {
+    P->qn = (float*)(base + o_qn); P->kn = (float*)(base + o_kn); P->vn = (float*)(base + o_vn);
+    P->glog = (float*)(base + o_g); P->beta = (float*)(base + o_b); P->yraw = (float*)(base + o_y);
+    P->chunk_ws = base + o_chunk;
+  }
+  return off;
+}
+
+}  // namespace cr
+
+extern "C" size_t cr_gdn_prefill_workspace_bytes(const cr_geometry* g, int rows) {
+  if (!g || rows < 1) return 0;
+  return cr::gdn_workspace_layout(g, rows, nullptr, nullptr);
+}
+
+extern "C" int cr_gdn_algo_available(cr_gdn_algo algo) {
+  return algo == CR_GDN_SERIAL_F32 || (algo == CR_GDN_CHUNK_TC && cr::gdn_chunk_available());
+}
+
+extern "C" cr_status cr_gdn_prefill(const cr_geometry* g, const cr_gdn_prefill_args* args, cr_gdn_algo algo,
+                                    cr_out_format fmt, void* stream_) {
+  using namespace cr;
+  if (cr_status s = check_geometry(g)) return s;
+  CR_REQUIRE(args, "cr_gdn_prefill: null args");
+  const cr_gdn_args& a = args->input;
+  cudaStream_t stream = (cudaStream_t)stream_;
+  use_stream(stream);
+  CR_REQUIRE(a.R >= 1 && a.pos0 >= 0, "cr_gdn_prefill: need R >= 1 and pos0 >= 0 (R=%d pos0=%d)", a.R, a.pos0);
+  CR_REQUIRE(a.replay == 0 && a.commit == a.R, "cr_gdn_prefill: prefill rows are all committed (replay=0, commit=R)");
+  CR_REQUIRE(a.qkv && a.z && a.conv && a.A_log && a.dt_bias && a.gamma && a.hist && a.state && a.out && args->ab_logits,
+             "cr_gdn_prefill: null buffer");
+  CR_REQUIRE(args->in_dtype == CR_IN_F32 || args->in_dtype == CR_IN_BF16, "cr_gdn_prefill: bad in_dtype");
+  CR_REQUIRE(fmt == CR_OUT_RAW_F32 || fmt == CR_OUT_RAW_BF16 || fmt == CR_OUT_EXL3_WHT, "cr_gdn_prefill: bad output format");
+  CR_REQUIRE(fmt != CR_OUT_EXL3_WHT || a.suh_out, "cr_gdn_prefill: suh_out needed for the EXL3 output");
+  CR_REQUIRE(fmt == CR_OUT_EXL3_WHT || a.pack_rows == 0, "cr_gdn_prefill: packed layout only with the EXL3 output");
+  CR_REQUIRE(algo == CR_GDN_SERIAL_F32 || algo == CR_GDN_CHUNK_TC, "cr_gdn_prefill: unknown algorithm");
+  const size_t need = gdn_workspace_layout(g, a.R, nullptr, nullptr);
+  CR_REQUIRE(args->workspace && args->workspace_bytes >= need, "cr_gdn_prefill: workspace of %zu bytes needed, %zu given",
+             need, args->workspace_bytes);
+  CR_REQUIRE(((uintptr_t)args->workspace & 255) == 0, "cr_gdn_prefill: workspace must be 256-byte aligned");
+
+  GdnPrefillParams P;
+  P.a = a; P.ab_logits = args->ab_logits;
+  P.Hv = g->gdn_vheads; P.Hk = g->gdn_kheads; P.fmt = (int)fmt;
+  gdn_workspace_layout(g, a.R, &P, (char*)args->workspace);
+  if (args->raw_y) P.yraw = args->raw_y;
+  const bool bf = args->in_dtype == CR_IN_BF16;
+  const dim3 pg((a.R + 15) / 16, g->gdn_kheads + g->gdn_vheads / 2 + 1);
+  if (bf) gdn_prep_kernel<true><<<pg, 256, 0, stream>>>(P); else gdn_prep_kernel<false><<<pg, 256, 0, stream>>>(P);
+  CR_LAUNCH_CHECK("gdn_prep_kernel");
+  if (algo == CR_GDN_SERIAL_F32) {
+    gdn_scan_serial_kernel<<<g->gdn_vheads * 4, 256, 0, stream>>>(P);
+    CR_LAUNCH_CHECK("gdn_scan_serial_kernel");
+  } else {
+    if (cr_status s = gdn_chunk_scan(g, P, stream)) return s;
+  }
+  const unsigned gg = (unsigned)(((long long)a.R * g->gdn_vheads + 7) / 8);
+  if (bf) gdn_gate_kernel<true><<<gg, 256, 0, stream>>>(P); else gdn_gate_kernel<false><<<gg, 256, 0, stream>>>(P);
+  CR_LAUNCH_CHECK("gdn_gate_kernel");
+  const int C = 2 * g->gdn_kheads * 128 + g->gdn_vheads * 128;
+  const unsigned rg = (unsigned)(((long long)(a.R < 16 ? a.R : 16) * C + 255) / 256);
+  if (bf) gdn_ring_kernel<true><<<rg, 256, 0, stream>>>(P); else gdn_ring_kernel<false><<<rg, 256, 0, stream>>>(P);
+  CR_LAUNCH_CHECK("gdn_ring_kernel");
+  return CR_OK;
+}
+
+extern "C" cr_status cr_gdn_materialize(const cr_geometry* g, float* const* states, int n_states, void* stream) {
+  using namespace cr;
+  if (cr_status s = check_geometry(g)) return s;
+  CR_REQUIRE(states && n_states >= 0, "cr_gdn_materialize: null states");
+  use_stream((cudaStream_t)stream);
+  for (int i = 0; i < n_states; i += 64) {
+    GdnStates s{};
+    const int n = n_states - i < 64 ? n_states - i : 64;
+    for (int j = 0; j < n; ++j) {
+      CR_REQUIRE(states[i + j], "cr_gdn_materialize: null state %d", i + j);
+      s.layer[j] = states[i + j];
+    }
+    s.Hv = g->gdn_vheads;
+    gdn_materialize_kernel<<<dim3(g->gdn_vheads, n), 1024, 0, (cudaStream_t)stream>>>(s);
+    CR_LAUNCH_CHECK("gdn_materialize_kernel");
+  }
+  return CR_OK;
+}

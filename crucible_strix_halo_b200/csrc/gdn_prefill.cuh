@@ -1,0 +1,22 @@
+// Shared declarations of the GDN prefill kernels (gdn_prefill.cu, gdn_chunk.cu).
+#pragma once
+#include "common.cuh"
+
+namespace cr {
+
+struct GdnPrefillParams {
+  cr_gdn_args a;
+  const void* ab_logits;   // [R][2Hv]
+  float *qn, *kn;          // [R][Hk][128] normalised q (already / sqrt(128)) and k
+  float* vn;               // [R][Hv][128] conv + SiLU values
+  float *glog, *beta;      // [R][Hv]
+  float* yraw;             // [R][Hv][128] un-gated readout
+  char* chunk_ws;          // workspace of the chunked scan
+  int Hv, Hk, fmt;
+};
+
+bool gdn_chunk_available();
+size_t gdn_chunk_workspace_bytes(const cr_geometry* g, int rows);
+cr_status gdn_chunk_scan(const cr_geometry* g, const GdnPrefillParams& P, cudaStream_t stream);
+
+}  // namespace cr

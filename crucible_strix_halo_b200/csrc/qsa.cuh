@@ -1,0 +1,29 @@
+// Shared declarations of the QSA kernels (qsa_prep.cu, qsa_select.cu, qsa_attn.cu, qsa_prefill.cu).
+#pragma once
+#include "common.cuh"
+
+namespace cr {
+
+// All spans of one launch; base[s] = first row of span s in scratch laid out by row.
+struct QsaParams {
+  cr_qsa_args span[kMaxSpans];
+  int base[kMaxSpans];
+  int Hq, Hkv, n;
+};
+
+cr_status qsa_validate(const cr_geometry* g, const cr_qsa_args* spans, int n_spans, int max_rows, const char* who);
+int qsa_max_rows(const cr_qsa_args* spans, int n);
+void qsa_fill_params(QsaParams& P, const cr_geometry* g, const cr_qsa_args* spans, int n);
+cr_status qsa_prep_launch(const cr_geometry* g, const cr_qsa_args* spans, int n_spans, int u0, __half* q_hi, int q_skip,
+                          cudaStream_t stream);
+cr_status qsa_score_launch(const cr_geometry* g, const cr_qsa_args* spans, int n_spans, cudaStream_t stream);
+cr_status qsa_topk_launch(const cr_geometry* g, const cr_qsa_args* spans, int n_spans, cudaStream_t stream);
+cr_status qsa_select_launch(const cr_geometry* g, const cr_qsa_args* spans, int n_spans, cudaStream_t stream);
+// splits: KV splits per (row, KV head). p0/p1: position window (shard mode) or 0 / INT_MAX.
+cr_status qsa_attn_launch(const cr_geometry* g, const cr_qsa_args* spans, int n_spans, float* partials, int splits,
+                          int p0, int p1, cudaStream_t stream);
+// Merges `nparts` partial records per (row, head) found at partials[((part_major ? part*rows_total+row : row) ...)].
+cr_status qsa_merge_launch(const cr_geometry* g, const cr_qsa_args* spans, int n_spans, const float* partials, int nparts,
+                           bool part_major, float* partial_out, cr_out_format fmt, cudaStream_t stream);
+
+}  // namespace cr

@@ -1,0 +1,213 @@
+// QSA row preparation for sm_100a: CN-RMSNorm + partial RoPE of the query / key / indexer-query heads, K/V
+// rows to the fp16 cache, raw indexer keys, pooled indexer keys of completed 4-token blocks, RoPE table.
+// Follows QsaPrepKernel / QsaPoolKernel / QsaRetainRawKernel / QsaPrefillQueryKernel
+// (engine/layers/ops.h:561-645; engine/layers/kernels/prefill_qsa.h:35-51, :220-242).
+#include "qsa.cuh"
+
+namespace cr {
+
+__global__ void rope_table_kernel(float* table) {
+  const int j = threadIdx.x;
+  if (j < 32) table[j] = powf(10000000.f, -2.f * j / 64.f);
+  else if (j < CR_ROPE_TABLE_FLOATS) table[j] = j == 32 ? 1.f : 0.f;
+}
+
+// Split-half RoPE of x[0..63] (shared memory) at position p by threads 0..31; two barriers.
+__device__ __forceinline__ void rope64_smem(float* x, const float* rope, int p) {
+  const int j = threadIdx.x;
+  float c = 0.f, s = 0.f, a = 0.f, b = 0.f;
+  if (j < 32) {
+    rope_cs(rope, j, p, c, s);
+    a = x[j];
+    b = x[j + 32];
+  }
+  __syncthreads();
+  if (j < 32) {
+    x[j] = a * c - b * s;
+    x[j + 32] = b * c + a * s;
+  }
+  __syncthreads();
+}
+
+// CN-RMSNorm of n (128 or 256) values in shared memory, one per thread.
+__device__ __forceinline__ void cnorm_smem(float* x, int n, const float* w1, float* red) {
+  const int j = threadIdx.x;
+  const float v = j < n ? x[j] : 0.f;
+  const float ss = block_sum<256>(v * v, red);
+  if (j < n) x[j] = v * rsqrtf(ss / n + kEps) * w1[j];
+  __syncthreads();
+}
+
+__device__ __forceinline__ bool raw_uses_chunk(int slots, int rows) { return slots != 0 && rows > 8; }
+
+// grid (units, Rmax, spans), 256 threads.  Units: [0,Hq) query heads, [Hq,Hq+Hkv) key heads,
+// [Hq+Hkv, Hq+2Hkv) value heads, then 4 indexer-query heads, then the raw indexer key.
+// u0 skips leading units (u0 = Hq runs the cache units only).  q_hi (optional): fp16 copy of the prepared
+// queries [R][Hq][256] for the prefill attention kernels; rows < q_skip are not written to q_hi.
+__global__ void __launch_bounds__(256) qsa_prep_kernel(const __grid_constant__ QsaParams P, int u0, __half* q_hi, int q_skip) {
+  const cr_qsa_args& a = P.span[blockIdx.z];
+  const int r = blockIdx.y;
+  if (r >= a.R) return;
+  __shared__ float x[256], red[8];
+  const int u = blockIdx.x + u0, j = threadIdx.x, p = a.pos0 + r;
+  const int Hq = P.Hq, Hkv = P.Hkv;
+  if (u < Hq) {
+    float* q = a.q + ((size_t)r * Hq + u) * 512;
+    x[j] = q[j];
+    __syncthreads();
+    cnorm_smem(x, 256, a.q_norm1, red);
+    rope64_smem(x, a.rope, p);
+    q[j] = x[j];
+    if (q_hi && r >= q_skip) q_hi[((size_t)r * Hq + u) * 256 + j] = __float2half(x[j]);
+  } else if (u < Hq + Hkv) {
+    const int g = u - Hq;
+    x[j] = a.k[(size_t)r * Hkv * 256 + g * 256 + j];
+    __syncthreads();
+    cnorm_smem(x, 256, a.k_norm1, red);
+    rope64_smem(x, a.rope, p);
+    reinterpret_cast<__half*>(a.c.k)[((size_t)p * Hkv + g) * 256 + j] = __float2half(x[j]);
+  } else if (u < Hq + 2 * Hkv) {
+    const int g = u - Hq - Hkv;
+    reinterpret_cast<__half*>(a.c.v)[((size_t)p * Hkv + g) * 256 + j] = __float2half(a.v[(size_t)r * Hkv * 256 + g * 256 + j]);
+  } else if (u < Hq + 2 * Hkv + 4) {
+    float* iq = a.idx + (size_t)r * 640 + (u - Hq - 2 * Hkv) * 128;
+    if (j < 128) x[j] = iq[j];
+    __syncthreads();
+    cnorm_smem(x, 128, a.iq_norm1, red);
+    rope64_smem(x, a.rope, p);
+    if (j < 128) iq[j] = x[j];
+  } else if (j < 128 && !raw_uses_chunk(a.c.raw_slots, a.R)) {
+    a.c.ik_raw[raw_offset(a.c.raw_slots, p, j)] = a.idx[(size_t)r * 640 + 512 + j];
+  }
+}
+
+// Pooled key of block b = pos0/4 + blockIdx.x of span blockIdx.y, if these rows complete it.
+__global__ void __launch_bounds__(256) qsa_pool_kernel(const __grid_constant__ QsaParams P) {
+  const cr_qsa_args& a = P.span[blockIdx.y];
+  __shared__ float x[256], red[8];
+  const int b = a.pos0 / 4 + blockIdx.x, j = threadIdx.x;
+  if (b >= (a.pos0 + a.R) / 4) return;
+  if (j < 128) {
+    float m = 0.f;
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const int pos = b * 4 + t;
+      m += (raw_uses_chunk(a.c.raw_slots, a.R) && pos >= a.pos0)
+               ? a.idx[(size_t)(pos - a.pos0) * 640 + 512 + j]
+               : a.c.ik_raw[raw_offset(a.c.raw_slots, pos, j)];
+    }
+    x[j] = round_h(m * 0.25f);
+  }
+  __syncthreads();
+  cnorm_smem(x, 128, a.ik_norm1, red);
+  rope64_smem(x, a.rope, b * 4);
+  if (j < 128) a.c.ik_pool[pool_offset(b, j)] = x[j];
+}
+
+// Bulk rows with a raw ring: keep the newest min(R, slots) raw keys (after every pool has read the old tail).
+__global__ void qsa_retain_raw_kernel(const __grid_constant__ QsaParams P) {
+  const cr_qsa_args& a = P.span[blockIdx.y];
+  if (!raw_uses_chunk(a.c.raw_slots, a.R)) return;
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  const int keep = min(a.R, a.c.raw_slots);
+  if (i >= keep * 128) return;
+  const int row = a.R - keep + i / 128, dim = i % 128;
+  a.c.ik_raw[raw_offset(a.c.raw_slots, a.pos0 + row, dim)] = a.idx[(size_t)row * 640 + 512 + dim];
+}
+
+cr_status qsa_validate(const cr_geometry* g, const cr_qsa_args* spans, int n_spans, int max_rows, const char* who) {
+  if (cr_status s = check_geometry(g)) return s;
+  CR_REQUIRE(spans && n_spans >= 1, "%s: no spans", who);
+  for (int s = 0; s < n_spans; ++s) {
+    const cr_qsa_args& a = spans[s];
+    CR_REQUIRE(a.R >= 1 && a.R <= max_rows, "%s: span %d has R=%d, need 1..%d", who, s, a.R, max_rows);
+    CR_REQUIRE(a.pos0 >= 0, "%s: span %d has negative pos0", who, s);
+    CR_REQUIRE(a.sstride >= (a.pos0 + a.R) / 4, "%s: span %d score stride %d < %d blocks", who, s, a.sstride, (a.pos0 + a.R) / 4);
+    CR_REQUIRE(a.q && a.k && a.v && a.idx && a.q_norm1 && a.k_norm1 && a.iq_norm1 && a.ik_norm1 && a.c.k && a.c.v &&
+               a.c.ik_raw && a.c.ik_pool && a.sel && a.nsel && a.rope, "%s: span %d has a null buffer", who, s);
+    CR_REQUIRE(a.scores || (a.pos0 + a.R) / 4 <= CR_SEL_BLOCKS, "%s: span %d needs a score buffer", who, s);
+    CR_REQUIRE(a.c.raw_slots == 0 || a.c.raw_slots >= 16, "%s: span %d raw ring of %d slots is too small", who, s, a.c.raw_slots);
+    if (a.mrope) { set_error("%s: multimodal RoPE positions are not supported", who); return CR_ERR_UNSUPPORTED; }
+  }
+  return CR_OK;
+}
+
+int qsa_max_rows(const cr_qsa_args* spans, int n) {
+  int m = 0;
+  for (int s = 0; s < n; ++s) m = spans[s].R > m ? spans[s].R : m;
+  return m;
+}
+
+void qsa_fill_params(QsaParams& P, const cr_geometry* g, const cr_qsa_args* spans, int n) {
+  for (int s = 0; s < n; ++s) P.span[s] = spans[s];
+  int base = 0;
+  for (int s = 0; s < n; ++s) { P.base[s] = base; base += spans[s].R; }
+  P.Hq = g->q_heads; P.Hkv = g->kv_heads; P.n = n;
+}
+
+cr_status qsa_prep_launch(const cr_geometry* g, const cr_qsa_args* spans, int n_spans, int u0, __half* q_hi, int q_skip,
+                          cudaStream_t stream) {
+  use_stream(stream);
+  for (int s0 = 0; s0 < n_spans; s0 += kMaxSpans) {
+    const int n = n_spans - s0 < kMaxSpans ? n_spans - s0 : kMaxSpans;
+    QsaParams P;
+    qsa_fill_params(P, g, spans + s0, n);
+    const int Rmax = qsa_max_rows(spans + s0, n);
+    const int units = g->q_heads + 2 * g->kv_heads + 5 - u0;
+    qsa_prep_kernel<<<dim3(units, Rmax, n), 256, 0, stream>>>(P, u0, q_hi, q_skip);
+    CR_LAUNCH_CHECK("qsa_prep_kernel");
+    int completed = 0;
+    bool ring = false;
+    for (int s = 0; s < n; ++s) {
+      const cr_qsa_args& a = spans[s0 + s];
+      const int c = (a.pos0 + a.R) / 4 - a.pos0 / 4;
+      completed = c > completed ? c : completed;
+      ring = ring || (a.c.raw_slots != 0 && a.R > 8);
+    }
+    if (completed) {
+      qsa_pool_kernel<<<dim3(completed, n), 256, 0, stream>>>(P);
+      CR_LAUNCH_CHECK("qsa_pool_kernel");
+    }
+    if (ring) {
+      qsa_retain_raw_kernel<<<dim3(64 * 128 / 256, n), 256, 0, stream>>>(P);
+      CR_LAUNCH_CHECK("qsa_retain_raw_kernel");
+    }
+  }
+  return CR_OK;
+}
+
+}  // namespace cr
+
+extern "C" cr_status cr_rope_table_fill(float* table, void* stream) {
+  using namespace cr;
+  CR_REQUIRE(table, "cr_rope_table_fill: null table");
+  use_stream((cudaStream_t)stream);
+  rope_table_kernel<<<1, CR_ROPE_TABLE_FLOATS, 0, (cudaStream_t)stream>>>(table);
+  CR_LAUNCH_CHECK("rope_table_kernel");
+  return CR_OK;
+}
+
+extern "C" cr_status cr_qsa_prep(const cr_geometry* g, const cr_qsa_args* spans, int n_spans, void* stream) {
+  using namespace cr;
+  if (cr_status s = qsa_validate(g, spans, n_spans, CR_MAX_STEP_ROWS, "cr_qsa_prep")) return s;
+  return qsa_prep_launch(g, spans, n_spans, 0, nullptr, 0, (cudaStream_t)stream);
+}
+
+extern "C" cr_status cr_qsa_prefill_cache(const cr_geometry* g, const cr_qsa_args* a, void* stream) {
+  using namespace cr;
+  if (cr_status s = qsa_validate(g, a, 1, CR_MAX_PREFILL_ROWS, "cr_qsa_prefill_cache")) return s;
+  return qsa_prep_launch(g, a, 1, g->q_heads, nullptr, 0, (cudaStream_t)stream);
+}
+
+extern "C" size_t cr_qsa_pool_floats(int ctx) { return (size_t)((ctx + 127) / 128) * 4096; }
+
+extern "C" cr_status cr_qsa_cache_bytes(const cr_geometry* g, int ctx, int bounded, size_t out_bytes[4]) {
+  using namespace cr;
+  if (cr_status s = check_geometry(g)) return s;
+  CR_REQUIRE(out_bytes, "cr_qsa_cache_bytes: null output");
+  CR_REQUIRE(ctx >= 1 && ctx <= 1048576, "cr_qsa_cache_bytes: context %d is out of range", ctx);
+  out_bytes[0] = out_bytes[1] = (size_t)ctx * g->kv_heads * 256 * 2;
+  out_bytes[2] = (size_t)(bounded ? 16 : ctx) * 128 * sizeof(float);
+  out_bytes[3] = cr_qsa_pool_floats(ctx) * sizeof(float);
+  return CR_OK;
+}

@@ -1,0 +1,145 @@
+"""GPU parity of the Gated DeltaNet kernels against the numpy oracle, through the C ABI.
+Tolerances: outputs max-abs <= 2e-2 and cosine >= 0.9995 (asserted much tighter for the fp32 kernels),
+recurrent state relative L2 <= 1e-3."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import attn_oracle as ao
+from tests.gpu_util import dev, rel_l2, assert_close_attn
+
+pytestmark = pytest.mark.gpu
+
+
+def _setup(Hv, Hk, hidden, seed):
+    from crucible_strix_halo_b200 import capi, layers
+    g = capi.Geometry(hidden, 16, 2, Hv, Hk)
+    og = ao.Geometry(hidden=hidden, gdn_vheads=Hv, gdn_kheads=Hk)
+    rng = np.random.default_rng(seed)
+    Cw = og.gdn_qkv_width
+    wts = dict(conv=rng.normal(size=(Cw, 4)) * 0.5, A_log=np.clip(rng.normal(-1, 1.5, Hv), -5, 1.5),
+               dt_bias=rng.normal(size=Hv) * 0.5, gamma=1 + 0.1 * rng.normal(size=128),
+               ab=(rng.normal(size=(2 * Hv, hidden)) * 0.05).astype(np.float16),
+               suh=(1 + 0.2 * rng.normal(size=Hv * 128)).astype(np.float16))
+    w = layers.GdnWeights(g, wts["conv"], wts["A_log"], wts["dt_bias"], wts["gamma"], wts["ab"], wts["suh"])
+    return capi, layers, g, og, rng, wts, w
+
+
+def _rows(rng, og, n):
+    return rng.normal(size=(n, og.gdn_qkv_width)), rng.normal(size=(n, og.gdn_value_width)), rng.normal(size=(n, og.hidden))
+
+
+@pytest.mark.parametrize("Hv,Hk,hidden", [(4, 2, 64), (6, 2, 40), (32, 16, 2048)])
+def test_step_serial_decode_matches_oracle(Hv, Hk, hidden):
+    capi, layers, g, og, rng, wts, w = _setup(Hv, Hk, hidden, 1)
+    T = 9 if Hv > 8 else 21
+    qkv, z, x = _rows(rng, og, T)
+    ost = ao.GdnDecodeState(og)
+    ses = layers.GdnSession(g)
+    for t in range(T):
+        ref = ao.gdn_step(ost, qkv[t:t + 1], z[t:t + 1], x[t:t + 1], wts["ab"], wts["conv"], wts["A_log"], wts["dt_bias"], wts["gamma"], t, 0, 1)
+        out = layers.gdn_step(w, [dict(session=ses, qkv=dev(qkv[t:t + 1]), z=dev(z[t:t + 1]), x=dev(x[t:t + 1]), pos0=t)])[0]
+        assert_close_attn(out.cpu().numpy(), ref, max_abs=2e-4, cos=0.999999, what="row %d" % t)
+    assert rel_l2(ses.state_view().cpu().numpy(), ost.state) < 1e-5
+    np.testing.assert_allclose(ses.hist.cpu().numpy(), ost.hist, rtol=0, atol=1e-6)
+
+
+def test_step_verify_replay_commit_and_spans():
+    """Lazy commit: a verify span (commit 1), then a pass replaying the accepted rows, for two sessions with
+    different acceptance in ONE launch; final state equals serial decode of the accepted tokens."""
+    capi, layers, g, og, rng, wts, w = _setup(4, 2, 64, 2)
+    T = 20
+    data = [_rows(rng, og, T) for _ in range(2)]
+    o_st = [ao.GdnDecodeState(og) for _ in range(2)]
+    g_st = [layers.GdnSession(g) for _ in range(2)]
+    plan = [[(0, 6, 0, 1), (3, 7, 2, 1), (9, 5, 5, 3)],      # (pos0, R, replay, commit) session 0
+            [(0, 4, 0, 1), (4, 8, 3, 1), (5, 1, 0, 1)]]      # session 1: full accept then reject all (replay 0)
+    for step in range(3):
+        spans, refs = [], []
+        for s in range(2):
+            pos0, R, replay, commit = plan[s][step]
+            qkv, z, x = (d[pos0:pos0 + R] for d in data[s])
+            refs.append(ao.gdn_step(o_st[s], qkv, z, x, wts["ab"], wts["conv"], wts["A_log"], wts["dt_bias"], wts["gamma"], pos0, replay, commit))
+            spans.append(dict(session=g_st[s], qkv=dev(qkv), z=dev(z), x=dev(x), pos0=pos0, replay=replay, commit=commit))
+        outs = layers.gdn_step(w, spans)
+        for s in range(2):
+            assert_close_attn(outs[s].cpu().numpy(), refs[s], max_abs=2e-4, cos=0.999999, what="step %d span %d" % (step, s))
+            assert rel_l2(g_st[s].state_view().cpu().numpy(), o_st[s].state) < 1e-5
+            R, commit = plan[s][step][1], plan[s][step][3]
+            np.testing.assert_allclose(g_st[s].pend[:, :R - commit].cpu().numpy(), o_st[s].pend[:, :R - commit], rtol=2e-4, atol=2e-5)
+
+
+def test_step_exl3_and_bf16_outputs():
+    capi, layers, g, og, rng, wts, w = _setup(4, 2, 64, 3)
+    qkv, z, x = _rows(rng, og, 5)
+    ref = ao.gdn_step(ao.GdnDecodeState(og), qkv, z, x, wts["ab"], wts["conv"], wts["A_log"], wts["dt_bias"], wts["gamma"], 0, 0, 5)
+    sp = lambda: [dict(session=layers.GdnSession(g), qkv=dev(qkv), z=dev(z), x=dev(x), pos0=0)]
+    xh = layers.gdn_step(w, sp(), fmt=capi.OUT_EXL3_WHT)[0].cpu().numpy()
+    want = ao.exl3_epilogue(ref, wts["suh"].astype(np.float32))
+    assert np.abs(xh.astype(np.float32) - want.astype(np.float32)).max() < 4e-3   # fp16 roundings of near-ties
+    bf = layers.gdn_step(w, sp(), fmt=capi.OUT_RAW_BF16)[0].float().cpu().numpy()
+    assert np.abs(bf - ref).max() < 2e-2
+
+
+@pytest.mark.parametrize("n,pos0", [(1, 0), (3, 0), (64, 0), (65, 0), (130, 0), (200, 37)])
+def test_prefill_serial_matches_oracle(n, pos0):
+    """Rows {1,3,64,65,130} as in ref/test_prefill.py:7; pos0 > 0 takes the conv taps from the ring."""
+    capi, layers, g, og, rng, wts, w = _setup(4, 2, 64, 4)
+    qkv, z, _ = _rows(rng, og, pos0 + n)
+    ab = rng.normal(size=(pos0 + n, 8))
+    ses = layers.GdnSession(g)
+    s0 = np.zeros((4, 128, 128))
+    if pos0:
+        _, s0, _ = ao.gdn_layer(qkv[:pos0], z[:pos0], ab[:pos0, :4], ab[:pos0, 4:], wts["conv"], wts["A_log"], wts["dt_bias"], wts["gamma"], s0, og)
+        layers.GdnPrefillPlan(w, pos0).run(ses, dev(qkv[:pos0]), dev(z[:pos0]), dev(ab[:pos0]), 0)
+    ref, st, yraw = ao.gdn_layer(qkv[pos0:], z[pos0:], ab[pos0:, :4], ab[pos0:, 4:], wts["conv"], wts["A_log"], wts["dt_bias"], wts["gamma"], s0, og,
+                                 history=qkv[pos0 - 3:pos0] if pos0 else None)
+    plan = layers.GdnPrefillPlan(w, n, raw_y=True)
+    out = plan.run(ses, dev(qkv[pos0:]), dev(z[pos0:]), dev(ab[pos0:]), pos0).cpu().numpy()
+    assert_close_attn(out, ref, max_abs=5e-4, cos=0.999999)
+    assert rel_l2(plan.raw_y.cpu().numpy(), yraw.reshape(n, -1)) < 3e-5
+    assert rel_l2(ses.state_view().cpu().numpy(), st) < 3e-5
+    keep = min(16, pos0 + n)
+    for p in range(pos0 + n - keep, pos0 + n):
+        np.testing.assert_array_equal(ses.hist[p & 15].cpu().numpy(), qkv[p].astype(np.float32))
+
+
+def test_prefill_then_decode_is_continuous_and_bf16_inputs():
+    """A prefill part followed by decode steps equals one long serial run; bf16 inputs are read exactly."""
+    capi, layers, g, og, rng, wts, w = _setup(4, 2, 64, 5)
+    n, m = 70, 4
+    bf = lambda a: torch.tensor(a, dtype=torch.float32).bfloat16().float().numpy().astype(np.float64)
+    qkv, z, x = _rows(rng, og, n + m)
+    qkv, z = bf(qkv), bf(z)
+    ab_pre = bf(rng.normal(size=(n, 8)))
+    ses = layers.GdnSession(g)
+    plan = layers.GdnPrefillPlan(w, n, in_dtype=capi.IN_BF16)
+    out = plan.run(ses, dev(qkv[:n], torch.bfloat16), dev(z[:n], torch.bfloat16), dev(ab_pre, torch.bfloat16), 0).cpu().numpy()
+    ref, st, _ = ao.gdn_layer(qkv[:n], z[:n], ab_pre[:, :4], ab_pre[:, 4:], wts["conv"], wts["A_log"], wts["dt_bias"], wts["gamma"], np.zeros((4, 128, 128)), og)
+    assert_close_attn(out, ref, max_abs=5e-4, cos=0.999999)
+    ost = ao.GdnDecodeState(og)
+    ost.state[...] = st
+    for p in range(n - 16, n):
+        ost.hist[p & 15] = qkv[p]
+    refd = ao.gdn_step(ost, qkv[n:], z[n:], x[n:], wts["ab"], wts["conv"], wts["A_log"], wts["dt_bias"], wts["gamma"], n, 0, m)
+    outd = layers.gdn_step(w, [dict(session=ses, qkv=dev(qkv[n:]), z=dev(z[n:]), x=dev(x[n:]), pos0=n)])[0].cpu().numpy()
+    assert_close_attn(outd, refd, max_abs=5e-4, cos=0.999999)
+
+
+def test_materialize_applies_lazy_scale():
+    import ctypes as C
+    capi, layers, g, og, rng, wts, w = _setup(4, 2, 64, 6)
+    ses = layers.GdnSession(g)
+    ses.state.normal_()
+    ses.state[4 * 16384:] = 0
+    before = ses.state.clone()
+    ses.state[4 * 16384 + 1] = 0.5
+    ses.state[4 * 16384 + 2] = 1.0
+    ptrs = (C.c_void_p * 1)(ses.state.data_ptr())
+    capi.check(capi.lib.cr_gdn_materialize(C.byref(g), ptrs, 1, None))
+    torch.cuda.synchronize()
+    want = before.clone()
+    want[16384:2 * 16384] *= 0.5
+    want[4 * 16384 + 1] = 1.0
+    want[4 * 16384 + 2] = 1.0
+    assert torch.equal(ses.state, want)
