@@ -44,6 +44,14 @@ __device__ __forceinline__ float sigmoidf_(float v) { return 1.f / (1.f + __expf
 __device__ __forceinline__ float siluf_(float v) { return v / (1.f + __expf(-v)); }
 __device__ __forceinline__ float bf16_bits_to_float(uint16_t u) { return __uint_as_float((uint32_t)u << 16); }
 
+// Round to tf32 (10-bit mantissa, nearest, ties away): the tensor-core unit ignores the low 13 bits of an
+// fp32 operand, so operands are rounded when they are written.
+__device__ __forceinline__ float tf32r(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return __uint_as_float(r);
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int m = 16; m > 0; m >>= 1) v += __shfl_xor_sync(0xffffffffu, v, m);

@@ -72,7 +72,9 @@ __global__ void __launch_bounds__(256) gdn_prep_kernel(GdnPrefillParams P) {
       if (i >= rows) break;
       const float ss = red[i][part * 4] + red[i][part * 4 + 1] + red[i][part * 4 + 2] + red[i][part * 4 + 3];
       const float sc = rsqrtf(ss + kEps) * (part ? 1.f : kInvSqrt128);
-      dst[((size_t)(r0 + i) * P.Hk + u) * 128 + j] = val[i] * sc;
+      float o = val[i] * sc;
+      if (P.tf32) o = tf32r(o);
+      dst[((size_t)(r0 + i) * P.Hk + u) * 128 + j] = o;
     }
   } else {
 #pragma unroll
@@ -258,6 +260,7 @@ extern "C" cr_status cr_gdn_prefill(const cr_geometry* g, const cr_gdn_prefill_a
   GdnPrefillParams P;
   P.a = a; P.ab_logits = args->ab_logits;
   P.Hv = g->gdn_vheads; P.Hk = g->gdn_kheads; P.fmt = (int)fmt;
+  P.tf32 = algo == CR_GDN_CHUNK_TC;
   gdn_workspace_layout(g, a.R, &P, (char*)args->workspace);
   if (args->raw_y) P.yraw = args->raw_y;
   const bool bf = args->in_dtype == CR_IN_BF16;

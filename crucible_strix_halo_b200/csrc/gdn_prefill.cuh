@@ -13,6 +13,7 @@ struct GdnPrefillParams {
   float* yraw;             // [R][Hv][128] un-gated readout
   char* chunk_ws;          // workspace of the chunked scan
   int Hv, Hk, fmt;
+  int tf32;                // 1: prep rounds q/k to tf32 (operands of the tensor-core scan)
 };
 
 bool gdn_chunk_available();

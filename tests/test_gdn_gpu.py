@@ -143,3 +143,55 @@ def test_materialize_applies_lazy_scale():
     want[4 * 16384 + 1] = 1.0
     want[4 * 16384 + 2] = 1.0
     assert torch.equal(ses.state, want)
+
+
+@pytest.mark.parametrize("n,pos0", [(1, 0), (3, 0), (64, 0), (65, 0), (130, 0), (200, 37), (517, 0)])
+def test_prefill_chunk_tc_matches_oracle(n, pos0):
+    """The chunk-64 tensor-core scan (tf32 operands) against the fp64 oracle: outputs within the path's tolerance
+    (max-abs 2e-2, cosine 0.9995; asserted at 2e-3), recurrent state within relative 1e-3."""
+    capi, layers, g, og, rng, wts, w = _setup(4, 2, 64, 7)
+    qkv, z, _ = _rows(rng, og, pos0 + n)
+    ab = rng.normal(size=(pos0 + n, 8))
+    ses = layers.GdnSession(g)
+    s0 = np.zeros((4, 128, 128))
+    if pos0:
+        _, s0, _ = ao.gdn_layer(qkv[:pos0], z[:pos0], ab[:pos0, :4], ab[:pos0, 4:], wts["conv"], wts["A_log"], wts["dt_bias"], wts["gamma"], s0, og)
+        layers.GdnPrefillPlan(w, pos0).run(ses, dev(qkv[:pos0]), dev(z[:pos0]), dev(ab[:pos0]), 0, capi.GDN_CHUNK_TC)
+    ref, st, yraw = ao.gdn_layer(qkv[pos0:], z[pos0:], ab[pos0:, :4], ab[pos0:, 4:], wts["conv"], wts["A_log"], wts["dt_bias"], wts["gamma"], s0, og,
+                                 history=qkv[pos0 - 3:pos0] if pos0 else None)
+    plan = layers.GdnPrefillPlan(w, n, raw_y=True)
+    out = plan.run(ses, dev(qkv[pos0:]), dev(z[pos0:]), dev(ab[pos0:]), pos0, capi.GDN_CHUNK_TC).cpu().numpy()
+    assert_close_attn(out, ref, max_abs=2e-3, cos=0.99999)
+    assert rel_l2(plan.raw_y.cpu().numpy(), yraw.reshape(n, -1)) < 1e-3
+    assert rel_l2(ses.state_view().cpu().numpy(), st) < 1e-3
+
+
+def test_prefill_chunk_tc_full_geometry_against_serial_scan():
+    """Benchmark geometry (32 value / 16 key heads), 4096 bf16 rows in two calls of 2048: the tensor-core scan
+    agrees with the exact fp32 serial scan on the same device (state rel <= 1e-3) and with the oracle on one head."""
+    capi, layers, g, og, rng, wts, w = _setup(32, 16, 2048, 8)
+    T = 4096
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    qkv = torch.randn(T, og.gdn_qkv_width, device="cuda", generator=gen).bfloat16()
+    z = torch.randn(T, og.gdn_value_width, device="cuda", generator=gen).bfloat16()
+    ab = torch.randn(T, 64, device="cuda", generator=gen).bfloat16()
+    res = {}
+    for algo in (capi.GDN_SERIAL_F32, capi.GDN_CHUNK_TC):
+        ses = layers.GdnSession(g)
+        plan = layers.GdnPrefillPlan(w, 2048, in_dtype=capi.IN_BF16, raw_y=True)
+        outs = []
+        for p0 in (0, 2048):
+            outs.append(plan.run(ses, qkv[p0:p0 + 2048], z[p0:p0 + 2048], ab[p0:p0 + 2048], p0, algo).clone())
+        res[algo] = (torch.cat(outs).cpu().numpy(), ses.state_view().cpu().numpy())
+    o_s, s_s = res[capi.GDN_SERIAL_F32]
+    o_c, s_c = res[capi.GDN_CHUNK_TC]
+    assert rel_l2(s_c, s_s) < 1e-3
+    assert_close_attn(o_c, o_s, max_abs=5e-3, cos=0.9999)
+    # one head against the fp64 oracle (the serial oracle finishes 4096 rows of one head in a second)
+    f = lambda a: a.float().cpu().numpy().astype(np.float64)
+    q, k, v = ao.gdn_frontend(f(qkv), wts["conv"], og)
+    glog, beta = ao.gdn_gates(f(ab)[:, :32], f(ab)[:, 32:], wts["A_log"], wts["dt_bias"])
+    h = 5
+    _, st = ao.gdn_serial(q[:, h // 2], k[:, h // 2], v[:, h], glog[:, h], beta[:, h], np.zeros((128, 128)))
+    assert rel_l2(s_c[h], st) < 1e-3
+    assert rel_l2(s_s[h], st) < 1e-4

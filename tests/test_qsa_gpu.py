@@ -130,7 +130,7 @@ def test_decode_steps_match_oracle(Hq, ctx0):
         if nb > 512:
             assert int(ses.nsel[0]) == 512
             got = ses.sel[0].cpu().numpy()
-            np.testing.assert_allclose(ses.scores[0, :nb].cpu().numpy(), scs[0], rtol=0, atol=2e-5)
+            np.testing.assert_allclose(ses.scores[0, :nb].cpu().numpy(), scs[0], rtol=0, atol=2e-4)
             assert ao.selection_agrees(scs[0], got, sels[0]), "selection differs beyond near ties at p=%d" % p
             if not np.array_equal(got, sels[0]):
                 continue    # a near tie went the other way: outputs legitimately differ
