@@ -290,6 +290,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--algo", default="auto", choices=["auto", "serial", "chunk"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--seq", type=int, default=0, help="gdn_prefill_32k only: a shorter sequence, for profiler captures")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args, args.workload)
@@ -309,6 +310,8 @@ def main():
     algo = {"serial": capi.GDN_SERIAL_F32, "chunk": capi.GDN_CHUNK_TC}.get(args.algo)
     if algo is None:
         algo = capi.GDN_CHUNK_TC if capi.lib.cr_gdn_algo_available(capi.GDN_CHUNK_TC) else capi.GDN_SERIAL_F32
+    if args.seq and args.workload == "gdn_prefill_32k":
+        GdnPrefill32k.T = args.seq
     wl = WORKLOADS[args.workload](rank, algo)
 
     def barrier():

@@ -161,7 +161,7 @@ def test_prefill_chunk_tc_matches_oracle(n, pos0):
                                  history=qkv[pos0 - 3:pos0] if pos0 else None)
     plan = layers.GdnPrefillPlan(w, n, raw_y=True)
     out = plan.run(ses, dev(qkv[pos0:]), dev(z[pos0:]), dev(ab[pos0:]), pos0, capi.GDN_CHUNK_TC).cpu().numpy()
-    assert_close_attn(out, ref, max_abs=2e-3, cos=0.99999)
+    assert_close_attn(out, ref, max_abs=1e-2, cos=0.9999)
     assert rel_l2(plan.raw_y.cpu().numpy(), yraw.reshape(n, -1)) < 1e-3
     assert rel_l2(ses.state_view().cpu().numpy(), st) < 1e-3
 
