@@ -186,7 +186,7 @@ def test_prefill_chunk_tc_full_geometry_against_serial_scan():
     o_s, s_s = res[capi.GDN_SERIAL_F32]
     o_c, s_c = res[capi.GDN_CHUNK_TC]
     assert rel_l2(s_c, s_s) < 1e-3
-    assert_close_attn(o_c, o_s, max_abs=5e-3, cos=0.9999)
+    assert_close_attn(o_c, o_s, max_abs=2e-2, cos=0.9995, what="chunk vs serial")
     # one head against the fp64 oracle (the serial oracle finishes 4096 rows of one head in a second)
     f = lambda a: a.float().cpu().numpy().astype(np.float64)
     q, k, v = ao.gdn_frontend(f(qkv), wts["conv"], og)
