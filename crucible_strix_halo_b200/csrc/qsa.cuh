@@ -18,6 +18,7 @@ cr_status qsa_prep_launch(const cr_geometry* g, const cr_qsa_args* spans, int n_
                           cudaStream_t stream);
 cr_status qsa_score_launch(const cr_geometry* g, const cr_qsa_args* spans, int n_spans, cudaStream_t stream);
 cr_status qsa_topk_launch(const cr_geometry* g, const cr_qsa_args* spans, int n_spans, cudaStream_t stream);
+cr_status qsa_topk_cluster_launch(const QsaParams& P, int Rmax, int n, int nb_max, cudaStream_t stream);
 cr_status qsa_select_launch(const cr_geometry* g, const cr_qsa_args* spans, int n_spans, cudaStream_t stream);
 // splits: KV splits per (row, KV head). p0/p1: position window (shard mode) or 0 / INT_MAX.
 cr_status qsa_attn_launch(const cr_geometry* g, const cr_qsa_args* spans, int n_spans, float* partials, int splits,

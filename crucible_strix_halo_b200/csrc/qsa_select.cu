@@ -299,6 +299,10 @@ cr_status qsa_topk_launch(const cr_geometry* g, const cr_qsa_args* spans, int n_
     const int Rmax = qsa_max_rows(spans + s0, n);
     int nb_max = 0;
     for (int s = 0; s < n; ++s) nb_max = max(nb_max, (spans[s0 + s].pos0 + spans[s0 + s].R) / 4);
+    if (nb_max > 8192 && nb_max <= 262144) {   // long rows: 8 SMs per row
+      if (cr_status st = qsa_topk_cluster_launch(P, Rmax, n, nb_max, stream)) return st;
+      continue;
+    }
     cr_status st = topk_dispatch(nb_max, [&](auto pt, auto reg) -> cr_status {
       qsa_topk_kernel<decltype(pt)::value, decltype(reg)::value><<<dim3(Rmax, n), 1024, 0, stream>>>(P);
       CR_LAUNCH_CHECK("qsa_topk_kernel");
