@@ -166,19 +166,28 @@ __global__ void __launch_bounds__(256) qsa_merge_kernel(const __grid_constant__ 
     const size_t i = part_major ? ((size_t)p * rows_total + row) * P.Hq + h : ((size_t)row * P.Hq + h) * nparts + p;
     return partials + i * CR_QSA_PART;
   };
-  float m = -INFINITY;
-  for (int p = 0; p < nparts; ++p) {
-    const float* s = rec(p);
-    if (s[1] != 0.f) m = fmaxf(m, s[0]);
+  // (m, l) of the parts are combined by the first warp; every thread then sums its channel with the factors
+  // from shared memory, so the loads of the second pass are independent of each other.
+  __shared__ float fs[32];
+  __shared__ float ml[2];
+  if (d < 32) {
+    float pm = -INFINITY, pl = 0.f;
+    if (d < nparts) {
+      const float2 v = *reinterpret_cast<const float2*>(rec(d));
+      pl = v.y;
+      pm = pl != 0.f ? v.x : -INFINITY;
+    }
+    const float mx = warp_max(pm);
+    const float f = pl != 0.f ? __expf(pm - mx) : 0.f;
+    const float lt = warp_sum(pl * f);
+    fs[d] = f;
+    if (d == 0) { ml[0] = mx; ml[1] = lt; }
   }
-  float lsum = 0.f, o = 0.f;
-  for (int p = 0; p < nparts; ++p) {
-    const float* s = rec(p);
-    if (s[1] == 0.f) continue;
-    const float f = __expf(s[0] - m);
-    lsum = fmaf(s[1], f, lsum);
-    o = fmaf(s[2 + d], f, o);
-  }
+  __syncthreads();
+  const float m = ml[0], lsum = ml[1];
+  float o = 0.f;
+#pragma unroll 8
+  for (int p = 0; p < nparts; ++p) o = fmaf(rec(p)[2 + d], fs[p], o);
   if (partial_out) {      // shard mode: one merged partial per (row, head)
     float* dst = partial_out + ((size_t)row * P.Hq + h) * CR_QSA_PART;
     if (d == 0) { dst[0] = m; dst[1] = lsum; }
@@ -306,6 +315,6 @@ extern "C" cr_status cr_qsa_merge_partials(const cr_geometry* g, const cr_qsa_ar
   using namespace cr;
   if (cr_status s = qsa_validate(g, a, 1, CR_MAX_PREFILL_ROWS, "cr_qsa_merge_partials")) return s;
   if (cr_status s = check_out(a, 1, fmt, "cr_qsa_merge_partials")) return s;
-  CR_REQUIRE(partials && ranks >= 1, "cr_qsa_merge_partials: need gathered partials");
+  CR_REQUIRE(partials && ranks >= 1 && ranks <= 32, "cr_qsa_merge_partials: need gathered partials of 1..32 ranks");
   return qsa_merge_launch(g, a, 1, partials, ranks, true, nullptr, fmt, (cudaStream_t)stream);
 }

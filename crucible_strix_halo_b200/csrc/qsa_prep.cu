@@ -40,15 +40,22 @@ __device__ __forceinline__ void cnorm_smem(float* x, int n, const float* w1, flo
 
 __device__ __forceinline__ bool raw_uses_chunk(int slots, int rows) { return slots != 0 && rows > 8; }
 
-// grid (units, Rmax, spans), 256 threads.  Units: [0,Hq) query heads, [Hq,Hq+Hkv) key heads,
+__device__ __forceinline__ void pool_block(const cr_qsa_args& a, int b, float* x, float* red);
+
+// grid (units + pool_units, Rmax, spans), 256 threads.  Blocks x >= units (row 0 only) pool completed blocks.  Units: [0,Hq) query heads, [Hq,Hq+Hkv) key heads,
 // [Hq+Hkv, Hq+2Hkv) value heads, then 4 indexer-query heads, then the raw indexer key.
 // u0 skips leading units (u0 = Hq runs the cache units only).  q_hi (optional): fp16 copy of the prepared
 // queries [R][Hq][256] for the prefill attention kernels; rows < q_skip are not written to q_hi.
-__global__ void __launch_bounds__(256) qsa_prep_kernel(const __grid_constant__ QsaParams P, int u0, __half* q_hi, int q_skip) {
+__global__ void __launch_bounds__(256) qsa_prep_kernel(const __grid_constant__ QsaParams P, int u0, __half* q_hi, int q_skip, int units) {
   const cr_qsa_args& a = P.span[blockIdx.z];
   const int r = blockIdx.y;
   if (r >= a.R) return;
   __shared__ float x[256], red[8];
+  if ((int)blockIdx.x >= units) {
+    const int b = a.pos0 / 4 + ((int)blockIdx.x - units);
+    if (r == 0 && b < (a.pos0 + a.R) / 4) pool_block(a, b, x, red);
+    return;
+  }
   const int u = blockIdx.x + u0, j = threadIdx.x, p = a.pos0 + r;
   const int Hq = P.Hq, Hkv = P.Hkv;
   if (u < Hq) {
@@ -81,20 +88,17 @@ __global__ void __launch_bounds__(256) qsa_prep_kernel(const __grid_constant__ Q
   }
 }
 
-// Pooled key of block b = pos0/4 + blockIdx.x of span blockIdx.y, if these rows complete it.
-__global__ void __launch_bounds__(256) qsa_pool_kernel(const __grid_constant__ QsaParams P) {
-  const cr_qsa_args& a = P.span[blockIdx.y];
-  __shared__ float x[256], red[8];
-  const int b = a.pos0 / 4 + blockIdx.x, j = threadIdx.x;
-  if (b >= (a.pos0 + a.R) / 4) return;
+// Pooled key of block b (complete within rows pos0..pos0+R-1 or earlier): mean of 4 raw keys -> fp16 round ->
+// CN-RMSNorm -> RoPE at the block start.  Raw keys of this call's rows are read from the input rows, older ones
+// from the cache, so the result does not depend on the prep units having run.
+__device__ __forceinline__ void pool_block(const cr_qsa_args& a, int b, float* x, float* red) {
+  const int j = threadIdx.x;
   if (j < 128) {
     float m = 0.f;
 #pragma unroll
     for (int t = 0; t < 4; ++t) {
       const int pos = b * 4 + t;
-      m += (raw_uses_chunk(a.c.raw_slots, a.R) && pos >= a.pos0)
-               ? a.idx[(size_t)(pos - a.pos0) * 640 + 512 + j]
-               : a.c.ik_raw[raw_offset(a.c.raw_slots, pos, j)];
+      m += pos >= a.pos0 ? a.idx[(size_t)(pos - a.pos0) * 640 + 512 + j] : a.c.ik_raw[raw_offset(a.c.raw_slots, pos, j)];
     }
     x[j] = round_h(m * 0.25f);
   }
@@ -102,6 +106,15 @@ __global__ void __launch_bounds__(256) qsa_pool_kernel(const __grid_constant__ Q
   cnorm_smem(x, 128, a.ik_norm1, red);
   rope64_smem(x, a.rope, b * 4);
   if (j < 128) a.c.ik_pool[pool_offset(b, j)] = x[j];
+}
+
+// Block b = pos0/4 + blockIdx.x of span blockIdx.y, if these rows complete it (bulk rows; steps pool inside prep).
+__global__ void __launch_bounds__(256) qsa_pool_kernel(const __grid_constant__ QsaParams P) {
+  const cr_qsa_args& a = P.span[blockIdx.y];
+  __shared__ float x[256], red[8];
+  const int b = a.pos0 / 4 + blockIdx.x;
+  if (b >= (a.pos0 + a.R) / 4) return;
+  pool_block(a, b, x, red);
 }
 
 // Bulk rows with a raw ring: keep the newest min(R, slots) raw keys (after every pool has read the old tail).
@@ -154,22 +167,24 @@ cr_status qsa_prep_launch(const cr_geometry* g, const cr_qsa_args* spans, int n_
     qsa_fill_params(P, g, spans + s0, n);
     const int Rmax = qsa_max_rows(spans + s0, n);
     const int units = g->q_heads + 2 * g->kv_heads + 5 - u0;
-    qsa_prep_kernel<<<dim3(units, Rmax, n), 256, 0, stream>>>(P, u0, q_hi, q_skip);
-    CR_LAUNCH_CHECK("qsa_prep_kernel");
-    int completed = 0;
+    int completed = 0, keep = 0;
     bool ring = false;
     for (int s = 0; s < n; ++s) {
       const cr_qsa_args& a = spans[s0 + s];
       const int c = (a.pos0 + a.R) / 4 - a.pos0 / 4;
       completed = c > completed ? c : completed;
       ring = ring || (a.c.raw_slots != 0 && a.R > 8);
+      keep = a.c.raw_slots > keep ? a.c.raw_slots : keep;
     }
-    if (completed) {
+    const bool fused_pool = Rmax <= 16;            // steps: pooling rides in the prep launch
+    qsa_prep_kernel<<<dim3(units + (fused_pool ? completed : 0), Rmax, n), 256, 0, stream>>>(P, u0, q_hi, q_skip, units);
+    CR_LAUNCH_CHECK("qsa_prep_kernel");
+    if (completed && !fused_pool) {
       qsa_pool_kernel<<<dim3(completed, n), 256, 0, stream>>>(P);
       CR_LAUNCH_CHECK("qsa_pool_kernel");
     }
     if (ring) {
-      qsa_retain_raw_kernel<<<dim3(64 * 128 / 256, n), 256, 0, stream>>>(P);
+      qsa_retain_raw_kernel<<<dim3((keep * 128 + 255) / 256, n), 256, 0, stream>>>(P);
       CR_LAUNCH_CHECK("qsa_retain_raw_kernel");
     }
   }

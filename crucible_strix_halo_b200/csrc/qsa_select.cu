@@ -72,6 +72,87 @@ __global__ void __launch_bounds__(256) qsa_score_kernel(const __grid_constant__ 
   }
 }
 
+// Same scores for one or two rows with 128-bit loads: lane l reads blocks 4(l%8)..+3 of dims l/8, l/8+4, ...,
+// so a warp load covers four 128-byte lines and the tile costs 32 load instructions per lane instead of 128.
+// The four lanes that share a block group add their partial dots with two shuffles.
+template <int RT>
+__global__ void __launch_bounds__(256) qsa_score4_kernel(const __grid_constant__ QsaParams P) {
+  const cr_qsa_args& a = P.span[blockIdx.z];
+  const int rg0 = blockIdx.y * RT;
+  if (rg0 >= a.R) return;
+  const int nr = min(RT, a.R - rg0);
+  const int nb_hi = (a.pos0 + rg0 + nr) / 4;
+  if (nb_hi <= CR_SEL_BLOCKS) return;
+  const int t = threadIdx.x, w = t >> 5, l = t & 31;
+  __shared__ float4 iqs[128][RT];
+  for (int i = t; i < 128 * RT; i += 256) {
+    const int d = i / RT, r = i % RT;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (r < nr) {
+      const float* iq = a.idx + (size_t)(rg0 + r) * 640;
+      v = make_float4(iq[d], iq[128 + d], iq[256 + d], iq[384 + d]);
+    }
+    iqs[d][r] = v;
+  }
+  __syncthreads();
+  const int tile = blockIdx.x * 8 + w;
+  if (tile * 32 >= nb_hi) return;
+  const int bq = (l & 7) * 4, dl = l >> 3;
+  const float4* pt = reinterpret_cast<const float4*>(a.c.ik_pool + (size_t)tile * 4096 + dl * 32 + bq);
+  float acc[RT][4][4];                        // [row][block][head]
+#pragma unroll
+  for (int r = 0; r < RT; ++r)
+#pragma unroll
+    for (int b = 0; b < 4; ++b) acc[r][b][0] = acc[r][b][1] = acc[r][b][2] = acc[r][b][3] = 0.f;
+#pragma unroll
+  for (int it0 = 0; it0 < 32; it0 += 8) {
+    float4 key[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) key[j] = __ldg(pt + (it0 + j) * 32);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float kb[4] = {key[j].x, key[j].y, key[j].z, key[j].w};
+#pragma unroll
+      for (int r = 0; r < RT; ++r) {
+        const float4 q = iqs[(it0 + j) * 4 + dl][r];
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+          acc[r][b][0] = fmaf(q.x, kb[b], acc[r][b][0]);
+          acc[r][b][1] = fmaf(q.y, kb[b], acc[r][b][1]);
+          acc[r][b][2] = fmaf(q.z, kb[b], acc[r][b][2]);
+          acc[r][b][3] = fmaf(q.w, kb[b], acc[r][b][3]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < RT; ++r)
+#pragma unroll
+    for (int b = 0; b < 4; ++b)
+#pragma unroll
+      for (int h = 0; h < 4; ++h) {
+        acc[r][b][h] += __shfl_xor_sync(0xffffffffu, acc[r][b][h], 8);
+        acc[r][b][h] += __shfl_xor_sync(0xffffffffu, acc[r][b][h], 16);
+      }
+  if (dl != 0) return;
+#pragma unroll
+  for (int r = 0; r < RT; ++r) {
+    if (r >= nr) break;
+    const int nb = (a.pos0 + rg0 + r + 1) / 4;
+    if (nb <= CR_SEL_BLOCKS) continue;
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+      const int blk = tile * 32 + bq + b;
+      if (blk >= nb) continue;
+      float s = fmaxf(acc[r][b][0], 0.f);
+      s += fmaxf(acc[r][b][1], 0.f);
+      s += fmaxf(acc[r][b][2], 0.f);
+      s += fmaxf(acc[r][b][3], 0.f);
+      a.scores[(size_t)(rg0 + r) * a.sstride + blk] = s * kInvSqrt128;
+    }
+  }
+}
+
 // ---- exact top-512 ------------------------------------------------------------------------------------
 // Source element idx lives at keys[(idx / 512) * group_stride + idx % 512] (group_stride = 512: contiguous);
 // ids (optional) uses the same addressing and marks padding with id < 0.  1024 threads.
@@ -273,8 +354,13 @@ cr_status qsa_score_launch(const cr_geometry* g, const cr_qsa_args* spans, int n
     if (nb_max <= CR_SEL_BLOCKS) continue;
     const int tiles = (nb_max + 31) / 32;
     cr_status st;
-    if (Rmax == 1) st = score_launch_t<1>(P, tiles, Rmax, n, stream);
-    else if (Rmax == 2) st = score_launch_t<2>(P, tiles, Rmax, n, stream);
+    if (Rmax <= 2) {
+      const dim3 grid((tiles + 7) / 8, 1, n);
+      if (Rmax == 1) qsa_score4_kernel<1><<<grid, 256, 0, stream>>>(P);
+      else qsa_score4_kernel<2><<<grid, 256, 0, stream>>>(P);
+      CR_LAUNCH_CHECK("qsa_score_kernel");
+      st = CR_OK;
+    }
     else if (Rmax <= 4) st = score_launch_t<4>(P, tiles, Rmax, n, stream);
     else st = score_launch_t<8>(P, tiles, Rmax, n, stream);
     if (st) return st;
