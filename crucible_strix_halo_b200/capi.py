@@ -83,6 +83,7 @@ _protos = {
     "cr_qsa_prep": (C.c_int, [G, C.POINTER(QsaArgs), C.c_int, P]),
     "cr_qsa_select": (C.c_int, [G, C.POINTER(QsaArgs), C.c_int, P, C.c_size_t, P]),
     "cr_qsa_attn": (C.c_int, [G, C.POINTER(QsaArgs), C.c_int, P, C.c_size_t, C.c_int, P]),
+    "cr_qsa_attn_static": (C.c_int, [G, C.POINTER(QsaArgs), C.c_int, C.c_int, P]),
     "cr_qsa_step": (C.c_int, [G, C.POINTER(QsaArgs), C.c_int, P, C.c_size_t, C.c_int, P]),
     "cr_qsa_prefill_scratch_bytes": (C.c_size_t, [G, C.c_int]),
     "cr_qsa_prefill_cache": (C.c_int, [G, C.POINTER(QsaArgs), P]),

@@ -195,6 +195,17 @@ cr_status cr_qsa_select(const cr_geometry* g, const cr_qsa_args* spans, int n_sp
 cr_status cr_qsa_attn(const cr_geometry* g, const cr_qsa_args* spans, int n_spans, void* scratch,
                       size_t scratch_bytes, cr_out_format fmt, void* stream);
 
+/* No counterpart in the reference (its engine always owns scratch).  Same work and output as cr_qsa_attn, for
+ * callers that cannot allocate device memory or pass scratch: a serving process whose HBM is fully committed to
+ * caches, a plugin without access to its host's allocator, or a caller that must not allocate while a stream
+ * capture is open.  The split-KV partials live in an array inside the library (8.45 MB per GPU, held until the
+ * process exits).  Limit: total rows x q_heads <= CR_STATIC_ATTN_MAX_ROW_HEADS, else CR_ERR_INVALID.  All calls on
+ * a device share the array: calls whose kernels may overlap on the GPU race.  The first call on a device resolves
+ * the array's address; make it before any stream capture starts. */
+enum { CR_STATIC_ATTN_MAX_ROW_HEADS = 256 };
+cr_status cr_qsa_attn_static(const cr_geometry* g, const cr_qsa_args* spans, int n_spans, cr_out_format fmt,
+                             void* stream);
+
 /* prep + select + attn, the whole AttentionCore of a QSA layer for decode / verify
  * (engine/runtime/batch_forward.h:300-333). */
 cr_status cr_qsa_step(const cr_geometry* g, const cr_qsa_args* spans, int n_spans, void* scratch,
