@@ -1,0 +1,80 @@
+// Shared pieces of the chunk-64 WY Gated DeltaNet scan (gdn_chunk_local.cu, gdn_chunk_scan.cu).
+//
+// The algebra is the reference's chunked form (ref/prefill_ref.py:16-34;
+// engine/layers/kernels/prefill_gdn.h:111-249).  Per chunk of 64 tokens and value head, with G the cumulative
+// log-decay inside the chunk:
+//   L   = tril(beta_i (k_i . k_j) exp(G_i - G_j), -1)        T = (I + L)^-1
+//   W   = T (beta e^G K)      Ut = T (beta V)                QKd = tril((q_i . k_j) exp(G_i - G_j))
+//   U   = Ut - W S            Y = e^G (Q S) + QKd U          S <- e^{G_end} S + (K e^{G_end - G})^T U
+// exp(-G) is never formed.  Products use tf32 operands (rounded to nearest when written) with fp32
+// accumulation; the carried state is fp32; the triangular inverse is exact fp32.  tf32 keeps the recurrent
+// state within 1e-3 relative of the fp64 oracle (3.4e-4 over 4096 tokens); single-pass bf16 does not (3e-3).
+#pragma once
+#include "gdn_prefill.cuh"
+
+namespace cr {
+
+constexpr int kChunk = 64;
+constexpr int kLdK = 132;   // [64][128] operand read row-major as A, or as B stored [n][k]: stride % 32 == 4
+constexpr int kLdX = 136;   // [64][128] operand read as B stored [k][n], or as transposed A: stride % 32 == 8
+constexpr int kLdM = 68;    // [64][64] operand read row-major as A
+
+struct ChunkWs {
+  float* W;    // [Hv][chunks][64][128]  tf32
+  float* Ut;   // [Hv][chunks][64][128]  fp32
+  float* QKd;  // [Hv][chunks][64][64]   tf32
+  float* G;    // [Hv][chunks][64]       cumulative log decay inside the chunk
+  int chunks;
+};
+
+__device__ __forceinline__ void mma_tf32(float (&d)[4], const float (&a)[4], float b0, float b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(__float_as_uint(a[0])), "r"(__float_as_uint(a[1])), "r"(__float_as_uint(a[2])), "r"(__float_as_uint(a[3])),
+        "r"(__float_as_uint(b0)), "r"(__float_as_uint(b1)));
+}
+
+// acc[16 x 8NT] += A[16 x 8KT] B.  A row-major in shared memory (lda % 32 == 4), or A_T: stored [k][m]
+// (lda % 32 == 8).  B stored [k][n] (ldb % 32 == 8), or B_NK: stored [n][k] (ldb % 32 == 4).
+// Operands hold tf32-rounded values.  Bank-conflict free for the stated strides.
+template <int NT, int KT, bool A_T, bool B_NK>
+__device__ __forceinline__ void warp_gemm(float (&acc)[NT][4], const float* A, int lda, const float* B, int ldb) {
+  const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+#pragma unroll
+  for (int kk = 0; kk < KT; ++kk) {
+    float a[4];
+    if constexpr (!A_T) {
+      a[0] = A[g * lda + kk * 8 + t];       a[1] = A[(g + 8) * lda + kk * 8 + t];
+      a[2] = A[g * lda + kk * 8 + t + 4];   a[3] = A[(g + 8) * lda + kk * 8 + t + 4];
+    } else {
+      a[0] = A[(kk * 8 + t) * lda + g];     a[1] = A[(kk * 8 + t) * lda + g + 8];
+      a[2] = A[(kk * 8 + t + 4) * lda + g]; a[3] = A[(kk * 8 + t + 4) * lda + g + 8];
+    }
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+      float b0, b1;
+      if constexpr (B_NK) {
+        b0 = B[(n * 8 + g) * ldb + kk * 8 + t];
+        b1 = B[(n * 8 + g) * ldb + kk * 8 + t + 4];
+      } else {
+        b0 = B[(kk * 8 + t) * ldb + n * 8 + g];
+        b1 = B[(kk * 8 + t + 4) * ldb + n * 8 + g];
+      }
+      mma_tf32(acc[n], a, b0, b1);
+    }
+  }
+}
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+  const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+  const int bytes = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;\n" ::: "memory"); }
+
+cr_status gdn_chunk_local_launch(const cr_geometry* g, const GdnPrefillParams& P, const ChunkWs& ws, bool bf16_in, cudaStream_t stream);
+cr_status gdn_chunk_scan_launch(const cr_geometry* g, const GdnPrefillParams& P, const ChunkWs& ws, cudaStream_t stream);
+
+}  // namespace cr

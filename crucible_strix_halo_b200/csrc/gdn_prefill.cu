@@ -260,18 +260,18 @@ extern "C" cr_status cr_gdn_prefill(const cr_geometry* g, const cr_gdn_prefill_a
   GdnPrefillParams P;
   P.a = a; P.ab_logits = args->ab_logits;
   P.Hv = g->gdn_vheads; P.Hk = g->gdn_kheads; P.fmt = (int)fmt;
-  P.tf32 = algo == CR_GDN_CHUNK_TC;
+  P.tf32 = 0;
   gdn_workspace_layout(g, a.R, &P, (char*)args->workspace);
   if (args->raw_y) P.yraw = args->raw_y;
   const bool bf = args->in_dtype == CR_IN_BF16;
-  const dim3 pg((a.R + 15) / 16, g->gdn_kheads + g->gdn_vheads / 2 + 1);
-  if (bf) gdn_prep_kernel<true><<<pg, 256, 0, stream>>>(P); else gdn_prep_kernel<false><<<pg, 256, 0, stream>>>(P);
-  CR_LAUNCH_CHECK("gdn_prep_kernel");
   if (algo == CR_GDN_SERIAL_F32) {
+    const dim3 pg((a.R + 15) / 16, g->gdn_kheads + g->gdn_vheads / 2 + 1);
+    if (bf) gdn_prep_kernel<true><<<pg, 256, 0, stream>>>(P); else gdn_prep_kernel<false><<<pg, 256, 0, stream>>>(P);
+    CR_LAUNCH_CHECK("gdn_prep_kernel");
     gdn_scan_serial_kernel<<<g->gdn_vheads * 4, 256, 0, stream>>>(P);
     CR_LAUNCH_CHECK("gdn_scan_serial_kernel");
-  } else {
-    if (cr_status s = gdn_chunk_scan(g, P, stream)) return s;
+  } else {   // the chunked scan prepares its rows itself
+    if (cr_status s = gdn_chunk_scan(g, P, bf, stream)) return s;
   }
   const unsigned gg = (unsigned)(((long long)a.R * g->gdn_vheads + 7) / 8);
   if (bf) gdn_gate_kernel<true><<<gg, 256, 0, stream>>>(P); else gdn_gate_kernel<false><<<gg, 256, 0, stream>>>(P);
