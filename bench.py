@@ -119,7 +119,7 @@ class GdnPrefill32k:
         self.h_out = torch.empty(T, 4096, dtype=torch.bfloat16).pin_memory()
         self.h2d = self.h_qkv.numel() * 2 + self.h_z.numel() * 2 + self.h_ab.numel() * 2
         self.d2h = self.h_out.numel() * 2
-        self.dominant = "gdn_scan_serial_kernel" if algo == capi.GDN_SERIAL_F32 else "gdn_chunk_scan_kernel"
+        self.dominant = {capi.GDN_SERIAL_F32: "gdn_scan_serial_kernel", capi.GDN_CHUNK_TC: "gdn_chunk_local_kernel", capi.GDN_CHUNK_MMA: "gdn_chunk_scan_kernel"}[algo]
         self.dominant_bytes = self.alg_bytes               # the layer's algorithmic bytes, charged to its longest kernel
         self.launches_per_step = 4 if algo == capi.GDN_SERIAL_F32 else 5
 
@@ -136,7 +136,7 @@ class GdnPrefill32k:
 
     def config(self):
         return {"workload": self.name, "seq_len": self.T, "gdn_heads": "16qk/32v x128", "chunk": 64, "sessions_per_gpu": 1,
-                "algo": "serial_f32" if self.algo == self.capi.GDN_SERIAL_F32 else "chunk64_tc",
+                "algo": {0: "serial_f32", 1: "chunk64_tcgen05", 2: "chunk64_mma_sync"}[self.algo],
                 "l2": "inputs (0.8 GB per step) exceed the 126 MB L2"}
 
 
@@ -315,7 +315,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--workload", default="gdn_prefill_32k", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--algo", default="auto", choices=["auto", "serial", "chunk"])
+    ap.add_argument("--algo", default="auto", choices=["auto", "serial", "chunk", "mma"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--seq", type=int, default=0, help="gdn_prefill_32k only: a shorter sequence, for profiler captures")
     args = ap.parse_args()
@@ -334,7 +334,7 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
         dist.barrier()
     from crucible_strix_halo_b200 import capi
-    algo = {"serial": capi.GDN_SERIAL_F32, "chunk": capi.GDN_CHUNK_TC}.get(args.algo)
+    algo = {"serial": capi.GDN_SERIAL_F32, "chunk": capi.GDN_CHUNK_TC, "mma": capi.GDN_CHUNK_MMA}.get(args.algo)
     if algo is None:
         algo = capi.GDN_CHUNK_TC if capi.lib.cr_gdn_algo_available(capi.GDN_CHUNK_TC) else capi.GDN_SERIAL_F32
     if args.seq and args.workload == "gdn_prefill_32k":

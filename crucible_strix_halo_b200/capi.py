@@ -8,7 +8,7 @@ LIB_PATH = os.path.join(_HERE, "libcrucible_attn.so")
 OK, ERR_INVALID, ERR_CUDA, ERR_UNSUPPORTED, ERR_TIMEOUT = range(5)
 OUT_RAW_F32, OUT_RAW_BF16, OUT_EXL3_WHT = range(3)
 IN_F32, IN_BF16 = range(2)
-GDN_SERIAL_F32, GDN_CHUNK_TC = range(2)
+GDN_SERIAL_F32, GDN_CHUNK_TC, GDN_CHUNK_MMA = range(3)
 PEND_FLOATS, QSA_PART, QSA_SPLITS, SEL_BLOCKS = 258, 258, 32, 512
 
 
@@ -92,8 +92,10 @@ _protos = {
     "cr_qsa_merge_candidates": (C.c_int, [G, C.POINTER(QsaArgs), C.c_int, P, P, P]),
     "cr_qsa_shard_attn": (C.c_int, [G, C.POINTER(QsaArgs), C.c_int, C.c_int, P, P, C.c_size_t, P]),
     "cr_qsa_merge_partials": (C.c_int, [G, C.POINTER(QsaArgs), C.c_int, P, C.c_int, P]),
+    "cr_debug_umma_gemm": (C.c_int, [P, P, P, C.c_int, C.c_int, C.c_int, C.c_int, P, P]),
     "cr_last_error": (C.c_char_p, []),
     "cr_version": (C.c_int, []),
+    "cr_device_status": (C.c_int, []),
     "cr_kernel_launches": (C.c_ulonglong, []),
     "cr_profile_enable": (C.c_int, [C.c_int]),
     "cr_profile_begin": (C.c_int, [P]),

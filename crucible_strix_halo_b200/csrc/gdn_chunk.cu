@@ -12,8 +12,10 @@ static size_t chunk_layout(const cr_geometry* g, int rows, ChunkWs* ws, char* ba
   auto take = [&](size_t bytes) { const size_t o = off; off += (bytes + 255) & ~(size_t)255; return o; };
   const size_t oW = take(Hv * chunks * 64 * 128 * 4), oU = take(Hv * chunks * 64 * 128 * 4);
   const size_t oQ = take(Hv * chunks * 64 * 64 * 4), oG = take(Hv * chunks * 64 * 4);
+  const size_t oQt = take(Hv * chunks * 8192 * 4), oKt = take((size_t)g->gdn_kheads * chunks * 8192 * 4);
   if (ws) {
     ws->W = (float*)(base + oW); ws->Ut = (float*)(base + oU); ws->QKd = (float*)(base + oQ); ws->G = (float*)(base + oG);
+    ws->Qt = (float*)(base + oQt); ws->Kt = (float*)(base + oKt);
     ws->chunks = (int)chunks;
   }
   return off;
@@ -21,11 +23,13 @@ static size_t chunk_layout(const cr_geometry* g, int rows, ChunkWs* ws, char* ba
 
 size_t gdn_chunk_workspace_bytes(const cr_geometry* g, int rows) { return chunk_layout(g, rows, nullptr, nullptr); }
 
-cr_status gdn_chunk_scan(const cr_geometry* g, const GdnPrefillParams& P, bool bf16_in, cudaStream_t stream) {
+cr_status gdn_chunk_scan(const cr_geometry* g, const GdnPrefillParams& P, bool bf16_in, bool tcgen05, cudaStream_t stream) {
   ChunkWs ws;
   chunk_layout(g, P.a.R, &ws, P.chunk_ws);
-  if (cr_status s = gdn_chunk_local_launch(g, P, ws, bf16_in, stream)) return s;
-  return gdn_chunk_scan_launch(g, P, ws, stream);
+  if (cr_status s = gdn_chunk_local_launch(g, P, ws, bf16_in, tcgen05, stream)) return s;
+  return tcgen05 ? gdn_chunk_scan_tc_launch(g, P, ws, stream) : gdn_chunk_scan_launch(g, P, ws, stream);
 }
 
 }  // namespace cr
+
+extern "C" int cr_device_status(void) { return cr::gdn_scan_status_read(); }

@@ -24,6 +24,8 @@ struct ChunkWs {
   float* Ut;   // [Hv][chunks][64][128]  fp32
   float* QKd;  // [Hv][chunks][64][64]   tf32
   float* G;    // [Hv][chunks][64]       cumulative log decay inside the chunk
+  float* Qt;   // [Hv][chunks][32][64][4]  e^G Q as a K-major tile (tcgen05 scan only)
+  float* Kt;   // [Hk][chunks][16][128][4] K^T as a K-major tile (tcgen05 scan only)
   int chunks;
 };
 
@@ -74,7 +76,10 @@ __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool vali
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;\n" ::: "memory"); }
 
-cr_status gdn_chunk_local_launch(const cr_geometry* g, const GdnPrefillParams& P, const ChunkWs& ws, bool bf16_in, cudaStream_t stream);
+cr_status gdn_chunk_local_launch(const cr_geometry* g, const GdnPrefillParams& P, const ChunkWs& ws, bool bf16_in, bool umma_layout,
+                                 cudaStream_t stream);
+cr_status gdn_chunk_scan_tc_launch(const cr_geometry* g, const GdnPrefillParams& P, const ChunkWs& ws, cudaStream_t stream);
+int gdn_scan_status_read();
 cr_status gdn_chunk_scan_launch(const cr_geometry* g, const GdnPrefillParams& P, const ChunkWs& ws, cudaStream_t stream);
 
 }  // namespace cr

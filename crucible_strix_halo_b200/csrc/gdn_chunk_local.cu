@@ -47,7 +47,8 @@ __device__ __forceinline__ void conv_rows(const cr_gdn_args& a, int C, int row0,
   }
 }
 
-template <bool BF16>
+// UM: operands for the tcgen05 scan are written as K-major tiles float[K/4][rows][4] (plus Qt = e^G Q and K^T).
+template <bool BF16, bool UM>
 __global__ void __launch_bounds__(256, 2) gdn_chunk_local_kernel(GdnPrefillParams P, ChunkWs ws) {
   extern __shared__ __align__(16) float sm[];
   float* Ks = sm;                       // [64][132] khat (tf32)
@@ -90,6 +91,14 @@ __global__ void __launch_bounds__(256, 2) gdn_chunk_local_kernel(GdnPrefillParam
     }
   }
   __syncthreads();
+  if constexpr (UM) {   // K^T of the chunk, K-major over tokens: unit (token/4, key) holds 4 tokens of one key
+    float* kt = ws.Kt + ((size_t)kh * ws.chunks + c) * 8192;
+    for (int i = t; i < 16 * 128; i += 256) {
+      const int key = i & 127, tc = i >> 7;
+      *reinterpret_cast<float4*>(kt + (size_t)i * 4) = make_float4(Ks[(4 * tc) * kLdK + key], Ks[(4 * tc + 1) * kLdK + key],
+                                                                   Ks[(4 * tc + 2) * kLdK + key], Ks[(4 * tc + 3) * kLdK + key]);
+    }
+  }
   // Gram matrices stay in registers: warps 0-3 hold K K^T, warps 4-7 hold Q K^T, 16 rows each
   const int mt = w & 3, nh = w >> 2;
   float gram[8][4];
@@ -140,7 +149,8 @@ __global__ void __launch_bounds__(256, 2) gdn_chunk_local_kernel(GdnPrefillParam
             const float b = bs[row];
             *reinterpret_cast<float2*>(LT + row * kLdM + col) = make_float2(col < row ? b * v0 * p0 : 0.f, col + 1 < row ? b * v1 * p1 : 0.f);
           } else {
-            *reinterpret_cast<float2*>(qkd + row * 64 + col) = make_float2(col <= row ? tf32r(v0 * p0) : 0.f, col + 1 <= row ? tf32r(v1 * p1) : 0.f);
+            const int at = UM ? ((col >> 2) * 64 + row) * 4 + (col & 3) : row * 64 + col;
+            *reinterpret_cast<float2*>(qkd + at) = make_float2(col <= row ? tf32r(v0 * p0) : 0.f, col + 1 <= row ? tf32r(v1 * p1) : 0.f);
           }
         }
     }
@@ -149,6 +159,16 @@ __global__ void __launch_bounds__(256, 2) gdn_chunk_local_kernel(GdnPrefillParam
       const float4 kv = *reinterpret_cast<const float4*>(Ks + row * kLdK + c4);
       const float e = es[row];
       *reinterpret_cast<float4*>(Qx + row * kLdX + c4) = make_float4(tf32r(e * kv.x), tf32r(e * kv.y), tf32r(e * kv.z), tf32r(e * kv.w));
+    }
+    if constexpr (UM) {   // Qt = e^G Q of this value head, K-major over keys (q was published to qn above)
+      float* qt = ws.Qt + unit * 8192;
+      for (int i = t; i < 32 * 64; i += 256) {
+        const int row = i & 63, kc = i >> 6;
+        float4 q = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (row < valid) q = *reinterpret_cast<const float4*>(P.qn + ((size_t)(r0 + row) * P.Hk + kh) * 128 + kc * 4);
+        const float e = __expf(Gs[row]);
+        *reinterpret_cast<float4*>(qt + (size_t)i * 4) = make_float4(tf32r(e * q.x), tf32r(e * q.y), tf32r(e * q.z), tf32r(e * q.w));
+      }
     }
     __syncthreads();
     // T = (I + L)^-1 in exact fp32, blocked 16x16, in place.  Diagonal blocks: forward substitution, one thread
@@ -198,11 +218,21 @@ __global__ void __launch_bounds__(256, 2) gdn_chunk_local_kernel(GdnPrefillParam
 #pragma unroll
       for (int n = 0; n < 8; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
       warp_gemm<8, 8, false, false>(acc, LT + mt * 16 * kLdM, kLdM, Qx + nh * 64, kLdX);
-      float* dst = ws.W + (unit * 64 + mt * 16) * 128 + nh * 64;
+      if constexpr (UM) {
+        float* dst = ws.W + unit * 8192;
 #pragma unroll
-      for (int n = 0; n < 8; ++n) {
-        *reinterpret_cast<float2*>(dst + g * 128 + n * 8 + 2 * tq) = make_float2(tf32r(acc[n][0]), tf32r(acc[n][1]));
-        *reinterpret_cast<float2*>(dst + (g + 8) * 128 + n * 8 + 2 * tq) = make_float2(tf32r(acc[n][2]), tf32r(acc[n][3]));
+        for (int n = 0; n < 8; ++n) {
+          const int col = nh * 64 + n * 8 + 2 * tq, r_lo = mt * 16 + g;
+          *reinterpret_cast<float2*>(dst + ((col >> 2) * 64 + r_lo) * 4 + (col & 3)) = make_float2(tf32r(acc[n][0]), tf32r(acc[n][1]));
+          *reinterpret_cast<float2*>(dst + ((col >> 2) * 64 + r_lo + 8) * 4 + (col & 3)) = make_float2(tf32r(acc[n][2]), tf32r(acc[n][3]));
+        }
+      } else {
+        float* dst = ws.W + (unit * 64 + mt * 16) * 128 + nh * 64;
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+          *reinterpret_cast<float2*>(dst + g * 128 + n * 8 + 2 * tq) = make_float2(tf32r(acc[n][0]), tf32r(acc[n][1]));
+          *reinterpret_cast<float2*>(dst + (g + 8) * 128 + n * 8 + 2 * tq) = make_float2(tf32r(acc[n][2]), tf32r(acc[n][3]));
+        }
       }
     }
     __syncthreads();
@@ -231,16 +261,21 @@ __global__ void __launch_bounds__(256, 2) gdn_chunk_local_kernel(GdnPrefillParam
   }
 }
 
-cr_status gdn_chunk_local_launch(const cr_geometry* g, const GdnPrefillParams& P, const ChunkWs& ws, bool bf16_in, cudaStream_t stream) {
+cr_status gdn_chunk_local_launch(const cr_geometry* g, const GdnPrefillParams& P, const ChunkWs& ws, bool bf16_in, bool umma_layout,
+                                 cudaStream_t stream) {
   static bool configured = false;
   if (!configured) {
-    CR_CUDA(cudaFuncSetAttribute(gdn_chunk_local_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kLocalSmem));
-    CR_CUDA(cudaFuncSetAttribute(gdn_chunk_local_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kLocalSmem));
+    CR_CUDA(cudaFuncSetAttribute(gdn_chunk_local_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kLocalSmem));
+    CR_CUDA(cudaFuncSetAttribute(gdn_chunk_local_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kLocalSmem));
+    CR_CUDA(cudaFuncSetAttribute(gdn_chunk_local_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kLocalSmem));
+    CR_CUDA(cudaFuncSetAttribute(gdn_chunk_local_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kLocalSmem));
     configured = true;
   }
   const dim3 grid(ws.chunks, g->gdn_kheads);
-  if (bf16_in) gdn_chunk_local_kernel<true><<<grid, 256, kLocalSmem, stream>>>(P, ws);
-  else gdn_chunk_local_kernel<false><<<grid, 256, kLocalSmem, stream>>>(P, ws);
+  if (bf16_in && umma_layout) gdn_chunk_local_kernel<true, true><<<grid, 256, kLocalSmem, stream>>>(P, ws);
+  else if (bf16_in) gdn_chunk_local_kernel<true, false><<<grid, 256, kLocalSmem, stream>>>(P, ws);
+  else if (umma_layout) gdn_chunk_local_kernel<false, true><<<grid, 256, kLocalSmem, stream>>>(P, ws);
+  else gdn_chunk_local_kernel<false, false><<<grid, 256, kLocalSmem, stream>>>(P, ws);
   CR_LAUNCH_CHECK("gdn_chunk_local_kernel");
   return CR_OK;
 }

@@ -232,7 +232,7 @@ extern "C" size_t cr_gdn_prefill_workspace_bytes(const cr_geometry* g, int rows)
 }
 
 extern "C" int cr_gdn_algo_available(cr_gdn_algo algo) {
-  return algo == CR_GDN_SERIAL_F32 || (algo == CR_GDN_CHUNK_TC && cr::gdn_chunk_available());
+  return algo == CR_GDN_SERIAL_F32 || ((algo == CR_GDN_CHUNK_TC || algo == CR_GDN_CHUNK_MMA) && cr::gdn_chunk_available());
 }
 
 extern "C" cr_status cr_gdn_prefill(const cr_geometry* g, const cr_gdn_prefill_args* args, cr_gdn_algo algo,
@@ -251,7 +251,7 @@ extern "C" cr_status cr_gdn_prefill(const cr_geometry* g, const cr_gdn_prefill_a
   CR_REQUIRE(fmt == CR_OUT_RAW_F32 || fmt == CR_OUT_RAW_BF16 || fmt == CR_OUT_EXL3_WHT, "cr_gdn_prefill: bad output format");
   CR_REQUIRE(fmt != CR_OUT_EXL3_WHT || a.suh_out, "cr_gdn_prefill: suh_out needed for the EXL3 output");
   CR_REQUIRE(fmt == CR_OUT_EXL3_WHT || a.pack_rows == 0, "cr_gdn_prefill: packed layout only with the EXL3 output");
-  CR_REQUIRE(algo == CR_GDN_SERIAL_F32 || algo == CR_GDN_CHUNK_TC, "cr_gdn_prefill: unknown algorithm");
+  CR_REQUIRE(algo == CR_GDN_SERIAL_F32 || algo == CR_GDN_CHUNK_TC || algo == CR_GDN_CHUNK_MMA, "cr_gdn_prefill: unknown algorithm");
   const size_t need = gdn_workspace_layout(g, a.R, nullptr, nullptr);
   CR_REQUIRE(args->workspace && args->workspace_bytes >= need, "cr_gdn_prefill: workspace of %zu bytes needed, %zu given",
              need, args->workspace_bytes);
@@ -271,7 +271,7 @@ extern "C" cr_status cr_gdn_prefill(const cr_geometry* g, const cr_gdn_prefill_a
     gdn_scan_serial_kernel<<<g->gdn_vheads * 4, 256, 0, stream>>>(P);
     CR_LAUNCH_CHECK("gdn_scan_serial_kernel");
   } else {   // the chunked scan prepares its rows itself
-    if (cr_status s = gdn_chunk_scan(g, P, bf, stream)) return s;
+    if (cr_status s = gdn_chunk_scan(g, P, bf, algo == CR_GDN_CHUNK_TC, stream)) return s;
   }
   const unsigned gg = (unsigned)(((long long)a.R * g->gdn_vheads + 7) / 8);
   if (bf) gdn_gate_kernel<true><<<gg, 256, 0, stream>>>(P); else gdn_gate_kernel<false><<<gg, 256, 0, stream>>>(P);

@@ -18,6 +18,6 @@ struct GdnPrefillParams {
 
 bool gdn_chunk_available();
 size_t gdn_chunk_workspace_bytes(const cr_geometry* g, int rows);
-cr_status gdn_chunk_scan(const cr_geometry* g, const GdnPrefillParams& P, bool bf16_in, cudaStream_t stream);
+cr_status gdn_chunk_scan(const cr_geometry* g, const GdnPrefillParams& P, bool bf16_in, bool tcgen05, cudaStream_t stream);
 
 }  // namespace cr

@@ -1,0 +1,138 @@
+// tcgen05 (5th-generation tensor core) primitives for sm_100a: TMEM allocation, shared-memory matrix
+// descriptors, instruction descriptors, MMA issue, commit to an mbarrier, bounded waits and TMEM loads.
+//
+// Operand layouts used here are the un-swizzled canonical ones, which are plain arrays for 32-bit elements:
+//   K-major  operand X[rows][K]  is stored as  float[K/4][rows][4]     (16-byte units: K chunk, then row)
+//   MN-major operand X[K][mn]    is stored as  float[mn/4][K][4]       (16-byte units: mn group, then k)
+// A core matrix is 8 consecutive 16-byte units (128 contiguous bytes) in both cases, so shared-memory writes
+// by consecutive lanes are conflict-free and no swizzle pattern has to be reproduced by hand.
+#pragma once
+#include <cstdint>
+#include <cuda_runtime.h>
+
+namespace cr {
+namespace umma {
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+// ---- TMEM ------------------------------------------------------------------------------------------
+// One full warp allocates `cols` (power of two, 32..512) columns; the base address lands in *slot (shared).
+__device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(slot)), "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+// Generic-proxy writes to shared memory become visible to the tensor core (async proxy).
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
+
+// ---- mbarrier ----------------------------------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_fence_init() { asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory"); }
+// Waits for the phase with the given parity; gives up after `limit` polls and returns false.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit = 1u << 22) {
+  const uint32_t addr = smem_u32(bar);
+  for (uint32_t i = 0; i < limit; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}\n"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+
+// ---- descriptors -------------------------------------------------------------------------------------
+// Shared-memory matrix descriptor, no swizzle (layout type 0), descriptor version 1 (Blackwell).
+// lbo / sbo in bytes: K-major: lbo = distance between the 16-byte K chunks, sbo = between 8-row groups;
+// MN-major: sbo = distance between the 16-byte mn groups, lbo = between groups of 8 k rows.
+__device__ __forceinline__ uint64_t smem_desc(const void* base, uint32_t lbo, uint32_t sbo) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_u32(base) & 0x3FFFF) >> 4);
+  d |= (uint64_t)((lbo >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)((sbo >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)1 << 46;
+  return d;
+}
+// K-major operand stored float[K/4][rows][4]; k0 = first K element of this MMA (multiple of 8).
+__device__ __forceinline__ uint64_t desc_kmajor(const float* base, int rows, int k0) {
+  return smem_desc(base + (size_t)(k0 / 4) * rows * 4, (uint32_t)rows * 16u, 128u);
+}
+// MN-major operand stored float[mn/4][K][4] with K rows in total; k0 as above.
+__device__ __forceinline__ uint64_t desc_mnmajor(const float* base, int K, int k0) {
+  return smem_desc(base + (size_t)k0 * 4, 128u, (uint32_t)K * 16u);
+}
+// Instruction descriptor for kind::tf32, fp32 accumulation.
+__host__ __device__ constexpr uint32_t idesc_tf32(int M, int N, bool a_mn, bool b_mn) {
+  return (1u << 4) | (2u << 7) | (2u << 10) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) |
+         ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
+// ---- MMA ---------------------------------------------------------------------------------------------
+// D[tmem] (+)= A[smem] B[smem]; one thread issues.  accumulate = 0 overwrites D.
+__device__ __forceinline__ void mma_tf32_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// The mbarrier receives one arrival when every MMA issued so far by this thread has completed.
+__device__ __forceinline__ void commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// ---- TMEM -> registers -----------------------------------------------------------------------------------
+// 32 consecutive fp32 columns of this thread's lane (lane = 32 * (warp % 4) + lane id).
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+        "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+// TMEM address of (lane quarter of this warp, column).
+__device__ __forceinline__ uint32_t tmem_addr(uint32_t base, int warp, int col) {
+  return base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)col;
+}
+
+}  // namespace umma
+}  // namespace cr
+
+// ---- bulk copies global -> shared with mbarrier completion (TMA, untiled) --------------------------------
+namespace cr {
+namespace umma {
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// dst and src 16-byte aligned, bytes a multiple of 16.  Completes `bytes` on the mbarrier.
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(smem_u32(dst)),
+               "l"(src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+// K-major operand with padded planes: float[K/4][plane_units][4], rows < plane_units.
+__device__ __forceinline__ uint64_t desc_kmajor_padded(const float* base, int plane_units, int k0) {
+  return smem_desc(base + (size_t)(k0 / 4) * plane_units * 4, (uint32_t)plane_units * 16u, 128u);
+}
+}  // namespace umma
+}  // namespace cr

@@ -100,8 +100,9 @@ cr_status cr_gdn_step(const cr_geometry* g, const cr_gdn_args* spans, int n_span
 typedef enum {
   CR_GDN_SERIAL_F32 = 0,  /* exact fp32 token-serial scan (the role of GdnPersistentColumnKernel,
                              engine/layers/kernels/prefill_gdn.h:285-315) */
-  CR_GDN_CHUNK_TC = 1     /* chunk-64 WY form on tensor cores (LaunchGdnPrefill / LaunchGdnMicro,
-                             engine/layers/kernels/prefill_gdn.h:1229-1279) */
+  CR_GDN_CHUNK_TC = 1,    /* chunk-64 WY form, scan on tcgen05 tensor cores with TMEM accumulators
+                             (LaunchGdnPrefill / LaunchGdnMicro, engine/layers/kernels/prefill_gdn.h:1229-1279) */
+  CR_GDN_CHUNK_MMA = 2    /* the same algebra with warp-level mma.sync in the scan (kept as the comparison point) */
 } cr_gdn_algo;
 
 /* Replaces struct GdnPrefill (engine/layers/kernels/prefill_gdn.h:12-29).  input.replay = 0,
@@ -256,6 +257,8 @@ cr_status cr_qsa_merge_partials(const cr_geometry* g, const cr_qsa_args* a, int 
  * ------------------------------------------------------------------------------------------------- */
 const char* cr_last_error(void);   /* text of the last error on this thread */
 int cr_version(void);
+/* 0, or non-zero if a bounded device-side wait gave up since the library was loaded (synchronises the device). */
+int cr_device_status(void);
 /* Number of kernels this library has launched in this process (for launch accounting in benches). */
 unsigned long long cr_kernel_launches(void);
 
@@ -266,6 +269,12 @@ unsigned long long cr_kernel_launches(void);
 cr_status cr_profile_enable(int on);
 cr_status cr_profile_begin(void* stream);
 int cr_profile_collect(char* names, float* ms, int* calls, int max_stages);
+
+/* Self-check of the tensor-core (tcgen05) building blocks: D[128][N] = A B in tf32 on one CTA.
+ * A is [128][K] (a_mn = 0) or [K][128] (a_mn = 1); B is [N][K] (b_mn = 0) or [K][N] (b_mn = 1).
+ * *status (device int) becomes 1 if the bounded wait on the MMA gave up.  No counterpart in the reference. */
+cr_status cr_debug_umma_gemm(const float* A, const float* B, float* D, int K, int N, int a_mn, int b_mn, int* status,
+                             void* stream);
 
 #ifdef __cplusplus
 }

@@ -145,22 +145,25 @@ def test_materialize_applies_lazy_scale():
     assert torch.equal(ses.state, want)
 
 
+@pytest.mark.parametrize("algo_name", ["tc", "mma"])
 @pytest.mark.parametrize("n,pos0", [(1, 0), (3, 0), (64, 0), (65, 0), (130, 0), (200, 37), (517, 0)])
-def test_prefill_chunk_tc_matches_oracle(n, pos0):
+def test_prefill_chunk_tc_matches_oracle(n, pos0, algo_name):
     """The chunk-64 tensor-core scan (tf32 operands) against the fp64 oracle: outputs within the path's tolerance
     (max-abs 2e-2, cosine 0.9995; asserted at 2e-3), recurrent state within relative 1e-3."""
     capi, layers, g, og, rng, wts, w = _setup(4, 2, 64, 7)
+    algo = capi.GDN_CHUNK_TC if algo_name == "tc" else capi.GDN_CHUNK_MMA
     qkv, z, _ = _rows(rng, og, pos0 + n)
     ab = rng.normal(size=(pos0 + n, 8))
     ses = layers.GdnSession(g)
     s0 = np.zeros((4, 128, 128))
     if pos0:
         _, s0, _ = ao.gdn_layer(qkv[:pos0], z[:pos0], ab[:pos0, :4], ab[:pos0, 4:], wts["conv"], wts["A_log"], wts["dt_bias"], wts["gamma"], s0, og)
-        layers.GdnPrefillPlan(w, pos0).run(ses, dev(qkv[:pos0]), dev(z[:pos0]), dev(ab[:pos0]), 0, capi.GDN_CHUNK_TC)
+        layers.GdnPrefillPlan(w, pos0).run(ses, dev(qkv[:pos0]), dev(z[:pos0]), dev(ab[:pos0]), 0, algo)
     ref, st, yraw = ao.gdn_layer(qkv[pos0:], z[pos0:], ab[pos0:, :4], ab[pos0:, 4:], wts["conv"], wts["A_log"], wts["dt_bias"], wts["gamma"], s0, og,
                                  history=qkv[pos0 - 3:pos0] if pos0 else None)
     plan = layers.GdnPrefillPlan(w, n, raw_y=True)
-    out = plan.run(ses, dev(qkv[pos0:]), dev(z[pos0:]), dev(ab[pos0:]), pos0, capi.GDN_CHUNK_TC).cpu().numpy()
+    out = plan.run(ses, dev(qkv[pos0:]), dev(z[pos0:]), dev(ab[pos0:]), pos0, algo).cpu().numpy()
+    assert capi.lib.cr_device_status() == 0
     assert_close_attn(out, ref, max_abs=1e-2, cos=0.9999)
     assert rel_l2(plan.raw_y.cpu().numpy(), yraw.reshape(n, -1)) < 1e-3
     assert rel_l2(ses.state_view().cpu().numpy(), st) < 1e-3
@@ -176,7 +179,7 @@ def test_prefill_chunk_tc_full_geometry_against_serial_scan():
     z = torch.randn(T, og.gdn_value_width, device="cuda", generator=gen).bfloat16()
     ab = torch.randn(T, 64, device="cuda", generator=gen).bfloat16()
     res = {}
-    for algo in (capi.GDN_SERIAL_F32, capi.GDN_CHUNK_TC):
+    for algo in (capi.GDN_SERIAL_F32, capi.GDN_CHUNK_TC, capi.GDN_CHUNK_MMA):
         ses = layers.GdnSession(g)
         plan = layers.GdnPrefillPlan(w, 2048, in_dtype=capi.IN_BF16, raw_y=True)
         outs = []
@@ -185,6 +188,8 @@ def test_prefill_chunk_tc_full_geometry_against_serial_scan():
         res[algo] = (torch.cat(outs).cpu().numpy(), ses.state_view().cpu().numpy())
     o_s, s_s = res[capi.GDN_SERIAL_F32]
     o_c, s_c = res[capi.GDN_CHUNK_TC]
+    assert rel_l2(res[capi.GDN_CHUNK_MMA][1], s_s) < 1e-3
+    assert capi.lib.cr_device_status() == 0
     assert rel_l2(s_c, s_s) < 1e-3
     assert_close_attn(o_c, o_s, max_abs=2e-2, cos=0.9995, what="chunk vs serial")
     # one head against the fp64 oracle (the serial oracle finishes 4096 rows of one head in a second)
