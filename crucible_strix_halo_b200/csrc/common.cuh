@@ -99,7 +99,7 @@ __host__ __device__ __forceinline__ size_t out_index(int r, int c, int width, in
 
 // Loads element i of a row buffer that is fp32 or bf16.
 template <bool BF16>
-__device__ __forceinline__ float load_in(const void* p, size_t i) {
+__device__ __forceinline__ float load_in(const void* p, long long i) {
   if constexpr (BF16) return bf16_bits_to_float(reinterpret_cast<const uint16_t*>(p)[i]);
   else return reinterpret_cast<const float*>(p)[i];
 }

@@ -16,6 +16,8 @@
 namespace cr {
 
 __device__ int g_gdn_scan_status = 0;
+__device__ long long g_prof[16];
+#define PROF(i) do { if (blockIdx.x == 0 && t == 32) { long long now_ = clock64(); g_prof[i] += now_ - last_; last_ = now_; } } while (0)
 
 template <int NC>
 struct TcSmem {
@@ -85,6 +87,10 @@ __global__ void __launch_bounds__(128) gdn_chunk_scan_tc_kernel(GdnPrefillParams
   if (t == 0) { load_w(0); load_q(0); load_k(0); load_qk(0); }
 
   constexpr uint32_t idesc64 = umma::idesc_tf32(64, NC, false, false), idesc128 = umma::idesc_tf32(128, NC, false, false);
+  // descriptors of the first K step; a step of 8 along K advances the start address by 2 planes (16-byte units)
+  const uint64_t dW = umma::desc_kmajor(Wsm, 64, 0), dQ = umma::desc_kmajor(Qsm, 64, 0), dK = umma::desc_kmajor(Ksm, 128, 0);
+  const uint64_t dQK = umma::desc_kmajor(QKsm, 64, 0), dS = umma::desc_kmajor_padded(Ssm, NCP, 0);
+  const uint64_t dU = umma::desc_kmajor_padded(Usm, NCP, 0), dUp = umma::desc_kmajor_padded(Upsm, NCP, 0);
   float ut[NC];                                           // Ut row of this thread's token
   float Gtok = 0.f, Gend = 0.f;
   auto fetch_rows = [&](int c) {
@@ -102,22 +108,20 @@ __global__ void __launch_bounds__(128) gdn_chunk_scan_tc_kernel(GdnPrefillParams
   };
   fetch_rows(0);
 
+  long long last_ = clock64();
   for (int c = 0; c < nch; ++c) {
     const uint32_t ph = c & 1;
+    PROF(0);
     if (t == 0) {
       wait(fullW, ph);
       umma::fence_after_sync();
 #pragma unroll
-      for (int k0 = 0; k0 < 128; k0 += 8)
-        umma::mma_tf32_ss(tm, umma::desc_kmajor(Wsm, 64, k0), umma::desc_kmajor_padded(Ssm, NCP, k0), idesc64, k0 > 0);
+      for (int s8 = 0; s8 < 16; ++s8) umma::mma_tf32_ss(tm, dW + (uint64_t)(s8 * 128), dS + (uint64_t)(s8 * 2 * NCP), idesc64, s8 > 0);
       umma::commit(d1a);
-      wait(fullQ, ph);
-#pragma unroll
-      for (int k0 = 0; k0 < 128; k0 += 8)
-        umma::mma_tf32_ss(tm + NC, umma::desc_kmajor(Qsm, 64, k0), umma::desc_kmajor_padded(Ssm, NCP, k0), idesc64, k0 > 0);
     }
     wait(d1a, ph);
     umma::fence_after_sync();
+    PROF(1);
     if (t == 0 && c + 1 < nch) load_w(c + 1);
     const float gt = Gtok, ge = Gend;
     {   // U = Ut - W S, transposed into shared memory (tf32), and U' = e^{G_end - G} U
@@ -137,27 +141,33 @@ __global__ void __launch_bounds__(128) gdn_chunk_scan_tc_kernel(GdnPrefillParams
         }
       }
     }
+    PROF(2);
     umma::fence_async_smem();
     umma::fence_before_sync();
     __syncthreads();
     umma::fence_after_sync();
+    PROF(3);
     if (t == 0) {
       wait(fullK, ph);
 #pragma unroll
-      for (int k0 = 0; k0 < 64; k0 += 8)
-        umma::mma_tf32_ss(tm + 2 * NC, umma::desc_kmajor(Ksm, 128, k0), umma::desc_kmajor_padded(Upsm, NCP, k0), idesc128, k0 > 0);
+      for (int s8 = 0; s8 < 8; ++s8) umma::mma_tf32_ss(tm + 2 * NC, dK + (uint64_t)(s8 * 256), dUp + (uint64_t)(s8 * 2 * NCP), idesc128, s8 > 0);
       umma::commit(d2);
+      // the readout products are off the chain: Qt S^T (S^T stays untouched until d3), then + QKd U^T
+      wait(fullQ, ph);
+#pragma unroll
+      for (int s8 = 0; s8 < 16; ++s8) umma::mma_tf32_ss(tm + NC, dQ + (uint64_t)(s8 * 128), dS + (uint64_t)(s8 * 2 * NCP), idesc64, s8 > 0);
       wait(fullQK, ph);
 #pragma unroll
-      for (int k0 = 0; k0 < 64; k0 += 8)
-        umma::mma_tf32_ss(tm + NC, umma::desc_kmajor(QKsm, 64, k0), umma::desc_kmajor_padded(Usm, NCP, k0), idesc64, 1u);
+      for (int s8 = 0; s8 < 8; ++s8) umma::mma_tf32_ss(tm + NC, dQK + (uint64_t)(s8 * 128), dU + (uint64_t)(s8 * 2 * NCP), idesc64, 1u);
       umma::commit(d3);
     }
     if (c + 1 < nch) fetch_rows(c + 1);                    // global loads fly while the tensor core works
+    PROF(4);
     wait(d2, ph);
     umma::fence_after_sync();
+    PROF(5);
     if (t == 0 && c + 1 < nch) load_k(c + 1);
-    {   // S <- e^{G_end} S + K^T U'; D1b (which read S^T) completed before D2
+    {   // S <- e^{G_end} S + K^T U' (registers; the transposed copy is rewritten after d3)
       const float eend = __expf(ge);
 #pragma unroll
       for (int j0 = 0; j0 < NC; j0 += 32) {
@@ -166,13 +176,16 @@ __global__ void __launch_bounds__(128) gdn_chunk_scan_tc_kernel(GdnPrefillParams
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
           S[j0 + j] = fmaf(eend, S[j0 + j], p[j]);
-          Ssm[((t >> 2) * NCP + j0 + j) * 4 + (t & 3)] = tf32r(S[j0 + j]);
         }
       }
     }
+    PROF(6);
     wait(d3, ph);
     umma::fence_after_sync();
+    PROF(7);
     if (t == 0 && c + 1 < nch) { load_q(c + 1); load_qk(c + 1); }
+#pragma unroll
+    for (int j = 0; j < NC; ++j) Ssm[((t >> 2) * NCP + j) * 4 + (t & 3)] = tf32r(S[j]);   // Qt S^T has completed
     {   // Y = e^G (Q S) + QKd U
       const int row = c * kChunk + tk;
 #pragma unroll
@@ -186,10 +199,12 @@ __global__ void __launch_bounds__(128) gdn_chunk_scan_tc_kernel(GdnPrefillParams
         }
       }
     }
+    PROF(8);
     umma::fence_async_smem();
     umma::fence_before_sync();
     __syncthreads();
     umma::fence_after_sync();
+    PROF(9);
   }
 #pragma unroll
   for (int j = 0; j < NC; j += 4) *reinterpret_cast<float4*>(st + j) = make_float4(S[j], S[j + 1], S[j + 2], S[j + 3]);
@@ -209,6 +224,7 @@ cr_status gdn_chunk_scan_tc_launch(const cr_geometry* g, const GdnPrefillParams&
   return CR_OK;
 }
 
+extern "C" void cr_debug_prof(long long* out) { cudaMemcpyFromSymbol(out, g_prof, sizeof(long long) * 16); long long z[16] = {0}; cudaMemcpyToSymbol(g_prof, z, sizeof(z)); }
 int gdn_scan_status_read() {
   int v = 0;
   cudaMemcpyFromSymbol(&v, g_gdn_scan_status, sizeof(int));

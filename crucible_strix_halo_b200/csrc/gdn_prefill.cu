@@ -40,7 +40,7 @@ __global__ void __launch_bounds__(256) gdn_prep_kernel(GdnPrefillParams P) {
   const int ch = is_qk ? (t < 128 ? u * 128 + t : KW + u * 128 + (t - 128)) : 2 * KW + (u - P.Hk) * 256 + t;
   const float4 wv = *reinterpret_cast<const float4*>(a.conv + (size_t)ch * 4);
   auto raw = [&](int r) -> float {   // raw projection value of this channel at call row r (may be negative)
-    if (r >= 0) return load_in<BF16>(a.qkv, (size_t)r * C + ch);
+    if (r >= 0 || P.halo_in) return load_in<BF16>(a.qkv, (long long)r * C + ch);
     const int p = a.pos0 + r;
     return p < 0 ? 0.f : a.hist[(size_t)(p & 15) * C + ch];
   };
@@ -228,7 +228,7 @@ size_t gdn_workspace_layout(const cr_geometry* g, int rows, GdnPrefillParams* P,
 
 extern "C" size_t cr_gdn_prefill_workspace_bytes(const cr_geometry* g, int rows) {
   if (!g || rows < 1) return 0;
-  return cr::gdn_workspace_layout(g, rows, nullptr, nullptr);
+  return cr::gdn_workspace_layout(g, rows < cr::kGdnPartRows ? rows : cr::kGdnPartRows, nullptr, nullptr);
 }
 
 extern "C" int cr_gdn_algo_available(cr_gdn_algo algo) {
@@ -252,30 +252,46 @@ extern "C" cr_status cr_gdn_prefill(const cr_geometry* g, const cr_gdn_prefill_a
   CR_REQUIRE(fmt != CR_OUT_EXL3_WHT || a.suh_out, "cr_gdn_prefill: suh_out needed for the EXL3 output");
   CR_REQUIRE(fmt == CR_OUT_EXL3_WHT || a.pack_rows == 0, "cr_gdn_prefill: packed layout only with the EXL3 output");
   CR_REQUIRE(algo == CR_GDN_SERIAL_F32 || algo == CR_GDN_CHUNK_TC || algo == CR_GDN_CHUNK_MMA, "cr_gdn_prefill: unknown algorithm");
-  const size_t need = gdn_workspace_layout(g, a.R, nullptr, nullptr);
+  const int part_rows = a.R < kGdnPartRows ? a.R : kGdnPartRows;
+  const size_t need = gdn_workspace_layout(g, part_rows, nullptr, nullptr);
   CR_REQUIRE(args->workspace && args->workspace_bytes >= need, "cr_gdn_prefill: workspace of %zu bytes needed, %zu given",
              need, args->workspace_bytes);
   CR_REQUIRE(((uintptr_t)args->workspace & 255) == 0, "cr_gdn_prefill: workspace must be 256-byte aligned");
 
-  GdnPrefillParams P;
-  P.a = a; P.ab_logits = args->ab_logits;
-  P.Hv = g->gdn_vheads; P.Hk = g->gdn_kheads; P.fmt = (int)fmt;
-  P.tf32 = 0;
-  gdn_workspace_layout(g, a.R, &P, (char*)args->workspace);
-  if (args->raw_y) P.yraw = args->raw_y;
   const bool bf = args->in_dtype == CR_IN_BF16;
-  if (algo == CR_GDN_SERIAL_F32) {
-    const dim3 pg((a.R + 15) / 16, g->gdn_kheads + g->gdn_vheads / 2 + 1);
-    if (bf) gdn_prep_kernel<true><<<pg, 256, 0, stream>>>(P); else gdn_prep_kernel<false><<<pg, 256, 0, stream>>>(P);
-    CR_LAUNCH_CHECK("gdn_prep_kernel");
-    gdn_scan_serial_kernel<<<g->gdn_vheads * 4, 256, 0, stream>>>(P);
-    CR_LAUNCH_CHECK("gdn_scan_serial_kernel");
-  } else {   // the chunked scan prepares its rows itself
-    if (cr_status s = gdn_chunk_scan(g, P, bf, algo == CR_GDN_CHUNK_TC, stream)) return s;
+  const size_t in_elt = bf ? 2 : 4, out_elt = fmt == CR_OUT_RAW_F32 ? 4 : 2;
+  const size_t Cw = 2 * (size_t)g->gdn_kheads * 128 + (size_t)g->gdn_vheads * 128, VWs = (size_t)g->gdn_vheads * 128;
+  GdnPrefillParams P;
+  // The call runs in parts of kGdnPartRows rows that reuse one workspace, so the intermediates of a part stay
+  // in L2 between the kernels that write and read them; the state carries from part to part.
+  for (int p0 = 0; p0 < a.R; p0 += kGdnPartRows) {
+    P.a = a;
+    P.a.qkv = (const char*)a.qkv + (size_t)p0 * Cw * in_elt;
+    P.a.z = (const char*)a.z + (size_t)p0 * VWs * in_elt;
+    if (a.pack_rows) P.a.pack_off = a.pack_off + p0; else P.a.out = (char*)a.out + (size_t)p0 * VWs * out_elt;
+    P.a.pos0 = a.pos0 + p0;
+    P.a.R = a.R - p0 < kGdnPartRows ? a.R - p0 : kGdnPartRows;
+    P.a.commit = P.a.R;
+    P.ab_logits = (const char*)args->ab_logits + (size_t)p0 * 2 * g->gdn_vheads * in_elt;
+    P.Hv = g->gdn_vheads; P.Hk = g->gdn_kheads; P.fmt = (int)fmt;
+    P.tf32 = 0;
+    P.halo_in = p0 > 0;
+    gdn_workspace_layout(g, part_rows, &P, (char*)args->workspace);
+    if (args->raw_y) P.yraw = args->raw_y + (size_t)p0 * VWs;
+    if (algo == CR_GDN_SERIAL_F32) {
+      const dim3 pg((P.a.R + 15) / 16, g->gdn_kheads + g->gdn_vheads / 2 + 1);
+      if (bf) gdn_prep_kernel<true><<<pg, 256, 0, stream>>>(P); else gdn_prep_kernel<false><<<pg, 256, 0, stream>>>(P);
+      CR_LAUNCH_CHECK("gdn_prep_kernel");
+      gdn_scan_serial_kernel<<<g->gdn_vheads * 4, 256, 0, stream>>>(P);
+      CR_LAUNCH_CHECK("gdn_scan_serial_kernel");
+    } else {   // the chunked scan prepares its rows itself
+      if (cr_status s = gdn_chunk_scan(g, P, bf, algo == CR_GDN_CHUNK_TC, stream)) return s;
+    }
+    const unsigned gg = (unsigned)(((long long)P.a.R * g->gdn_vheads + 7) / 8);
+    if (bf) gdn_gate_kernel<true><<<gg, 256, 0, stream>>>(P); else gdn_gate_kernel<false><<<gg, 256, 0, stream>>>(P);
+    CR_LAUNCH_CHECK("gdn_gate_kernel");
   }
-  const unsigned gg = (unsigned)(((long long)a.R * g->gdn_vheads + 7) / 8);
-  if (bf) gdn_gate_kernel<true><<<gg, 256, 0, stream>>>(P); else gdn_gate_kernel<false><<<gg, 256, 0, stream>>>(P);
-  CR_LAUNCH_CHECK("gdn_gate_kernel");
+  P.a = a;
   const int C = 2 * g->gdn_kheads * 128 + g->gdn_vheads * 128;
   const unsigned rg = (unsigned)(((long long)(a.R < 16 ? a.R : 16) * C + 255) / 256);
   if (bf) gdn_ring_kernel<true><<<rg, 256, 0, stream>>>(P); else gdn_ring_kernel<false><<<rg, 256, 0, stream>>>(P);

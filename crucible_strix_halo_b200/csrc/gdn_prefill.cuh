@@ -4,6 +4,8 @@
 
 namespace cr {
 
+constexpr int kGdnPartRows = 2048;   // rows per internal part (kPrefillCoreRows, engine/runtime/prefill_rows.h:7)
+
 struct GdnPrefillParams {
   cr_gdn_args a;
   const void* ab_logits;   // [R][2Hv]
@@ -13,6 +15,7 @@ struct GdnPrefillParams {
   float* yraw;             // [R][Hv][128] un-gated readout
   char* chunk_ws;          // workspace of the chunked scan
   int Hv, Hk, fmt;
+  int halo_in;             // 1: rows before this part's first row are read from the input (a later part of one call)
   int tf32;                // 1: prep rounds q/k to tf32 (operands of the tensor-core scan)
 };
 
