@@ -15,7 +15,7 @@ namespace cr {
 
 constexpr int kRawRows = 67;                               // 64 rows + 3 halo rows
 constexpr int kStageBytes = kRawRows * 128 * 2;            // one 128-channel bf16 tile (or 64 fp32 channels)
-constexpr size_t kLocalSmem = (size_t)(2 * 64 * kLdK + 64 * kLdM + 9 * 64 + 64 * 4) * sizeof(float) + kStageBytes + 256;
+constexpr size_t kLocalSmem = (size_t)(64 * kLdK + 64 * kLdX + 64 * kLdM + 9 * 64 + 64 * 4 + 3 * 256) * sizeof(float) + kStageBytes + 256;
 
 // Stages rows row0-3 .. row0+63 of channels [ch0, ch0+CH) into dst[67][CH] (element type of the input).
 // Rows before the call come from the input itself (halo_in: a later part of one call), the ring, or zero.
@@ -56,23 +56,59 @@ __device__ __forceinline__ float staged_one(const void* buf, int CH, int rr, int
   else return reinterpret_cast<const float*>(buf)[rr * CH + ch];
 }
 
-// out[i] = x(i) - sum_{m<i} L[i][m] out[m] for i < 64: the thread's column of (I + L)^-1 X, exact fp32.
-template <typename FX, typename FO>
-__device__ __forceinline__ void solve_column(const float* LT, FX&& x, FO&& emit) {
-  float out[64];
+// T = (I + L)^-1 for the 64x64 unit lower-triangular I + L held in LT, exact fp32, in place, by 16x16 blocks:
+// diagonal blocks by forward substitution (one thread per column, column in registers), then block row by block
+// row, T_ab = -T_aa (sum_{c=b}^{a-1} L_ac T_cb): every phase is a product of 16-long unrolled dot products with
+// all 256 threads busy (thread = element (t/16, t%16) of each block of the row).
+__device__ __forceinline__ void invert_unit_lower_64(float* LT, float* Ms) {
+  const int t = threadIdx.x, i = t >> 4, j = t & 15;
+  float D[16];
+  if (t < 64) {
+    const int b = t >> 4;
 #pragma unroll
-  for (int i = 0; i < 64; ++i) {
-    float a0 = x(i), a1 = 0.f, a2 = 0.f, a3 = 0.f;
+    for (int r = 0; r < 16; ++r) {
+      float acc = (r == j) ? 1.f : 0.f;
 #pragma unroll
-    for (int m4 = 0; m4 < (i + 3) / 4; ++m4) {
-      const float4 lv = *reinterpret_cast<const float4*>(&LT[i * kLdM + m4 * 4]);
-      a0 = fmaf(-lv.x, out[m4 * 4], a0);
-      if (m4 * 4 + 1 < i) a1 = fmaf(-lv.y, out[m4 * 4 + 1], a1);
-      if (m4 * 4 + 2 < i) a2 = fmaf(-lv.z, out[m4 * 4 + 2], a2);
-      if (m4 * 4 + 3 < i) a3 = fmaf(-lv.w, out[m4 * 4 + 3], a3);
+      for (int m = 0; m < r; ++m) acc = fmaf(-LT[(16 * b + r) * kLdM + 16 * b + m], D[m], acc);
+      D[r] = acc;
     }
-    out[i] = (a0 + a1) + (a2 + a3);
-    emit(i, out[i]);
+  }
+  __syncthreads();
+  if (t < 64) {
+    const int b = t >> 4;
+#pragma unroll
+    for (int r = 0; r < 16; ++r) LT[(16 * b + r) * kLdM + 16 * b + j] = D[r];
+  }
+  __syncthreads();
+  for (int a = 1; a < 4; ++a) {          // block row a: its L blocks are still untouched
+    for (int b = 0; b < a; ++b) {        // M_ab = sum_{c=b}^{a-1} L_ac T_cb
+      float m0 = 0.f, m1 = 0.f, m2 = 0.f, m3 = 0.f;
+      for (int cb = b; cb < a; ++cb) {
+        const float* Lr = LT + (16 * a + i) * kLdM + 16 * cb;
+        const float* Tc = LT + (16 * cb) * kLdM + 16 * b + j;
+#pragma unroll
+        for (int m = 0; m < 16; m += 4) {
+          m0 = fmaf(Lr[m], Tc[m * kLdM], m0);
+          m1 = fmaf(Lr[m + 1], Tc[(m + 1) * kLdM], m1);
+          m2 = fmaf(Lr[m + 2], Tc[(m + 2) * kLdM], m2);
+          m3 = fmaf(Lr[m + 3], Tc[(m + 3) * kLdM], m3);
+        }
+      }
+      Ms[b * 256 + t] = (m0 + m1) + (m2 + m3);
+    }
+    __syncthreads();
+    for (int b = 0; b < a; ++b) {        // T_ab = -T_aa M_ab  (T_aa lower triangular: m <= i)
+      const float* Tr = LT + (16 * a + i) * kLdM + 16 * a;
+      const float* Mc = Ms + b * 256 + j;
+      float m0 = 0.f, m1 = 0.f;
+#pragma unroll
+      for (int m = 0; m < 16; m += 2) {
+        m0 = fmaf(m <= i ? Tr[m] : 0.f, Mc[m * 16], m0);
+        m1 = fmaf(m + 1 <= i ? Tr[m + 1] : 0.f, Mc[(m + 1) * 16], m1);
+      }
+      LT[(16 * a + i) * kLdM + 16 * b + j] = -(m0 + m1);
+    }
+    __syncthreads();
   }
 }
 
@@ -82,13 +118,14 @@ template <bool BF16, bool UM>
 __global__ void __launch_bounds__(256, 2) gdn_chunk_local_kernel(GdnPrefillParams P, ChunkWs ws) {
   extern __shared__ __align__(16) float sm[];
   float* Ks = sm;                       // [64][132] khat (tf32)
-  float* Qs = Ks + 64 * kLdK;           // [64][132] qhat (tf32); with fp32 inputs later the head of the v staging tile
-  char* RB = reinterpret_cast<char*>(Qs + 64 * kLdK);      // raw staging tile (directly after Qs)
+  float* Qs = Ks + 64 * kLdK;           // [64][132] qhat (tf32), later [64][136] X = beta e^G K / beta V
+  char* RB = reinterpret_cast<char*>(Qs + 64 * kLdX);      // raw staging tile
   float* LT = reinterpret_cast<float*>(RB + kStageBytes);  // [64][68] L
   float* Gs = LT + 64 * kLdM;           // [3][64] cumulative log decay per value head
   float* bs = Gs + 3 * 64;              // [3][64] beta
   float* es = bs + 3 * 64;              // [3][64] beta * exp(G)
   float* red = es + 3 * 64;             // [64][4] partial sums of squares: q halves, k halves
+  float* Ms = red + 64 * 4;             // [3][256] scratch of the blocked inverse
   const cr_gdn_args& a = P.a;
   const int c = blockIdx.x, kh = blockIdx.y;
   const int t = threadIdx.x, w = t >> 5, l = t & 31, g = l >> 2, tq = l & 3;
@@ -219,28 +256,77 @@ __global__ void __launch_bounds__(256, 2) gdn_chunk_local_kernel(GdnPrefillParam
           }
         }
     }
-    // raw v rows of value head h: 128 channels (with fp32 inputs the tile spills into the freed qhat buffer)
-    void* vbuf = BF16 ? (void*)RB : (void*)Qs;
-    stage_raw<BF16, 128>(P, C, r0, 2 * KW + h * 128, vbuf);
+    for (int i = t; i < 64 * 32; i += 256) {   // X = beta e^G K
+      const int row = i >> 5, c4 = (i & 31) * 4;
+      const float4 kv = *reinterpret_cast<const float4*>(Ks + row * kLdK + c4);
+      const float e = ev[row];
+      *reinterpret_cast<float4*>(Qs + row * kLdX + c4) = make_float4(tf32r(e * kv.x), tf32r(e * kv.y), tf32r(e * kv.z), tf32r(e * kv.w));
+    }
+    // raw v rows of value head h, 128 channels per round with bf16 inputs, 64 with fp32 inputs
+    constexpr int VCH = BF16 ? 128 : 64;
+    stage_raw<BF16, VCH>(P, C, r0, 2 * KW + h * 128, RB);
     __syncthreads();
-    if (t < 128) {   // W column (key t): X = beta e^G K
-      float* Wg = ws.W + unit * 8192;
-      solve_column(LT, [&](int i) { return ev[i] * Ks[i * kLdK + t]; },
-                   [&](int i, float v) { Wg[UM ? ((t >> 2) * 64 + i) * 4 + (t & 3) : i * 128 + t] = tf32r(v); });
-    } else {         // Ut column (value channel t - 128): X = beta SiLU(conv(v)), conv fused into the recurrence
-      const int d = t - 128;
-      const float4 wv = *reinterpret_cast<const float4*>(a.conv + (size_t)(2 * KW + h * 128 + d) * 4);
-      float x0 = staged_one<BF16>(vbuf, 128, 0, d), x1 = staged_one<BF16>(vbuf, 128, 1, d), x2 = staged_one<BF16>(vbuf, 128, 2, d);
-      float* Ug = ws.Ut + unit * 8192 + d;
-      solve_column(LT,
-                   [&](int i) {
-                     const float x3 = staged_one<BF16>(vbuf, 128, i + 3, d);
-                     float cv = wv.x * x0;
-                     cv = fmaf(wv.y, x1, cv); cv = fmaf(wv.z, x2, cv); cv = fmaf(wv.w, x3, cv);
-                     x0 = x1; x1 = x2; x2 = x3;
-                     return i < valid ? bv[i] * siluf_(cv) : 0.f;
-                   },
-                   [&](int i, float v) { Ug[i * 128] = v; });
+    invert_unit_lower_64(LT, Ms);
+    for (int i = t; i < 64 * 64; i += 256) {
+      float* p = LT + (i >> 6) * kLdM + (i & 63);
+      *p = tf32r(*p);
+    }
+    __syncthreads();
+    const int nh = w >> 2;
+    {   // W = T X
+      float acc[8][4];
+#pragma unroll
+      for (int n = 0; n < 8; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+      warp_gemm<8, 8, false, false>(acc, LT + mt * 16 * kLdM, kLdM, Qs + nh * 64, kLdX);
+      float* dst = ws.W + unit * 8192;
+#pragma unroll
+      for (int n = 0; n < 8; ++n) {
+        const int col = nh * 64 + n * 8 + 2 * tq, r_lo = mt * 16 + g;
+        if constexpr (UM) {
+          *reinterpret_cast<float2*>(dst + ((col >> 2) * 64 + r_lo) * 4 + (col & 3)) = make_float2(tf32r(acc[n][0]), tf32r(acc[n][1]));
+          *reinterpret_cast<float2*>(dst + ((col >> 2) * 64 + r_lo + 8) * 4 + (col & 3)) = make_float2(tf32r(acc[n][2]), tf32r(acc[n][3]));
+        } else {
+          *reinterpret_cast<float2*>(dst + r_lo * 128 + col) = make_float2(tf32r(acc[n][0]), tf32r(acc[n][1]));
+          *reinterpret_cast<float2*>(dst + (r_lo + 8) * 128 + col) = make_float2(tf32r(acc[n][2]), tf32r(acc[n][3]));
+        }
+      }
+    }
+    __syncthreads();                    // X = beta e^G K consumed
+    for (int round = 0; round < 128 / VCH; ++round) {   // X = beta SiLU(conv(v)) from the staged raw rows
+      if (round) {
+        __syncthreads();
+        stage_raw<BF16, VCH>(P, C, r0, 2 * KW + h * 128 + round * VCH, RB);
+        __syncthreads();
+      }
+      constexpr int VP = VCH / 2, VSEG = 256 / VP, VR = 64 / VSEG;
+      const int cp = t % VP, seg = t / VP, chl = 2 * cp, chg = 2 * KW + h * 128 + round * VCH + chl, rb = seg * VR;
+      const float4 w0 = *reinterpret_cast<const float4*>(a.conv + (size_t)chg * 4);
+      const float4 w1 = *reinterpret_cast<const float4*>(a.conv + (size_t)(chg + 1) * 4);
+      float2 x0 = staged_pair<BF16>(RB, VCH, rb, chl), x1 = staged_pair<BF16>(RB, VCH, rb + 1, chl), x2 = staged_pair<BF16>(RB, VCH, rb + 2, chl);
+#pragma unroll
+      for (int i = 0; i < VR; ++i) {
+        const float2 x3 = staged_pair<BF16>(RB, VCH, rb + 3 + i, chl);
+        float c0 = w0.x * x0.x, c1 = w1.x * x0.y;
+        c0 = fmaf(w0.y, x1.x, c0); c1 = fmaf(w1.y, x1.y, c1);
+        c0 = fmaf(w0.z, x2.x, c0); c1 = fmaf(w1.z, x2.y, c1);
+        c0 = fmaf(w0.w, x3.x, c0); c1 = fmaf(w1.w, x3.y, c1);
+        const float b = rb + i < valid ? bv[rb + i] : 0.f;
+        *reinterpret_cast<float2*>(Qs + (rb + i) * kLdX + round * VCH + chl) = make_float2(tf32r(b * siluf_(c0)), tf32r(b * siluf_(c1)));
+        x0 = x1; x1 = x2; x2 = x3;
+      }
+    }
+    __syncthreads();
+    {   // Ut = T X  (stored fp32: it is added, not multiplied, in the scan)
+      float acc[8][4];
+#pragma unroll
+      for (int n = 0; n < 8; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+      warp_gemm<8, 8, false, false>(acc, LT + mt * 16 * kLdM, kLdM, Qs + nh * 64, kLdX);
+      float* dst = ws.Ut + (unit * 64 + mt * 16) * 128 + nh * 64;
+#pragma unroll
+      for (int n = 0; n < 8; ++n) {
+        *reinterpret_cast<float2*>(dst + g * 128 + n * 8 + 2 * tq) = make_float2(acc[n][0], acc[n][1]);
+        *reinterpret_cast<float2*>(dst + (g + 8) * 128 + n * 8 + 2 * tq) = make_float2(acc[n][2], acc[n][3]);
+      }
     }
   }
 }

@@ -4,7 +4,9 @@
 
 namespace cr {
 
-constexpr int kGdnPartRows = 2048;   // rows per internal part (kPrefillCoreRows, engine/runtime/prefill_rows.h:7)
+// Rows per internal part: 37 chunks x 16 key heads = 592 local CTAs = two full waves of 2 CTAs on 148 SMs, and the
+// part's intermediates (about 65 KB per row) stay within the 126 MB L2.
+constexpr int kGdnPartRows = 37 * 64;
 
 struct GdnPrefillParams {
   cr_gdn_args a;
