@@ -92,7 +92,7 @@ _protos = {
     "cr_qsa_merge_candidates": (C.c_int, [G, C.POINTER(QsaArgs), C.c_int, P, P, P]),
     "cr_qsa_shard_attn": (C.c_int, [G, C.POINTER(QsaArgs), C.c_int, C.c_int, P, P, C.c_size_t, P]),
     "cr_qsa_merge_partials": (C.c_int, [G, C.POINTER(QsaArgs), C.c_int, P, C.c_int, P]),
-    "cr_debug_umma_gemm": (C.c_int, [P, P, P, C.c_int, C.c_int, C.c_int, C.c_int, P, P]),
+    "cr_debug_umma_gemm": (C.c_int, [P, P, P, C.c_int, C.c_int, P, P]),
     "cr_last_error": (C.c_char_p, []),
     "cr_version": (C.c_int, []),
     "cr_device_status": (C.c_int, []),

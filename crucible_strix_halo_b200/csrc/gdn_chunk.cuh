@@ -24,7 +24,8 @@ struct ChunkWs {
   float* Ut;   // [Hv][chunks][64][128]  fp32
   float* QKd;  // [Hv][chunks][64][64]   tf32
   float* G;    // [Hv][chunks][64]       cumulative log decay inside the chunk
-  float* Qt;   // [Hv][chunks][32][64][4]  e^G Q as a K-major tile (tcgen05 scan only)
+  float* WQ;   // [Hv][chunks][32][128][4] rows 0-63 W, rows 64-127 e^G Q, one K-major tile (tcgen05 scan only)
+  float* QKp;  // [Hv][chunks][16][128][4] rows 0-63 zero, rows 64-127 QKd, K-major tile (tcgen05 scan only)
   float* Kt;   // [Hk][chunks][16][128][4] K^T as a K-major tile (tcgen05 scan only)
   int chunks;
 };

@@ -215,12 +215,12 @@ __global__ void __launch_bounds__(256, 2) gdn_chunk_local_kernel(GdnPrefillParam
     }
     // Qt = e^G Q per value head, K-major over keys
     for (int vi = 0; vi < rep; ++vi) {
-      float* qt = ws.Qt + ((size_t)(kh * rep + vi) * ws.chunks + c) * 8192;
+      float* qt = ws.WQ + ((size_t)(kh * rep + vi) * ws.chunks + c) * 16384;
       for (int i = t; i < 32 * 64; i += 256) {
         const int row = i & 63, kc = i >> 6;
         const float4 q = *reinterpret_cast<const float4*>(Qs + row * kLdK + kc * 4);
         const float e = __expf(Gs[vi * 64 + row]);
-        *reinterpret_cast<float4*>(qt + (size_t)i * 4) = make_float4(tf32r(e * q.x), tf32r(e * q.y), tf32r(e * q.z), tf32r(e * q.w));
+        *reinterpret_cast<float4*>(qt + (size_t)(kc * 128 + 64 + row) * 4) = make_float4(tf32r(e * q.x), tf32r(e * q.y), tf32r(e * q.z), tf32r(e * q.w));
       }
     }
   }
@@ -238,7 +238,10 @@ __global__ void __launch_bounds__(256, 2) gdn_chunk_local_kernel(GdnPrefillParam
     const float* Gv = Gs + vi * 64; const float* bv = bs + vi * 64; const float* ev = es + vi * 64;
     __syncthreads();                    // previous head done with LT and the staging tile; qhat no longer needed
     {   // L (warps 0-3) and QKd (warps 4-7) straight from the Gram fragments
-      float* qkd = ws.QKd + unit * 64 * 64;
+      float* qkd = UM ? ws.QKp + unit * 8192 : ws.QKd + unit * 64 * 64;
+      if constexpr (UM) {   // rows 0-63 of the padded tile are zero (they meet the W rows of the accumulator)
+        for (int i = t; i < 16 * 64; i += 256) *reinterpret_cast<float4*>(qkd + (size_t)((i >> 6) * 128 + (i & 63)) * 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
 #pragma unroll
       for (int n = 0; n < 8; ++n)
 #pragma unroll
@@ -251,7 +254,7 @@ __global__ void __launch_bounds__(256, 2) gdn_chunk_local_kernel(GdnPrefillParam
             const float b = bv[row];
             *reinterpret_cast<float2*>(LT + row * kLdM + col) = make_float2(col < row ? b * v0 * p0 : 0.f, col + 1 < row ? b * v1 * p1 : 0.f);
           } else {
-            const int at = UM ? ((col >> 2) * 64 + row) * 4 + (col & 3) : row * 64 + col;
+            const int at = UM ? ((col >> 2) * 128 + 64 + row) * 4 + (col & 3) : row * 64 + col;
             *reinterpret_cast<float2*>(qkd + at) = make_float2(col <= row ? tf32r(v0 * p0) : 0.f, col + 1 <= row ? tf32r(v1 * p1) : 0.f);
           }
         }
@@ -278,13 +281,13 @@ __global__ void __launch_bounds__(256, 2) gdn_chunk_local_kernel(GdnPrefillParam
 #pragma unroll
       for (int n = 0; n < 8; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
       warp_gemm<8, 8, false, false>(acc, LT + mt * 16 * kLdM, kLdM, Qs + nh * 64, kLdX);
-      float* dst = ws.W + unit * 8192;
+      float* dst = UM ? ws.WQ + unit * 16384 : ws.W + unit * 8192;
 #pragma unroll
       for (int n = 0; n < 8; ++n) {
         const int col = nh * 64 + n * 8 + 2 * tq, r_lo = mt * 16 + g;
         if constexpr (UM) {
-          *reinterpret_cast<float2*>(dst + ((col >> 2) * 64 + r_lo) * 4 + (col & 3)) = make_float2(tf32r(acc[n][0]), tf32r(acc[n][1]));
-          *reinterpret_cast<float2*>(dst + ((col >> 2) * 64 + r_lo + 8) * 4 + (col & 3)) = make_float2(tf32r(acc[n][2]), tf32r(acc[n][3]));
+          *reinterpret_cast<float2*>(dst + ((col >> 2) * 128 + r_lo) * 4 + (col & 3)) = make_float2(tf32r(acc[n][0]), tf32r(acc[n][1]));
+          *reinterpret_cast<float2*>(dst + ((col >> 2) * 128 + r_lo + 8) * 4 + (col & 3)) = make_float2(tf32r(acc[n][2]), tf32r(acc[n][3]));
         } else {
           *reinterpret_cast<float2*>(dst + r_lo * 128 + col) = make_float2(tf32r(acc[n][0]), tf32r(acc[n][1]));
           *reinterpret_cast<float2*>(dst + (r_lo + 8) * 128 + col) = make_float2(tf32r(acc[n][2]), tf32r(acc[n][3]));

@@ -1,11 +1,14 @@
 // tcgen05 (5th-generation tensor core) primitives for sm_100a: TMEM allocation, shared-memory matrix
 // descriptors, instruction descriptors, MMA issue, commit to an mbarrier, bounded waits and TMEM loads.
 //
-// Operand layouts used here are the un-swizzled canonical ones, which are plain arrays for 32-bit elements:
-//   K-major  operand X[rows][K]  is stored as  float[K/4][rows][4]     (16-byte units: K chunk, then row)
-//   MN-major operand X[K][mn]    is stored as  float[mn/4][K][4]       (16-byte units: mn group, then k)
-// A core matrix is 8 consecutive 16-byte units (128 contiguous bytes) in both cases, so shared-memory writes
-// by consecutive lanes are conflict-free and no swizzle pattern has to be reproduced by hand.
+// Operands use the un-swizzled canonical K-major layout, which is a plain array for 32-bit elements:
+//   operand X[rows][K]  is stored as  float[K/4][rows][4]     (16-byte units: K chunk, then row)
+// A core matrix is 8 consecutive 16-byte units (128 contiguous bytes), so shared-memory writes by consecutive
+// lanes are conflict-free and no swizzle pattern has to be reproduced by hand.  Every operand is kept K-major:
+// with kind::tf32 the MN-major (transposed) operand form returned zeros on B200 in this build's tests, so
+// kernels transpose when they write an operand instead.  One tcgen05.mma of K = 8 costs about 46 cycles
+// whatever the tile (the 128 x 8 A tile alone is 4 KB of shared-memory reads), so N should be as wide as the
+// algorithm allows.
 #pragma once
 #include <cstdint>
 #include <cuda_runtime.h>
@@ -53,8 +56,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32
 
 // ---- descriptors -------------------------------------------------------------------------------------
 // Shared-memory matrix descriptor, no swizzle (layout type 0), descriptor version 1 (Blackwell).
-// lbo / sbo in bytes: K-major: lbo = distance between the 16-byte K chunks, sbo = between 8-row groups;
-// MN-major: sbo = distance between the 16-byte mn groups, lbo = between groups of 8 k rows.
+// lbo / sbo in bytes (K-major): lbo = distance between the 16-byte K chunks, sbo = between 8-row groups.
 __device__ __forceinline__ uint64_t smem_desc(const void* base, uint32_t lbo, uint32_t sbo) {
   uint64_t d = 0;
   d |= (uint64_t)((smem_u32(base) & 0x3FFFF) >> 4);
@@ -66,10 +68,6 @@ __device__ __forceinline__ uint64_t smem_desc(const void* base, uint32_t lbo, ui
 // K-major operand stored float[K/4][rows][4]; k0 = first K element of this MMA (multiple of 8).
 __device__ __forceinline__ uint64_t desc_kmajor(const float* base, int rows, int k0) {
   return smem_desc(base + (size_t)(k0 / 4) * rows * 4, (uint32_t)rows * 16u, 128u);
-}
-// MN-major operand stored float[mn/4][K][4] with K rows in total; k0 as above.
-__device__ __forceinline__ uint64_t desc_mnmajor(const float* base, int K, int k0) {
-  return smem_desc(base + (size_t)k0 * 4, 128u, (uint32_t)K * 16u);
 }
 // Instruction descriptor for kind::tf32, fp32 accumulation.
 __host__ __device__ constexpr uint32_t idesc_tf32(int M, int N, bool a_mn, bool b_mn) {

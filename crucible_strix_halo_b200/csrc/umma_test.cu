@@ -1,42 +1,29 @@
-// Self-check of the tcgen05 primitives in umma.cuh: D[128][N] = A B with tf32 operands, every combination of
-// K-major / MN-major operands, one CTA.  Exposed as cr_debug_umma_gemm so the GPU tests can pin the
-// descriptor conventions the production kernels rely on.
+// Self-check of the tcgen05 primitives in umma.cuh: D[128][N] = A B^T with tf32 operands on one CTA, both
+// operands K-major.  Exposed as cr_debug_umma_gemm so the GPU tests pin the descriptor conventions the
+// production kernels rely on.  (For tf32 the MN-major operand form returns zeros on this hardware, so the
+// production kernels write every operand K-major and this check covers that form only.)
 #include "common.cuh"
 #include "umma.cuh"
 
 namespace cr {
 
-// A: [128][K] (a_mn = 0) or [K][128] (a_mn = 1).  B: [N][K] (b_mn = 0) or [K][N] (b_mn = 1).  D: [128][N].
-__global__ void __launch_bounds__(128) umma_test_kernel(const float* A, const float* B, float* D, int K, int N, int a_mn, int b_mn,
-                                                        int* status, int raw) {
+// A: [128][K], B: [N][K], D: [128][N].
+__global__ void __launch_bounds__(128) umma_test_kernel(const float* A, const float* B, float* D, int K, int N, int* status) {
   extern __shared__ __align__(128) float sm[];
   float* As = sm;
   float* Bs = sm + 128 * K;
   __shared__ __align__(8) uint64_t bar;
   __shared__ uint32_t tmem_slot;
   const int t = threadIdx.x, w = t >> 5;
-  auto stage = [&](float* dst, const float* src, int rows, bool mn) {
-    const int units = rows * K / 4;
-    for (int u = t; u < units; u += 128) {
-      float4 v;
-      int slot;
-      if (!mn) {            // src [rows][K] -> [K/4][rows][4]
-        const int r = u % rows, kc = u / rows;
-        v = *reinterpret_cast<const float4*>(src + (size_t)r * K + kc * 4);
-        slot = kc * rows + r;
-      } else {              // src [K][rows] -> [rows/4][K][4]
-        const int k = u % K, mg = u / K;
-        v = *reinterpret_cast<const float4*>(src + (size_t)k * rows + mg * 4);
-        slot = mg * K + k;
-      }
-      *reinterpret_cast<float4*>(dst + (size_t)slot * 4) = make_float4(tf32r(v.x), tf32r(v.y), tf32r(v.z), tf32r(v.w));
+  auto stage = [&](float* dst, const float* src, int rows) {   // src [rows][K] -> [K/4][rows][4]
+    for (int u = t; u < rows * K / 4; u += 128) {
+      const int r = u % rows, kc = u / rows;
+      const float4 v = *reinterpret_cast<const float4*>(src + (size_t)r * K + kc * 4);
+      *reinterpret_cast<float4*>(dst + (size_t)(kc * rows + r) * 4) = make_float4(tf32r(v.x), tf32r(v.y), tf32r(v.z), tf32r(v.w));
     }
   };
-  stage(As, A, 128, a_mn);
-  stage(Bs, B, N, b_mn);
-  // layout probes: the operand holds its own float index, so D shows which word the tensor core read
-  if (raw & 1) for (int i = t; i < 128 * K; i += 128) As[i] = (float)(i + 1);
-  if (raw & 2) for (int i = t; i < N * K; i += 128) Bs[i] = (float)(i + 1);
+  stage(As, A, 128);
+  stage(Bs, B, N);
   if (t == 0) { umma::mbar_init(&bar, 1); umma::mbar_fence_init(); }
   if (w == 0) umma::tmem_alloc(&tmem_slot, 128);
   umma::fence_async_smem();
@@ -45,26 +32,21 @@ __global__ void __launch_bounds__(128) umma_test_kernel(const float* A, const fl
   umma::fence_after_sync();
   const uint32_t tmem = tmem_slot;
   if (t == 0) {
-    const uint32_t idesc = umma::idesc_tf32(128, N, a_mn, b_mn);
-    for (int k0 = 0; k0 < K; k0 += 8) {
-      const uint64_t ad = a_mn ? umma::desc_mnmajor(As, K, k0) : umma::desc_kmajor(As, 128, k0);
-      const uint64_t bd = b_mn ? umma::desc_mnmajor(Bs, K, k0) : umma::desc_kmajor(Bs, N, k0);
-      umma::mma_tf32_ss(tmem, ad, bd, idesc, k0 > 0);
-    }
+    const uint32_t idesc = umma::idesc_tf32(128, N, false, false);
+    for (int k0 = 0; k0 < K; k0 += 8) umma::mma_tf32_ss(tmem, umma::desc_kmajor(As, 128, k0), umma::desc_kmajor(Bs, N, k0), idesc, k0 > 0);
     umma::commit(&bar);
   }
   const bool ok = umma::mbar_wait(&bar, 0);
   umma::fence_after_sync();
-  if (ok) {
-    for (int c0 = 0; c0 < N; c0 += 32) {
-      float v[32];
-      umma::tmem_ld32(umma::tmem_addr(tmem, w, c0), v);
+  for (int c0 = 0; c0 < N; c0 += 32) {
+    float v[32];
+    umma::tmem_ld32(umma::tmem_addr(tmem, w, c0), v);
+    if (ok) {
 #pragma unroll
       for (int i = 0; i < 32; ++i) D[(size_t)t * N + c0 + i] = v[i];
     }
-  } else if (t == 0) {
-    *status = 1;          // the wait gave up: report instead of hanging
   }
+  if (!ok && t == 0) *status = 1;          // the wait gave up: report instead of hanging
   umma::fence_before_sync();
   __syncthreads();
   if (w == 0) umma::tmem_dealloc(tmem, 128);
@@ -72,17 +54,14 @@ __global__ void __launch_bounds__(128) umma_test_kernel(const float* A, const fl
 
 }  // namespace cr
 
-extern "C" cr_status cr_debug_umma_gemm(const float* A, const float* B, float* D, int K, int N, int a_mn, int b_mn, int* status,
-                                        void* stream) {
-  const int raw = a_mn >> 4 | (b_mn >> 4) << 1;
-  a_mn &= 1; b_mn &= 1;
+extern "C" cr_status cr_debug_umma_gemm(const float* A, const float* B, float* D, int K, int N, int* status, void* stream) {
   using namespace cr;
   CR_REQUIRE(A && B && D && status, "cr_debug_umma_gemm: null buffer");
   CR_REQUIRE(K >= 8 && K % 8 == 0 && K <= 128 && N >= 32 && N % 32 == 0 && N <= 128, "cr_debug_umma_gemm: K in 8..128 step 8, N in 32..128 step 32");
   const size_t smem = (size_t)(128 + N) * K * sizeof(float);
   CR_CUDA(cudaFuncSetAttribute(umma_test_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   use_stream((cudaStream_t)stream);
-  umma_test_kernel<<<1, 128, smem, (cudaStream_t)stream>>>(A, B, D, K, N, a_mn, b_mn, status, raw);
+  umma_test_kernel<<<1, 128, smem, (cudaStream_t)stream>>>(A, B, D, K, N, status);
   CR_LAUNCH_CHECK("umma_test_kernel");
   return CR_OK;
 }

@@ -270,11 +270,10 @@ cr_status cr_profile_enable(int on);
 cr_status cr_profile_begin(void* stream);
 int cr_profile_collect(char* names, float* ms, int* calls, int max_stages);
 
-/* Self-check of the tensor-core (tcgen05) building blocks: D[128][N] = A B in tf32 on one CTA.
- * A is [128][K] (a_mn = 0) or [K][128] (a_mn = 1); B is [N][K] (b_mn = 0) or [K][N] (b_mn = 1).
- * *status (device int) becomes 1 if the bounded wait on the MMA gave up.  No counterpart in the reference. */
-cr_status cr_debug_umma_gemm(const float* A, const float* B, float* D, int K, int N, int a_mn, int b_mn, int* status,
-                             void* stream);
+/* Self-check of the tensor-core (tcgen05) building blocks: D[128][N] = A B^T in tf32 on one CTA, A [128][K] and
+ * B [N][K] both K-major.  *status (device int) becomes 1 if the bounded wait on the MMA gave up.
+ * No counterpart in the reference. */
+cr_status cr_debug_umma_gemm(const float* A, const float* B, float* D, int K, int N, int* status, void* stream);
 
 #ifdef __cplusplus
 }

@@ -1,24 +1,20 @@
-"""tcgen05 building blocks: a 128 x N x K tf32 product on tensor memory equals torch, for K-major and MN-major
-operands.  This pins the shared-memory / instruction descriptor conventions the production kernels use."""
+"""tcgen05 building blocks: a 128 x N x K tf32 product on tensor memory equals torch.  This pins the
+shared-memory / instruction descriptor conventions the production kernels use."""
 import pytest
 import torch
 
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("a_mn", [0, 1])
-@pytest.mark.parametrize("b_mn", [0, 1])
-@pytest.mark.parametrize("K,N", [(8, 32), (64, 64), (128, 128), (128, 32)])
-def test_umma_gemm(a_mn, b_mn, K, N):
+@pytest.mark.parametrize("K,N", [(8, 32), (64, 64), (128, 128), (128, 32), (64, 96)])
+def test_umma_gemm(K, N):
     from crucible_strix_halo_b200 import capi
-    g = torch.Generator(device="cuda").manual_seed(K * 1000 + N + a_mn * 2 + b_mn)
+    g = torch.Generator(device="cuda").manual_seed(K * 1000 + N)
     A = torch.randn(128, K, device="cuda", generator=g)
     B = torch.randn(N, K, device="cuda", generator=g)
     D = torch.zeros(128, N, device="cuda")
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
-    a_in = A.t().contiguous() if a_mn else A
-    b_in = B.t().contiguous() if b_mn else B
-    capi.check(capi.lib.cr_debug_umma_gemm(a_in.data_ptr(), b_in.data_ptr(), D.data_ptr(), K, N, a_mn, b_mn, status.data_ptr(), None))
+    capi.check(capi.lib.cr_debug_umma_gemm(A.data_ptr(), B.data_ptr(), D.data_ptr(), K, N, status.data_ptr(), None))
     torch.cuda.synchronize()
     assert int(status.item()) == 0, "the bounded wait on the MMA gave up"
     ref = A.double() @ B.double().t()
