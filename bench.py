@@ -158,51 +158,75 @@ class Decode262k:
         self.gw = layers.GdnWeights(g, rn(g.gdn_channels, 4, std=0.5), rn(32, std=1.5, mean=-1).clamp(-5, 1.5), rn(32, std=0.5),
                                     1 + rn(128, std=0.1), ab=rn(64, 2048, std=0.05))
         self.pos = self.CTX - 1                                 # the new token completes the cache
+        S = self.SESSIONS
+        # one contiguous block of projection rows per step (what the engine's GEMMs would write), with views per session
+        sizes = dict(q=16 * 512, k=512, v=512, idx=640, qkv=g.gdn_channels, z=4096, x=2048)
+        width = sum(sizes.values())
+        self.inp_all = rn(S, width)
         self.qs, self.gs, self.inp = [], [], []
-        for s in range(self.SESSIONS):
+        for s in range(S):
             q = layers.QsaSession(g, self.CTX, max_rows=1)
             q.k.copy_(rn(self.CTX, 2, 256).half()); q.v.copy_(rn(self.CTX, 2, 256).half())
-            # pooled keys: unit-RMS rows (what CN-RMSNorm produces), stored in the tiled layout
-            q.ik_pool.copy_(rn(q.ik_pool.numel()))
+            q.ik_pool.copy_(rn(q.ik_pool.numel()))              # pooled keys: unit-RMS rows, tiled layout
             q.ik_raw.copy_(rn(self.CTX, 128))
             gs = layers.GdnSession(g)
             gs.state[:32 * 16384].copy_(rn(32 * 16384, std=0.05))
             self.qs.append(q); self.gs.append(gs)
-            self.inp.append(dict(q=rn(1, 16, 512), k=rn(1, 512), v=rn(1, 512), idx=rn(1, 640), qkv=rn(1, g.gdn_channels),
-                                 z=rn(1, 4096), x=rn(1, 2048)))
-        S = self.SESSIONS
-        # q and idx are normalised in place by the step: one batched copy restores the raw projection rows
-        self.q_raw = torch.stack([i["q"] for i in self.inp]); self.idx_raw = torch.stack([i["idx"] for i in self.inp])
-        self.q_work, self.idx_work = self.q_raw.clone(), self.idx_raw.clone()
+            views, off = {}, 0
+            for name, n in sizes.items():
+                views[name] = self.inp_all[s, off:off + n].view(1, 16, 512) if name == "q" else self.inp_all[s, off:off + n].view(1, n)
+                off += n
+            self.inp.append(views)
+        # q and idx are normalised in place by the step: they are copied to work buffers first
+        self.q_work = torch.empty(S, 1, 16, 512, device="cuda"); self.idx_work = torch.empty(S, 1, 640, device="cuda")
         self.plan = layers.QsaStepPlan(self.qw, S)
         self.units_per_step = S
         self.alg_bytes = DECODE_BYTES_PER_SESSION * S
-        self.h_in = [{k: v.cpu().pin_memory() for k, v in i.items()} for i in self.inp]
-        self.h_out = [torch.empty(1, 4096 * 2).pin_memory() for _ in range(S)]
-        self.h2d = sum(v.numel() * 4 for v in self.inp[0].values()) * S
-        self.d2h = 2 * 4096 * 4 * S
+        self.h_in = self.inp_all.cpu().pin_memory()
+        self.out_all = torch.empty(S, 2, 4096, device="cuda")
+        self.h_out = torch.empty(S, 2, 4096).pin_memory()
+        self.h2d = self.h_in.numel() * 4
+        self.d2h = self.h_out.numel() * 4
         # per-kernel algorithmic bytes: pool scan; K/V gather; GDN state in + out; scores read by the select
         self.kernel_bytes = {"qsa_score_kernel": 65536 * 512 * S, "qsa_attn_split_kernel": 2051 * 2048 * S,
                              "gdn_step_kernel": 2 * 2097152 * S, "qsa_topk_cluster_kernel": 65536 * 4 * S}
         self.side = torch.cuda.Stream()
-        self.graph, self.graph_out = None, None
+        self.graph = None
 
-    def step_eager(self):
-        torch = self.torch
-        self.q_work.copy_(self.q_raw); self.idx_work.copy_(self.idx_raw)
-        cur = torch.cuda.current_stream()
-        self.side.wait_stream(cur)
-        with torch.cuda.stream(self.side):       # the GDN layer does not depend on the QSA layer: a parallel branch
-            go = self.layers.gdn_step(self.gw, [dict(session=self.gs[s], qkv=self.inp[s]["qkv"], z=self.inp[s]["z"], x=self.inp[s]["x"],
-                                                     pos0=self.pos) for s in range(self.SESSIONS)])
+    def _work_copies(self):
+        S = self.SESSIONS
+        self.q_work.copy_(self.inp_all[:, :8192].view(S, 1, 16, 512)); self.idx_work.copy_(self.inp_all[:, 9216:9856].view(S, 1, 640))
+
+    def _qsa(self):
         spans = [dict(session=self.qs[s], q=self.q_work[s], k=self.inp[s]["k"], v=self.inp[s]["v"], idx=self.idx_work[s], pos0=self.pos)
                  for s in range(self.SESSIONS)]
-        qo = self.plan.run(spans)
-        cur.wait_stream(self.side)
-        return qo, go
+        return self.plan.run(spans, outs=[self.out_all[s, 0:1] for s in range(self.SESSIONS)])
+
+    def _gdn(self):
+        return self.layers.gdn_step(self.gw, [dict(session=self.gs[s], qkv=self.inp[s]["qkv"], z=self.inp[s]["z"], x=self.inp[s]["x"],
+                                                   pos0=self.pos) for s in range(self.SESSIONS)],
+                                    outs=[self.out_all[s, 1:2] for s in range(self.SESSIONS)])
+
+    def step_eager(self, parallel=True):
+        torch = self.torch
+        self._work_copies()
+        cur = torch.cuda.current_stream()
+        if parallel:                              # the GDN layer does not depend on the QSA layer: a parallel branch
+            self.side.wait_stream(cur)
+            with torch.cuda.stream(self.side):
+                go = self._gdn()
+            qo = self._qsa()
+            cur.wait_stream(self.side)
+        else:
+            qo = self._qsa()
+            go = self._gdn()
+        return self.out_all
+
+    def step_profile(self):
+        return self.step_eager(parallel=False)    # one stream, so consecutive events bracket single kernels
 
     def step(self):
-        """One decode step of all sessions, replayed from a CUDA graph (7 kernels + 2 copies per step)."""
+        """One decode step of all sessions, replayed from a CUDA graph."""
         torch = self.torch
         if self.graph is None:
             for _ in range(2):
@@ -210,18 +234,13 @@ class Decode262k:
             torch.cuda.synchronize()
             self.graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(self.graph):
-                self.graph_out = self.step_eager()
+                self.step_eager()
         self.graph.replay()
-        return self.graph_out
+        return self.out_all
 
     def step_e2e(self):
-        for s in range(self.SESSIONS):
-            for k, v in self.inp[s].items():
-                v.copy_(self.h_in[s][k], non_blocking=True)
-        self.q_raw.copy_(self.torch.stack([i["q"] for i in self.inp])); self.idx_raw.copy_(self.torch.stack([i["idx"] for i in self.inp]))
-        qo, go = self.step()
-        for s in range(self.SESSIONS):
-            self.h_out[s][:, :4096].copy_(qo[s], non_blocking=True); self.h_out[s][:, 4096:].copy_(go[s], non_blocking=True)
+        self.inp_all.copy_(self.h_in, non_blocking=True)
+        self.h_out.copy_(self.step(), non_blocking=True)
 
     def config(self):
         return {"workload": self.name, "sessions_per_gpu": self.SESSIONS, "context": self.CTX, "qsa_heads": "16q/2kv x256",
@@ -377,7 +396,7 @@ def main():
     barrier()
     for _ in range(args.steps):
         capi.lib.cr_profile_begin(C.c_void_p(torch.cuda.current_stream().cuda_stream))
-        wl.step_eager()
+        (wl.step_profile if hasattr(wl, "step_profile") else wl.step_eager)()
     prof = capi.profile_collect()
     capi.lib.cr_profile_enable(0)
     if rank != 0:

@@ -50,15 +50,15 @@ def _gdn_args(w: GdnWeights, s: GdnSession, qkv, z, x, out, pos0, R, replay, com
                    pos0, R, replay, commit, pack_rows, pack_off)
 
 
-def gdn_step(w: GdnWeights, spans, fmt=capi.OUT_RAW_F32):
+def gdn_step(w: GdnWeights, spans, fmt=capi.OUT_RAW_F32, outs=None):
     """spans: list of dicts(session, qkv [R,C] f32, z [R,Hv*128] f32, x [R,hidden] f32, pos0, replay, commit).
     One launch for all spans (LaunchGdnCore / packed verify).  Returns the list of outputs [R, Hv*128]."""
     g = w.g
-    outs, arr = [], (GdnArgs * len(spans))()
+    given, outs, arr = outs, [], (GdnArgs * len(spans))()
     pend_rows = spans[0]["session"].pend_rows
     for i, sp in enumerate(spans):
         R = sp["qkv"].shape[0]
-        out = torch.empty(R, g.gdn_vheads * 128, device=sp["qkv"].device, dtype=_out_dtype(fmt))
+        out = given[i] if given is not None else torch.empty(R, g.gdn_vheads * 128, device=sp["qkv"].device, dtype=_out_dtype(fmt))
         outs.append(out)
         arr[i] = _gdn_args(w, sp["session"], sp["qkv"], sp["z"], sp["x"], out, sp["pos0"], R,
                            sp.get("replay", 0), sp.get("commit", R))
@@ -137,14 +137,14 @@ class QsaStepPlan:
         n = lib.cr_qsa_scratch_bytes(C.byref(w.g), total_rows)
         self.scratch = torch.zeros(n, device=device, dtype=torch.uint8)
 
-    def run(self, spans, want_context=False):
+    def run(self, spans, want_context=False, outs=None):
         """spans: list of dicts(session, q [R,Hq,512] f32 (modified in place), k, v [R,Hkv*256], idx [R,640], pos0)."""
         g = self.w.g
         arr = (QsaArgs * len(spans))()
-        outs, ctxs = [], []
+        given, outs, ctxs = outs, [], []
         for i, sp in enumerate(spans):
             R = sp["q"].shape[0]
-            out = torch.empty(R, g.q_heads * 256, device=sp["q"].device, dtype=_out_dtype(self.fmt))
+            out = given[i] if given is not None else torch.empty(R, g.q_heads * 256, device=sp["q"].device, dtype=_out_dtype(self.fmt))
             ctx = torch.empty(R, g.q_heads, 256, device=sp["q"].device, dtype=torch.float32) if want_context else None
             outs.append(out)
             ctxs.append(ctx)

@@ -187,3 +187,43 @@ def test_prefill_part_matches_oracle(pos0, R):
             if not np.array_equal(got, sels[o]):
                 continue
         assert_close_attn(out[r], ref[o], max_abs=1e-3, cos=0.99999, what="row %d" % r)
+
+
+def test_c1_layer_seq4096_with_projections():
+    """The CPU-runnable configuration of the path: one gated full-attention layer, causal prefill, batch 1, seq 4096,
+    hidden 2048, 16 Q / 2 KV heads x 256, RoPE on the first 64 dims, sigmoid gate; activations ~ N(0,1), weights
+    ~ N(0,0.02), fp32, seed 0.  Projections are plain fp32 matmuls outside the attention core; the core runs as two
+    2048-row parts.  Sampled rows (around the dense/sparse boundary and the end) against the fp64 oracle."""
+    capi, layers, g, og, rng, _, suh, _ = _setup(16, seed=0)
+    torch.manual_seed(0)
+    T, hidden = 4096, 2048
+    x = torch.randn(T, hidden, device="cuda")
+    Wq, Wk, Wv, Wi = (torch.randn(n, hidden, device="cuda") * 0.02 for n in (16 * 512, 512, 512, 640))
+    q, k, v, idx = (x @ W.t() for W in (Wq, Wk, Wv, Wi))
+    ones = [np.ones(256), np.ones(256), np.ones(128), np.ones(128)]      # norm gamma = 1
+    w = layers.QsaWeights(g, *ones)
+    ses, oc = layers.QsaSession(g, T), ao.QsaCache(og, T)
+    ses.scores = torch.zeros(2048, ses.sstride, device="cuda"); ses.sel = torch.zeros(2048, 512, device="cuda", dtype=torch.int32)
+    ses.nsel = torch.zeros(2048, device="cuda", dtype=torch.int32)
+    plan = layers.QsaPrefillPlan(w, 2048)
+    f = lambda t_: t_.double().cpu().numpy()
+    outs = []
+    for p0 in (0, 2048):
+        sl = slice(p0, p0 + 2048)
+        qd = q[sl].reshape(2048, 16, 512).clone(); idxd = idx[sl].clone()
+        outs.append(plan.run(ses, qd, k[sl].contiguous(), v[sl].contiguous(), idxd, p0).clone())
+    out = torch.cat(outs).cpu().numpy()
+    sample0 = [0, 1, 5, 1023, 2046, 2047]
+    sample1 = [0, 1, 2, 3, 4, 7, 500, 1500, 2046, 2047]                   # absolute 2048.. : sparse from position 2051
+    ref0, *_ = ao.qsa_rows(f(q[:2048]).reshape(2048, 16, 512), f(k[:2048]), f(v[:2048]), f(idx[:2048]), ones, oc, 0, og, return_detail=True, rows=sample0)
+    ref1, sels, scs, _, _ = ao.qsa_rows(f(q[2048:]).reshape(2048, 16, 512), f(k[2048:]), f(v[2048:]), f(idx[2048:]), ones, oc, 2048, og,
+                                        return_detail=True, rows=sample1)
+    for o, r in enumerate(sample0):
+        assert_close_attn(out[r], ref0[o], max_abs=2e-3, cos=0.9999, what="row %d" % r)
+    for o, r in enumerate(sample1):
+        if sels[o] is not None:
+            got = ses.sel[r].cpu().numpy()
+            assert ao.selection_agrees(scs[o], got, sels[o]), "row %d" % (2048 + r)
+            if not np.array_equal(got, sels[o]):
+                continue
+        assert_close_attn(out[2048 + r], ref1[o], max_abs=2e-3, cos=0.9999, what="row %d" % (2048 + r))
