@@ -260,6 +260,7 @@ def cpu_baseline(workload, seconds_hint=10.0):
     lib_path = build.build_oracle()
     lib = C.CDLL(lib_path)
     lib.oracle_threads.restype = C.c_int
+    lib.oracle_set_threads(C.c_int(len(os.sched_getaffinity(0))))   # every core this process may run on
     cores = lib.oracle_threads()
     rng = np.random.default_rng(0)
     f32 = lambda a: np.ascontiguousarray(a, np.float32)

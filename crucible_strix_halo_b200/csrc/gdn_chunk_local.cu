@@ -4,9 +4,9 @@
 //      (3 halo rows from the previous rows, the ring, or zero), then conv(4) + SiLU + L2 norm -> qhat, khat (tf32);
 //   2. Gram matrices K K^T and Q K^T on tensor cores, kept in accumulator registers for all value heads;
 //   3. per value head: log-decay prefix G and beta, L = tril(beta K K^T e^{dG}, -1), QKd = tril(Q K^T e^{dG}), and
-//      W = (I + L)^-1 (beta e^G K),  Ut = (I + L)^-1 (beta V)  by exact fp32 forward substitution: one thread per
-//      output column with the column in registers, L rows broadcast from shared memory, no barriers; the v
-//      columns run conv + SiLU on the fly from the staged raw rows.
+//      T = (I + L)^-1 by an exact fp32 blocked inverse (16 x 16 diagonal blocks by substitution, off-diagonal blocks
+//      in block-row order), then W = T (beta e^G K) and Ut = T (beta V) on tensor cores with tf32 operands; the
+//      v columns run conv + SiLU from the staged raw rows.
 // Outputs go straight into the layouts the scan consumes (K-major tiles for the tcgen05 scan).
 // Two CTAs fit per SM (106 KB of shared memory each), so one CTA's loads hide behind the other's math.
 #include "gdn_chunk.cuh"

@@ -23,6 +23,15 @@ int oracle_threads(void) {
 #endif
 }
 
+/* Overrides OMP_NUM_THREADS (launchers such as torchrun export OMP_NUM_THREADS=1). */
+void oracle_set_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 static inline float sigmoidf_(float x) { return 1.f / (1.f + expf(-x)); }
 static inline float siluf_(float x) { return x / (1.f + expf(-x)); }
 
