@@ -45,12 +45,11 @@ __device__ __forceinline__ float siluf_(float v) { return v / (1.f + __expf(-v))
 __device__ __forceinline__ float bf16_bits_to_float(uint16_t u) { return __uint_as_float((uint32_t)u << 16); }
 
 // Round to tf32 (10-bit mantissa, nearest, ties away): the tensor-core unit ignores the low 13 bits of an
-// fp32 operand, so operands are rounded when they are written.
-__device__ __forceinline__ float tf32r(float x) {
-  uint32_t r;
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
-  return __uint_as_float(r);
-}
+// fp32 operand, so operands are rounded when they are written.  Integer add + mask gives the same bits as
+// cvt.rna.tf32.f32 for every finite value (and keeps infinities); the cvt instruction itself issues at the
+// rate of the special-function unit (about one warp instruction per 7 cycles per scheduler, measured), which
+// made it the longest part of every epilogue that used it.
+__device__ __forceinline__ float tf32r(float x) { return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xFFFFE000u); }
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

@@ -12,8 +12,8 @@ static size_t chunk_layout(const cr_geometry* g, int rows, ChunkWs* ws, char* ba
   auto take = [&](size_t bytes) { const size_t o = off; off += (bytes + 255) & ~(size_t)255; return o; };
   const size_t oW = take(Hv * chunks * 64 * 128 * 4), oU = take(Hv * chunks * 64 * 128 * 4);
   const size_t oQ = take(Hv * chunks * 64 * 64 * 4), oG = take(Hv * chunks * 64 * 4);
-  const size_t oWQ = take(Hv * chunks * 16384 * 4), oQKp = take(Hv * chunks * 8192 * 4);
-  const size_t oKt = take((size_t)g->gdn_kheads * chunks * 8192 * 4);
+  const size_t oWQ = take(Hv * chunks * 16384 * 4), oQKp = take(Hv * chunks * 4096 * 4);
+  const size_t oKt = take(Hv * chunks * 8192 * 4);
   if (ws) {
     ws->W = (float*)(base + oW); ws->Ut = (float*)(base + oU); ws->QKd = (float*)(base + oQ); ws->G = (float*)(base + oG);
     ws->WQ = (float*)(base + oWQ); ws->QKp = (float*)(base + oQKp); ws->Kt = (float*)(base + oKt);

@@ -21,12 +21,12 @@ constexpr int kLdM = 68;    // [64][64] operand read row-major as A
 
 struct ChunkWs {
   float* W;    // [Hv][chunks][64][128]  tf32
-  float* Ut;   // [Hv][chunks][64][128]  fp32
+  float* Ut;   // [Hv][chunks][64][128]  fp32; for the tcgen05 scan [Hv][chunks][4][4][128][4] = [token / 16][(token % 16) / 4][column][token % 4]
   float* QKd;  // [Hv][chunks][64][64]   tf32
   float* G;    // [Hv][chunks][64]       cumulative log decay inside the chunk
   float* WQ;   // [Hv][chunks][32][128][4] rows 0-63 W, rows 64-127 e^G Q, one K-major tile (tcgen05 scan only)
-  float* QKp;  // [Hv][chunks][16][128][4] rows 0-63 zero, rows 64-127 QKd, K-major tile (tcgen05 scan only)
-  float* Kt;   // [Hk][chunks][16][128][4] K^T as a K-major tile (tcgen05 scan only)
+  float* QKp;  // [Hv][chunks][16][64][4] QKd as a K-major tile (tcgen05 scan only)
+  float* Kt;   // [Hv][chunks][16][128][4] (e^{G_end - G} K)^T as a K-major tile (tcgen05 scan only)
   int chunks;
 };
 

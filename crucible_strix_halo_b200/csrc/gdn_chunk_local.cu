@@ -206,15 +206,20 @@ __global__ void __launch_bounds__(256, 2) gdn_chunk_local_kernel(GdnPrefillParam
   }
   __syncthreads();
   if constexpr (UM) {
-    // K^T of the chunk, K-major over tokens: unit (token/4, key) holds 4 tokens of one key
-    float* kt = ws.Kt + ((size_t)kh * ws.chunks + c) * 8192;
-    for (int i = t; i < 16 * 128; i += 256) {
-      const int key = i & 127, tc = i >> 7;
-      *reinterpret_cast<float4*>(kt + (size_t)i * 4) = make_float4(Ks[(4 * tc) * kLdK + key], Ks[(4 * tc + 1) * kLdK + key],
-                                                                   Ks[(4 * tc + 2) * kLdK + key], Ks[(4 * tc + 3) * kLdK + key]);
-    }
-    // Qt = e^G Q per value head, K-major over keys
+    // per value head: K'^T = (e^{G_end - G} K)^T, K-major over tokens (unit (token / 4, key) holds 4 tokens of one
+    // key; the decay towards the chunk end is folded into K so that the scan multiplies U itself), and
+    // Qt = e^G Q, K-major over keys
     for (int vi = 0; vi < rep; ++vi) {
+      float* kt = ws.Kt + ((size_t)(kh * rep + vi) * ws.chunks + c) * 8192;
+      const float* Gv = Gs + vi * 64;
+      const float Ge = Gv[63];
+      for (int i = t; i < 16 * 128; i += 256) {
+        const int key = i & 127, tc = i >> 7;
+        const float4 gq = *reinterpret_cast<const float4*>(Gv + 4 * tc);
+        *reinterpret_cast<float4*>(kt + (size_t)i * 4) =
+            make_float4(tf32r(__expf(Ge - gq.x) * Ks[(4 * tc) * kLdK + key]), tf32r(__expf(Ge - gq.y) * Ks[(4 * tc + 1) * kLdK + key]),
+                        tf32r(__expf(Ge - gq.z) * Ks[(4 * tc + 2) * kLdK + key]), tf32r(__expf(Ge - gq.w) * Ks[(4 * tc + 3) * kLdK + key]));
+      }
       float* qt = ws.WQ + ((size_t)(kh * rep + vi) * ws.chunks + c) * 16384;
       for (int i = t; i < 32 * 64; i += 256) {
         const int row = i & 63, kc = i >> 6;
@@ -238,10 +243,7 @@ __global__ void __launch_bounds__(256, 2) gdn_chunk_local_kernel(GdnPrefillParam
     const float* Gv = Gs + vi * 64; const float* bv = bs + vi * 64; const float* ev = es + vi * 64;
     __syncthreads();                    // previous head done with LT and the staging tile; qhat no longer needed
     {   // L (warps 0-3) and QKd (warps 4-7) straight from the Gram fragments
-      float* qkd = UM ? ws.QKp + unit * 8192 : ws.QKd + unit * 64 * 64;
-      if constexpr (UM) {   // rows 0-63 of the padded tile are zero (they meet the W rows of the accumulator)
-        for (int i = t; i < 16 * 64; i += 256) *reinterpret_cast<float4*>(qkd + (size_t)((i >> 6) * 128 + (i & 63)) * 4) = make_float4(0.f, 0.f, 0.f, 0.f);
-      }
+      float* qkd = UM ? ws.QKp + unit * 4096 : ws.QKd + unit * 64 * 64;
 #pragma unroll
       for (int n = 0; n < 8; ++n)
 #pragma unroll
@@ -254,7 +256,7 @@ __global__ void __launch_bounds__(256, 2) gdn_chunk_local_kernel(GdnPrefillParam
             const float b = bv[row];
             *reinterpret_cast<float2*>(LT + row * kLdM + col) = make_float2(col < row ? b * v0 * p0 : 0.f, col + 1 < row ? b * v1 * p1 : 0.f);
           } else {
-            const int at = UM ? ((col >> 2) * 128 + 64 + row) * 4 + (col & 3) : row * 64 + col;
+            const int at = UM ? ((col >> 2) * 64 + row) * 4 + (col & 3) : row * 64 + col;
             *reinterpret_cast<float2*>(qkd + at) = make_float2(col <= row ? tf32r(v0 * p0) : 0.f, col + 1 <= row ? tf32r(v1 * p1) : 0.f);
           }
         }
@@ -324,11 +326,22 @@ __global__ void __launch_bounds__(256, 2) gdn_chunk_local_kernel(GdnPrefillParam
 #pragma unroll
       for (int n = 0; n < 8; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
       warp_gemm<8, 8, false, false>(acc, LT + mt * 16 * kLdM, kLdM, Qs + nh * 64, kLdX);
-      float* dst = ws.Ut + (unit * 64 + mt * 16) * 128 + nh * 64;
+      if constexpr (UM) {   // [token / 16][(token % 16) / 4][column][token % 4]: a scan thread owns a column and reads
+                            // four tokens per 128-bit load, a warp 512 contiguous bytes
+        float* dst = ws.Ut + unit * 8192 + (size_t)mt * 2048;
 #pragma unroll
-      for (int n = 0; n < 8; ++n) {
-        *reinterpret_cast<float2*>(dst + g * 128 + n * 8 + 2 * tq) = make_float2(acc[n][0], acc[n][1]);
-        *reinterpret_cast<float2*>(dst + (g + 8) * 128 + n * 8 + 2 * tq) = make_float2(acc[n][2], acc[n][3]);
+        for (int n = 0; n < 8; ++n) {
+          const int col = nh * 64 + n * 8 + 2 * tq;
+          float* d = dst + (g >> 2) * 512 + col * 4 + (g & 3);
+          d[0] = acc[n][0]; d[4] = acc[n][1]; d[1024] = acc[n][2]; d[1028] = acc[n][3];
+        }
+      } else {
+        float* dst = ws.Ut + (unit * 64 + mt * 16) * 128 + nh * 64;
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+          *reinterpret_cast<float2*>(dst + g * 128 + n * 8 + 2 * tq) = make_float2(acc[n][0], acc[n][1]);
+          *reinterpret_cast<float2*>(dst + (g + 8) * 128 + n * 8 + 2 * tq) = make_float2(acc[n][2], acc[n][3]);
+        }
       }
     }
   }

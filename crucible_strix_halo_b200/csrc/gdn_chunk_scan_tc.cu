@@ -1,21 +1,25 @@
-// gdn_chunk_scan_tc_kernel: the sequential part of the chunk-64 WY scan on tcgen05 tensor cores.
+// gdn_chunk_scan_tc_kernel: the sequential part of the chunk-64 WY scan on tcgen05 tensor cores, with the
+// recurrent operands resident in tensor memory.
 //
-// One CTA per (value head, 64-column slice of the state): two compute warpgroups (each 128 threads = the 128 lanes
-// of tensor memory, 32 accumulator columns per warpgroup) and one issuer warp whose elected thread feeds the
-// tensor core and the bulk-copy engine.
-// Accumulators live in tensor memory; operands are K-major un-swizzled tiles in shared memory
-// (float[K/4][rows][4], see umma.cuh).  The local kernel writes them in exactly that layout, so each arrives
-// with one bulk copy (TMA, mbarrier transaction count) into a buffer that is re-filled for the next chunk as soon
-// as the MMAs that read it have completed.  S^T, U^T and U'^T are written by the compute warps themselves
-// (transposed; one buffer each is enough, because every writer waits on a commit that follows the last MMA
-// reading the old contents).  Per chunk, three MMA groups (32 tcgen05.mma of K = 8, N = 64):
-//   D1[128 x 64] = [W ; e^G Q] S^T   lanes 0-63: W S (tokens)        -> U = Ut - W S, U' = e^{G_end-G} U   (token warps)
-//                                    lanes 64-127: e^G Q S
-//   D2[128 x 64] = K^T U'            lanes = keys                    -> S = e^{G_end} S + D2 (fp32 registers, all warps)
-//   D1 += [0 ; QKd] U                lanes 64-127 become Y           -> readout stored by the other warps, off the chain
-// D1 alternates between two accumulators, so the readout of chunk c overlaps D1 of chunk c+1.  The warps
-// synchronise only through mbarriers.  Every wait is bounded: a wait that gives up raises a status word, after
-// which no thread waits again; the kernel runs to its end, frees its tensor memory and returns.
+// One CTA per value head.  Everything is kept transposed, so that a lane of tensor memory is one value column
+// v of the state and the 128 lanes are the 128 columns of the head:
+//   S^T [v][key]   tf32 copy of the state       TMEM columns   0-127   A operand of D1
+//   D1  [v][r]     r < 64: (W S)^T, r >= 64: Y^T  TMEM columns 128-255
+//   D2  [v][key]   (K'^T U)^T                     TMEM columns 256-383
+//   U^T [v][token]                                TMEM columns 384-447            A operand of D2 and D3
+// Per chunk (32 tcgen05.mma of K = 8, A from tensor memory, B a K-major tile in shared memory that the local
+// kernel wrote in exactly that layout and one bulk copy brings in):
+//   D1 = S^T [W ; e^G Q]^T  (N = 128)   ->  U = Ut - W S, written back to TMEM
+//   D2 = U^T K'             (N = 128)   ->  S = e^{G_end} S + D2   (fp32 master in registers, tf32 copy to TMEM)
+//        K' = e^{G_end - G} K: the local kernel folds the decay towards the chunk end into the key tile
+//   D1[:, 64:] += U^T QKd^T (N = 64)    ->  Y, stored to global memory
+// Because an accumulator row and an A-operand row are both "lane v", no epilogue transposes anything and nothing
+// recurrent passes through shared memory.  Four compute warpgroups split the columns of every accumulator
+// (warp w reaches lanes 32 (w % 4) .. +31, so each warpgroup covers all lanes); the fp32 master state is spread
+// the same way (thread = column v, 32 keys).  One issuer warp feeds the tensor core, one loader warp keeps two
+// chunks of operand tiles in flight (224 KB of shared memory, two stages).  Warps synchronise only through
+// mbarriers.  Every wait is bounded: a wait that gives up raises a status word, after which no thread waits
+// again; the kernel runs to its end, frees its tensor memory and returns.
 #include "gdn_chunk.cuh"
 #include "umma.cuh"
 
@@ -23,197 +27,190 @@ namespace cr {
 
 __device__ int g_gdn_scan_status = 0;
 
-constexpr int kWG = 2;                      // compute warpgroups per CTA, 32 state columns each
-constexpr int kNC = 32 * kWG, kNCP = kNC + 1;    // slice width; padded plane (conflict-free transposed stores)
-struct TcSmem {
-  static constexpr int kA1 = 0, kK = 16384, kQK = 24576, kS = 32768;      // float offsets
-  static constexpr int kSsz = 32 * kNCP * 4, kUsz = 16 * kNCP * 4;
-  static constexpr int kU = kS + kSsz, kUp = kU + kUsz, kEnd = kUp + kUsz;
-  static constexpr size_t kBytes = (size_t)kEnd * sizeof(float) + 128;
-};
+constexpr int kWG = 4;                                    // compute warpgroups
+constexpr int kScanThreads = 128 * kWG + 64;              // + issuer warp + loader warp
+constexpr int kStageFloats = 16384 + 8192 + 4096;         // [W ; e^G Q] 64 KB, K^T 32 KB, QKd 16 KB
+constexpr size_t kScanSmem = (size_t)2 * kStageFloats * sizeof(float) + 128;
+constexpr uint32_t kColS = 0, kColD1 = 128, kColD2 = 256, kColU = 384;
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_u32(bar)) : "memory");
 }
 
-__global__ void __launch_bounds__(128 * kWG + 32) gdn_chunk_scan_tc_kernel(GdnPrefillParams P, ChunkWs ws) {
-  using L = TcSmem;
-  constexpr int NC = kNC, NCP = kNCP;
-  constexpr uint32_t kTmemCols = kWG == 1 ? 128 : 256;   // D1 x 2 (NC columns each), D2 (NC)
-  constexpr int kIssuer = 4 * kWG;              // index of the issuer warp
+__global__ void __launch_bounds__(kScanThreads, 1) gdn_chunk_scan_tc_kernel(GdnPrefillParams P, ChunkWs ws) {
   extern __shared__ __align__(128) float sm[];
-  float* A1sm = sm + L::kA1;     // [32][128][4]  rows 0-63 W, rows 64-127 e^G Q; K-major over keys
-  float* Ksm = sm + L::kK;       // [16][128][4]  K^T, K-major over tokens
-  float* QKsm = sm + L::kQK;     // [16][128][4]  rows 0-63 zero, rows 64-127 QKd
-  float* Ssm = sm + L::kS;       // [32][NC+1][4] S^T, K-major over keys
-  float* Usm = sm + L::kU;       // [16][NC+1][4] U^T, K-major over tokens
-  float* Upsm = sm + L::kUp;     // [16][NC+1][4] U'^T
-  __shared__ __align__(8) uint64_t bars[8];
+  __shared__ __align__(8) uint64_t bars[12];
   __shared__ uint32_t tmem_slot;
   __shared__ volatile int dead;
-  uint64_t *fullA = &bars[0], *fullK = &bars[1], *fullQK = &bars[2];
-  uint64_t *d1 = &bars[3], *d2 = &bars[4], *d3 = &bars[5], *uReady = &bars[6], *sReady = &bars[7];
+  uint64_t* full = &bars[0];                               // one per stage: all three tiles of a chunk
+  uint64_t *d1 = &bars[6], *d2 = &bars[7], *d3 = &bars[8], *uReady = &bars[9], *sReady = &bars[10], *yDone = &bars[11];
   const int t = threadIdx.x, w = t >> 5, l = t & 31;
-  constexpr int SL = 128 / NC;
-  const int h = blockIdx.x / SL, col0 = (blockIdx.x % SL) * NC;
-  const int rep = P.Hv / P.Hk, kh = h / rep, VW = P.Hv * 128, R = P.a.R;
+  constexpr int kIssuer = 4 * kWG, kLoader = kIssuer + 1;
+  const int h = blockIdx.x, VW = P.Hv * 128, R = P.a.R;
   const int nch = ws.chunks;
 
   if (t == 0) {
 #pragma unroll
-    for (int i = 0; i < 6; ++i) umma::mbar_init(&bars[i], 1);
-    umma::mbar_init(uReady, 64 * kWG);
-    umma::mbar_init(sReady, 128 * kWG);
+    for (int i = 0; i < 9; ++i) umma::mbar_init(&bars[i], 1);
+    umma::mbar_init(uReady, 4 * kWG);                      // one arrival per compute warp
+    umma::mbar_init(sReady, 4 * kWG);
+    umma::mbar_init(yDone, 4 * kWG);
     umma::mbar_fence_init();
     dead = 0;
   }
-  if (w == kIssuer) umma::tmem_alloc(&tmem_slot, kTmemCols);
+  if (w == kIssuer) umma::tmem_alloc(&tmem_slot, 512);
   umma::fence_before_sync();
   __syncthreads();
   umma::fence_after_sync();
   const uint32_t tm = tmem_slot;
+  bool gave_up = false;                                    // a thread that gave up once does not wait again
   auto wait = [&](uint64_t* bar, uint32_t parity) {
-    if (dead) return;
-    if (!umma::mbar_wait(bar, parity)) { dead = 1; g_gdn_scan_status = 1; }
+    if (gave_up) return;
+    if (!umma::mbar_wait_timed(bar, parity, &dead)) { gave_up = true; dead = 1; g_gdn_scan_status = 1; }
+  };
+  // Compute warps: lane 0 polls and lane 0 arrives (an arrival is an atomic on one shared-memory word: 32 lanes
+  // arriving one by one cost more than the epilogue they follow); __syncwarp orders the other lanes' accesses.
+  auto warp_wait = [&](uint64_t* bar, uint32_t parity) {
+    if (l == 0) wait(bar, parity);
+    __syncwarp();
+    umma::fence_after_sync();
+  };
+  auto warp_arrive = [&](uint64_t* bar) {
+    umma::fence_before_sync();
+    __syncwarp();
+    if (l == 0) mbar_arrive(bar);
   };
 
-  if (w == kIssuer) {
-    // ------------------------------------------------------------------ issuer: loads and tensor-core work
+  if (w == kLoader) {
+    // ------------------------------------------------------------------ loader: two chunks of tiles in flight
     if (l == 0) {
-      auto load_a = [&](int c) { umma::mbar_expect_tx(fullA, 65536); umma::bulk_load(A1sm, ws.WQ + ((size_t)h * nch + c) * 16384, 65536, fullA); };
-      auto load_k = [&](int c) { umma::mbar_expect_tx(fullK, 32768); umma::bulk_load(Ksm, ws.Kt + ((size_t)kh * nch + c) * 8192, 32768, fullK); };
-      auto load_qk = [&](int c) { umma::mbar_expect_tx(fullQK, 32768); umma::bulk_load(QKsm, ws.QKp + ((size_t)h * nch + c) * 8192, 32768, fullQK); };
-      load_a(0); load_k(0); load_qk(0);
-      constexpr uint32_t idesc = umma::idesc_tf32(128, NC, false, false);
-      // descriptors of the first K step; a step of 8 along K advances the start address by 2 planes (16-byte units)
-      const uint64_t dA = umma::desc_kmajor(A1sm, 128, 0), dK = umma::desc_kmajor(Ksm, 128, 0), dQK = umma::desc_kmajor(QKsm, 128, 0);
-      const uint64_t dS = umma::desc_kmajor_padded(Ssm, NCP, 0), dU = umma::desc_kmajor_padded(Usm, NCP, 0);
-      const uint64_t dUp = umma::desc_kmajor_padded(Upsm, NCP, 0);
+      auto load = [&](int c) {
+        const int s = c & 1;
+        float* A1s = sm + s * kStageFloats;
+        const float* a = ws.WQ + ((size_t)h * nch + c) * 16384;
+        umma::mbar_expect_tx(&full[s], kStageFloats * 4);
+        umma::bulk_load(A1s, a, 32768, &full[s]);
+        umma::bulk_load(A1s + 8192, a + 8192, 32768, &full[s]);
+        umma::bulk_load(A1s + 16384, ws.Kt + ((size_t)h * nch + c) * 8192, 32768, &full[s]);
+        umma::bulk_load(A1s + 24576, ws.QKp + ((size_t)h * nch + c) * 4096, 16384, &full[s]);
+      };
+      load(0);
+      if (nch > 1) load(1);
+      for (int c = 0; c + 2 < nch; ++c) {   // the stage of chunk c is free once every MMA of chunk c has completed
+        wait(d3, c & 1);
+        load(c + 2);
+      }
+    }
+  } else if (w == kIssuer) {
+    // ------------------------------------------------------------------ issuer: tensor-core work
+    if (l == 0) {
+      constexpr uint32_t idesc128 = umma::idesc_tf32(128, 128, false, false), idesc64 = umma::idesc_tf32(128, 64, false, false);
       for (int c = 0; c < nch; ++c) {
-        const int b = c & 1;
-        const uint32_t acc1 = tm + b * NC;
+        const int b = c & 1, s = c & 1, ph = (c >> 1) & 1;
+        const float* A1s = sm + s * kStageFloats;
+        // a step of 8 along K advances a descriptor's start address by two planes (16-byte units)
+        const uint64_t dA = umma::desc_kmajor(A1s, 128, 0), dK = umma::desc_kmajor(A1s + 16384, 128, 0);
+        const uint64_t dQK = umma::desc_kmajor(A1s + 24576, 64, 0);
         wait(sReady, b);
-        wait(fullA, b);
+        if (c > 0) wait(yDone, b ^ 1);                     // the readout columns of the previous chunk have been stored
+        wait(&full[s], ph);
         umma::fence_after_sync();
 #pragma unroll
-        for (int s8 = 0; s8 < 16; ++s8) umma::mma_tf32_ss(acc1, dA + (uint64_t)(s8 * 256), dS + (uint64_t)(s8 * 2 * NCP), idesc, s8 > 0);
+        for (int s8 = 0; s8 < 16; ++s8) umma::mma_tf32_ts(tm + kColD1, tm + kColS + 8 * s8, dA + (uint64_t)(s8 * 256), idesc128, s8 > 0);
         umma::commit(d1);
         wait(uReady, b);
-        wait(fullK, b);
         umma::fence_after_sync();
 #pragma unroll
-        for (int s8 = 0; s8 < 8; ++s8) umma::mma_tf32_ss(tm + 2 * NC, dK + (uint64_t)(s8 * 256), dUp + (uint64_t)(s8 * 2 * NCP), idesc, s8 > 0);
+        for (int s8 = 0; s8 < 8; ++s8) umma::mma_tf32_ts(tm + kColD2, tm + kColU + 8 * s8, dK + (uint64_t)(s8 * 256), idesc128, s8 > 0);
         umma::commit(d2);
-        wait(fullQK, b);
 #pragma unroll
-        for (int s8 = 0; s8 < 8; ++s8) umma::mma_tf32_ss(acc1, dQK + (uint64_t)(s8 * 256), dU + (uint64_t)(s8 * 2 * NCP), idesc, 1u);
+        for (int s8 = 0; s8 < 8; ++s8) umma::mma_tf32_ts(tm + kColD1 + 64, tm + kColU + 8 * s8, dQK + (uint64_t)(s8 * 128), idesc64, 1u);
         umma::commit(d3);
-        // refill the buffers whose readers have completed
-        if (c + 1 < nch) {
-          wait(d1, b); load_a(c + 1);
-          wait(d2, b); load_k(c + 1);
-          wait(d3, b); load_qk(c + 1);
-        }
       }
     }
   } else {
-    // ------------------------------------------------------------------ compute warps (thread = TMEM lane)
-    const int wg = w >> 2, key = t & 127, cw = 32 * wg;    // warpgroup wg owns columns [cw, cw + 32) of every accumulator
-    const bool tokw = (w & 3) < 2;                         // lanes 0-63 of D1 = W S (tokens); lanes 64-127 = readout
-    const int tk = key & 63;
-    float S[32];                                           // state row of this key, this warpgroup's columns: fp32 master
-    float* st = P.a.state + (size_t)h * 16384 + (size_t)key * 128 + col0 + cw;
+    // ------------------------------------------------------------------ compute warps (thread = TMEM lane = column v)
+    const int wg = w >> 2, v = t & 127;
+    float S[32];                                           // state column v, keys 32 wg .. +31: fp32 master
+    float* st = P.a.state + (size_t)h * 16384 + (size_t)(32 * wg) * 128 + v;
 #pragma unroll
-    for (int j = 0; j < 32; j += 4) {
-      const float4 v = *reinterpret_cast<const float4*>(st + j);
-      S[j] = v.x; S[j + 1] = v.y; S[j + 2] = v.z; S[j + 3] = v.w;
+    for (int j = 0; j < 32; ++j) S[j] = st[j * 128];
+    {
+      float r[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) r[j] = tf32r(S[j]);
+      umma::tmem_st32(umma::tmem_addr(tm, w, kColS + 32 * wg), r);
+      umma::tmem_st_wait();
     }
-#pragma unroll
-    for (int j = 0; j < 32; ++j) Ssm[((key >> 2) * NCP + cw + j) * 4 + (key & 3)] = tf32r(S[j]);
-    umma::fence_async_smem();
-    mbar_arrive(sReady);
+    warp_arrive(sReady);
 
-    float ut[32];                                          // Ut row of this thread's token (token warps)
-    float Gtok = 0.f, Gend = 0.f;
+    float ut[16];                                          // Ut of column v, tokens 16 wg .. +15
+    float Gend = 0.f;
     auto fetch_rows = [&](int c) {
       const size_t unit = (size_t)h * nch + c;
       Gend = ws.G[unit * 64 + 63];
-      if (tokw) {
-        Gtok = ws.G[unit * 64 + tk];
-        const float* up = ws.Ut + (unit * 64 + tk) * 128 + col0 + cw;
+      const float* up = ws.Ut + unit * 8192 + (size_t)wg * 2048 + v * 4;   // [token / 16][(token % 16) / 4][v][token % 4]
 #pragma unroll
-        for (int j = 0; j < 32; j += 4) {
-          const float4 v = *reinterpret_cast<const float4*>(up + j);
-          ut[j] = v.x; ut[j + 1] = v.y; ut[j + 2] = v.z; ut[j + 3] = v.w;
-        }
+      for (int j = 0; j < 16; j += 4) {
+        const float4 x = *reinterpret_cast<const float4*>(up + j * 128);
+        ut[j] = x.x; ut[j + 1] = x.y; ut[j + 2] = x.z; ut[j + 3] = x.w;
       }
     };
     fetch_rows(0);
     for (int c = 0; c < nch; ++c) {
       const int b = c & 1;
       const float ge = Gend;
-      if (tokw) {   // U = Ut - W S, transposed into shared memory (tf32), and U' = e^{G_end - G} U
-        const float sc = __expf(ge - Gtok);
-        wait(d1, b);
-        umma::fence_after_sync();
-        float p[32];
-        umma::tmem_ld32(umma::tmem_addr(tm, w, b * NC + cw), p);
+      warp_wait(d1, b);
+      {   // U = Ut - W S, back into tensor memory as the A operand of D2 and D3
+        float p[16];
+        umma::tmem_ld16(umma::tmem_addr(tm, w, kColD1 + 16 * wg), p);
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const float u = ut[j] - p[j];
-          const int at = ((tk >> 2) * NCP + cw + j) * 4 + (tk & 3);
-          Usm[at] = tf32r(u);
-          Upsm[at] = tf32r(sc * u);
-        }
-        umma::fence_async_smem();
-        umma::fence_before_sync();
-        mbar_arrive(uReady);
+        for (int j = 0; j < 16; ++j) p[j] = tf32r(ut[j] - p[j]);
+        umma::tmem_st16(umma::tmem_addr(tm, w, kColU + 16 * wg), p);
+        umma::tmem_st_wait();
       }
+      warp_arrive(uReady);
       if (c + 1 < nch) fetch_rows(c + 1);                  // global loads fly while the tensor core works
-      wait(d2, b);
-      umma::fence_after_sync();
-      {   // S <- e^{G_end} S + K^T U'; D1 of this chunk, the only reader of S^T, completed before U
+      warp_wait(d2, b);
+      {   // S <- e^{G_end} S + K^T U'; every MMA that read the old S^T completed before D2 did
         const float eend = __expf(ge);
         float p[32];
-        umma::tmem_ld32(umma::tmem_addr(tm, w, 2 * NC + cw), p);
+        umma::tmem_ld32(umma::tmem_addr(tm, w, kColD2 + 32 * wg), p);
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
           S[j] = fmaf(eend, S[j], p[j]);
-          Ssm[((key >> 2) * NCP + cw + j) * 4 + (key & 3)] = tf32r(S[j]);
+          p[j] = tf32r(S[j]);
         }
+        umma::tmem_st32(umma::tmem_addr(tm, w, kColS + 32 * wg), p);
+        umma::tmem_st_wait();
       }
-      umma::fence_async_smem();
-      umma::fence_before_sync();
-      mbar_arrive(sReady);
-      if (!tokw) {   // Y(c) = e^G (Q S) + QKd U on lanes 64-127 of D1; overlaps D1 of the next chunk
-        wait(d3, b);
-        umma::fence_after_sync();
-        float p[32];
-        umma::tmem_ld32(umma::tmem_addr(tm, w, b * NC + cw), p);
-        const int row = c * kChunk + tk;
-        if (row < R) {
-          float* dst = P.yraw + (size_t)row * VW + h * 128 + col0 + cw;
+      warp_arrive(sReady);                                 // S^T is current
+      warp_wait(d3, b);
+      {   // Y^T of tokens 16 wg .. +15: a warp stores 32 consecutive columns of one row
+        float p[16];
+        umma::tmem_ld16(umma::tmem_addr(tm, w, kColD1 + 64 + 16 * wg), p);
+        float* dst = P.yraw + (size_t)(c * kChunk + 16 * wg) * VW + h * 128 + v;
 #pragma unroll
-          for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(dst + j) = make_float4(p[j], p[j + 1], p[j + 2], p[j + 3]);
-        }
-        umma::fence_before_sync();
+        for (int j = 0; j < 16; ++j)
+          if (c * kChunk + 16 * wg + j < R) dst[(size_t)j * VW] = p[j];
       }
+      warp_arrive(yDone);                                  // the readout half of D1 may be overwritten
     }
 #pragma unroll
-    for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(st + j) = make_float4(S[j], S[j + 1], S[j + 2], S[j + 3]);
+    for (int j = 0; j < 32; ++j) st[j * 128] = S[j];
   }
   umma::fence_before_sync();
   __syncthreads();
-  if (w == kIssuer) umma::tmem_dealloc(tm, kTmemCols);
+  if (w == kIssuer) umma::tmem_dealloc(tm, 512);
 }
 
 cr_status gdn_chunk_scan_tc_launch(const cr_geometry* g, const GdnPrefillParams& P, const ChunkWs& ws, cudaStream_t stream) {
   static bool configured = false;
   if (!configured) {
-    CR_CUDA(cudaFuncSetAttribute(gdn_chunk_scan_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TcSmem::kBytes));
+    CR_CUDA(cudaFuncSetAttribute(gdn_chunk_scan_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kScanSmem));
     configured = true;
   }
-  gdn_chunk_scan_tc_kernel<<<g->gdn_vheads * (128 / kNC), 128 * kWG + 32, TcSmem::kBytes, stream>>>(P, ws);
+  gdn_chunk_scan_tc_kernel<<<g->gdn_vheads, kScanThreads, kScanSmem, stream>>>(P, ws);
   CR_LAUNCH_CHECK("gdn_chunk_scan_tc_kernel");
   return CR_OK;
 }
