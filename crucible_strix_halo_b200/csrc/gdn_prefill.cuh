@@ -4,9 +4,10 @@
 
 namespace cr {
 
-// Rows per internal part: 37 chunks x 16 key heads = 592 local CTAs = two full waves of 2 CTAs on 148 SMs, and the
-// part's intermediates (about 65 KB per row) stay within the 126 MB L2.
-constexpr int kGdnPartRows = 37 * 64;
+// Rows per internal part: 148 chunks.  The scan pays a fixed cost per launch (state load and store, pipeline
+// fill, about 40 us measured), so parts are long; 148 chunks x 16 key heads = 2368 local CTAs = eight full waves
+// of 2 CTAs on 148 SMs, and the part's intermediates (about 72 KB per row) take 0.7 GB.
+constexpr int kGdnPartRows = 148 * 64;
 
 struct GdnPrefillParams {
   cr_gdn_args a;

@@ -40,36 +40,57 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count) : "memory");
 }
 __device__ __forceinline__ void mbar_fence_init() { asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory"); }
-// One poll: true once the phase with the given parity has completed.  A thread whose phase is still pending
-// may be suspended by the hardware for up to `suspend_ns` and is woken when the phase completes, so pollers
-// do not keep re-issuing the instruction.
-__device__ __forceinline__ bool mbar_try(uint32_t addr, uint32_t parity, uint32_t suspend_ns = 20000u) {
+// One poll: true once the phase with the given parity has completed (the hardware may suspend the thread for
+// a short, system-dependent time while the phase is pending).
+__device__ __forceinline__ bool mbar_try(uint32_t addr, uint32_t parity) {
   uint32_t done;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}\n"
       : "=r"(done)
-      : "r"(addr), "r"(parity), "r"(suspend_ns)
+      : "r"(addr), "r"(parity)
       : "memory");
   return done != 0;
+}
+// The same poll without acquire semantics.  An acquiring wait (and a releasing arrive) orders the thread's
+// other memory accesses around it, which in practice means that it does not return while the thread's own
+// global loads or stores are still in flight; a thread that only exchanges tensor-memory data (ordered by
+// tcgen05.wait and tcgen05.fence) and wants its prefetches to stay in flight uses the relaxed forms.
+__device__ __forceinline__ bool mbar_try_relaxed(uint32_t addr, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.relaxed.cta.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}\n"
+      : "=r"(done)
+      : "r"(addr), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+__device__ __forceinline__ void mbar_arrive_relaxed(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.relaxed.cta.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
 }
 // Waits for the phase with the given parity; gives up after `limit` polls and returns false.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit = 1u << 22) {
   const uint32_t addr = smem_u32(bar);
   for (uint32_t i = 0; i < limit; ++i)
-    if (mbar_try(addr, parity, 1000u)) return true;
+    if (mbar_try(addr, parity)) return true;
   return false;
 }
 // Waits with a bound in time: gives up after max_ns nanoseconds (or as soon as *abort is set by another
 // thread that gave up) and returns false.  The clock is read only when the first poll fails.
+template <bool RELAXED = false>
 __device__ __forceinline__ bool mbar_wait_timed(uint64_t* bar, uint32_t parity, const volatile int* abort, uint64_t max_ns = 2000000000ull) {
   const uint32_t addr = smem_u32(bar);
-  if (mbar_try(addr, parity)) return true;
+  auto poll = [&]() { return RELAXED ? mbar_try_relaxed(addr, parity) : mbar_try(addr, parity); };
+  if (poll()) return true;
   uint64_t t0;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
   for (;;) {
-    if (mbar_try(addr, parity)) return true;
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i)   // the clock and the abort flag are slow to read: look at them rarely
+      if (poll()) return true;
     uint64_t t1;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
     if (t1 - t0 > max_ns || (abort && *abort)) return false;
@@ -149,6 +170,10 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(smem_u32(dst)),
                "l"(src), "r"(bytes), "r"(smem_u32(bar))
                : "memory");
+}
+// Asks the copy engine to bring [src, src + bytes) into L2 (16-byte aligned, multiple of 16); nothing is signalled.
+__device__ __forceinline__ void bulk_prefetch_l2(const void* src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(src), "r"(bytes) : "memory");
 }
 // K-major operand with padded planes: float[K/4][plane_units][4], rows < plane_units.
 __device__ __forceinline__ uint64_t desc_kmajor_padded(const float* base, int plane_units, int k0) {
