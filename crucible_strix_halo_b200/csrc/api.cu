@@ -46,6 +46,8 @@ static void mark(const char* name) {
   g_marks.push_back({ev, name});
 }
 
+bool profiling() { return g_profile.load(std::memory_order_relaxed) != 0; }
+
 void count_launch(const char* name) {
   g_launches.fetch_add(1ull, std::memory_order_relaxed);
   if (g_profile.load(std::memory_order_relaxed)) mark(name);

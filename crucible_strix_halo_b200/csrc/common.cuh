@@ -19,6 +19,7 @@ constexpr int kMaxSpans = 32;                         // spans per launch (kerne
 void set_error(const char* fmt, ...);
 cr_status cuda_fail(cudaError_t e, const char* what);
 void count_launch(const char* name);
+bool profiling();                        // stage timing is on: launchers keep everything on one stream
 void use_stream(cudaStream_t stream);   // the stream the following launches go to (for stage timing)
 #define CR_CUDA(call)                                                          \
   do {                                                                         \

@@ -6,7 +6,7 @@ namespace cr {
 
 bool gdn_chunk_available() { return true; }
 
-static size_t chunk_layout(const cr_geometry* g, int rows, ChunkWs* ws, char* base) {
+size_t gdn_chunk_layout(const cr_geometry* g, int rows, ChunkWs* ws, char* base) {
   const size_t chunks = (size_t)(rows + kChunk - 1) / kChunk, Hv = g->gdn_vheads;
   size_t off = 0;
   auto take = [&](size_t bytes) { const size_t o = off; off += (bytes + 255) & ~(size_t)255; return o; };
@@ -22,13 +22,25 @@ static size_t chunk_layout(const cr_geometry* g, int rows, ChunkWs* ws, char* ba
   return off;
 }
 
-size_t gdn_chunk_workspace_bytes(const cr_geometry* g, int rows) { return chunk_layout(g, rows, nullptr, nullptr); }
+size_t gdn_chunk_workspace_bytes(const cr_geometry* g, int rows) { return gdn_chunk_layout(g, rows, nullptr, nullptr); }
 
 cr_status gdn_chunk_scan(const cr_geometry* g, const GdnPrefillParams& P, bool bf16_in, bool tcgen05, cudaStream_t stream) {
   ChunkWs ws;
-  chunk_layout(g, P.a.R, &ws, P.chunk_ws);
+  gdn_chunk_layout(g, P.a.R, &ws, P.chunk_ws);
   if (cr_status s = gdn_chunk_local_launch(g, P, ws, bf16_in, tcgen05, stream)) return s;
   return tcgen05 ? gdn_chunk_scan_tc_launch(g, P, ws, stream) : gdn_chunk_scan_launch(g, P, ws, stream);
+}
+
+cr_status gdn_chunk_local_only(const cr_geometry* g, const GdnPrefillParams& P, bool bf16_in, cudaStream_t stream) {
+  ChunkWs ws;
+  gdn_chunk_layout(g, P.a.R, &ws, P.chunk_ws);
+  return gdn_chunk_local_launch(g, P, ws, bf16_in, true, stream);
+}
+
+cr_status gdn_chunk_scan_only(const cr_geometry* g, const GdnPrefillParams& P, cudaStream_t stream) {
+  ChunkWs ws;
+  gdn_chunk_layout(g, P.a.R, &ws, P.chunk_ws);
+  return gdn_chunk_scan_tc_launch(g, P, ws, stream);
 }
 
 }  // namespace cr

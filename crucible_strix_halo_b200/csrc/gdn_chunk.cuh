@@ -81,6 +81,7 @@ cr_status gdn_chunk_local_launch(const cr_geometry* g, const GdnPrefillParams& P
                                  cudaStream_t stream);
 cr_status gdn_chunk_scan_tc_launch(const cr_geometry* g, const GdnPrefillParams& P, const ChunkWs& ws, cudaStream_t stream);
 int gdn_scan_status_read();
+size_t gdn_chunk_layout(const cr_geometry* g, int rows, ChunkWs* ws, char* base);
 cr_status gdn_chunk_scan_launch(const cr_geometry* g, const GdnPrefillParams& P, const ChunkWs& ws, cudaStream_t stream);
 
 }  // namespace cr

@@ -8,6 +8,7 @@
 //   gdn_gate   y * rsqrt(mean y^2 + eps) * gamma * sigmoid(z), output transform
 //   gdn_ring   last 16 raw rows -> hist ring (GdnPrefillHistoryKernel, prefill_gdn.h:274-282)
 #include "common.cuh"
+#include <mutex>
 #include "gdn_prefill.cuh"
 
 namespace cr {
@@ -224,11 +225,42 @@ size_t gdn_workspace_layout(const cr_geometry* g, int rows, GdnPrefillParams* P,
   return off;
 }
 
+// Internal streams and events of the part pipeline, one set per device, created on first use.  Calls on one
+// device are serialised while they enqueue (the events are shared).
+struct PipeStreams {
+  cudaStream_t hi = nullptr, lo = nullptr;
+  cudaEvent_t fork = nullptr, local_done[2] = {nullptr, nullptr}, part_done[2] = {nullptr, nullptr};
+  std::mutex mu;
+};
+static PipeStreams* pipe_streams() {
+  static std::mutex mu;
+  static PipeStreams* per_dev[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!per_dev[dev]) {
+    PipeStreams* ps = new PipeStreams();
+    int lo_pri = 0, hi_pri = 0;
+    bool ok = cudaDeviceGetStreamPriorityRange(&lo_pri, &hi_pri) == cudaSuccess;
+    ok = ok && cudaStreamCreateWithPriority(&ps->hi, cudaStreamNonBlocking, hi_pri) == cudaSuccess;
+    ok = ok && cudaStreamCreateWithPriority(&ps->lo, cudaStreamNonBlocking, lo_pri) == cudaSuccess;
+    ok = ok && cudaEventCreateWithFlags(&ps->fork, cudaEventDisableTiming) == cudaSuccess;
+    for (int i = 0; i < 2 && ok; ++i) {
+      ok = ok && cudaEventCreateWithFlags(&ps->local_done[i], cudaEventDisableTiming) == cudaSuccess;
+      ok = ok && cudaEventCreateWithFlags(&ps->part_done[i], cudaEventDisableTiming) == cudaSuccess;
+    }
+    if (!ok) { delete ps; return nullptr; }
+    per_dev[dev] = ps;
+  }
+  return per_dev[dev];
+}
+
 }  // namespace cr
 
 extern "C" size_t cr_gdn_prefill_workspace_bytes(const cr_geometry* g, int rows) {
   if (!g || rows < 1) return 0;
-  return cr::gdn_workspace_layout(g, rows < cr::kGdnPartRows ? rows : cr::kGdnPartRows, nullptr, nullptr);
+  const size_t part = cr::gdn_workspace_layout(g, rows < cr::kGdnPartRows ? rows : cr::kGdnPartRows, nullptr, nullptr);
+  return rows > cr::kGdnPartRows ? 2 * part : part;   // a call of several parts works on two workspaces in turn
 }
 
 extern "C" int cr_gdn_algo_available(cr_gdn_algo algo) {
@@ -253,7 +285,8 @@ extern "C" cr_status cr_gdn_prefill(const cr_geometry* g, const cr_gdn_prefill_a
   CR_REQUIRE(fmt == CR_OUT_EXL3_WHT || a.pack_rows == 0, "cr_gdn_prefill: packed layout only with the EXL3 output");
   CR_REQUIRE(algo == CR_GDN_SERIAL_F32 || algo == CR_GDN_CHUNK_TC || algo == CR_GDN_CHUNK_MMA, "cr_gdn_prefill: unknown algorithm");
   const int part_rows = a.R < kGdnPartRows ? a.R : kGdnPartRows;
-  const size_t need = gdn_workspace_layout(g, part_rows, nullptr, nullptr);
+  const size_t part_bytes = gdn_workspace_layout(g, part_rows, nullptr, nullptr);
+  const size_t need = a.R > kGdnPartRows ? 2 * part_bytes : part_bytes;
   CR_REQUIRE(args->workspace && args->workspace_bytes >= need, "cr_gdn_prefill: workspace of %zu bytes needed, %zu given",
              need, args->workspace_bytes);
   CR_REQUIRE(((uintptr_t)args->workspace & 255) == 0, "cr_gdn_prefill: workspace must be 256-byte aligned");
@@ -262,9 +295,8 @@ extern "C" cr_status cr_gdn_prefill(const cr_geometry* g, const cr_gdn_prefill_a
   const size_t in_elt = bf ? 2 : 4, out_elt = fmt == CR_OUT_RAW_F32 ? 4 : 2;
   const size_t Cw = 2 * (size_t)g->gdn_kheads * 128 + (size_t)g->gdn_vheads * 128, VWs = (size_t)g->gdn_vheads * 128;
   GdnPrefillParams P;
-  // The call runs in parts of kGdnPartRows rows that reuse one workspace, so the intermediates of a part stay
-  // in L2 between the kernels that write and read them; the state carries from part to part.
-  for (int p0 = 0; p0 < a.R; p0 += kGdnPartRows) {
+  // The call runs in parts of kGdnPartRows rows; the state carries from part to part.
+  auto part_params = [&](int p0, int buf) {
     P.a = a;
     P.a.qkv = (const char*)a.qkv + (size_t)p0 * Cw * in_elt;
     P.a.z = (const char*)a.z + (size_t)p0 * VWs * in_elt;
@@ -276,20 +308,60 @@ extern "C" cr_status cr_gdn_prefill(const cr_geometry* g, const cr_gdn_prefill_a
     P.Hv = g->gdn_vheads; P.Hk = g->gdn_kheads; P.fmt = (int)fmt;
     P.tf32 = 0;
     P.halo_in = p0 > 0;
-    gdn_workspace_layout(g, part_rows, &P, (char*)args->workspace);
+    gdn_workspace_layout(g, part_rows, &P, (char*)args->workspace + (size_t)buf * part_bytes);
     if (args->raw_y) P.yraw = args->raw_y + (size_t)p0 * VWs;
-    if (algo == CR_GDN_SERIAL_F32) {
-      const dim3 pg((P.a.R + 15) / 16, g->gdn_kheads + g->gdn_vheads / 2 + 1);
-      if (bf) gdn_prep_kernel<true><<<pg, 256, 0, stream>>>(P); else gdn_prep_kernel<false><<<pg, 256, 0, stream>>>(P);
-      CR_LAUNCH_CHECK("gdn_prep_kernel");
-      gdn_scan_serial_kernel<<<g->gdn_vheads * 4, 256, 0, stream>>>(P);
-      CR_LAUNCH_CHECK("gdn_scan_serial_kernel");
-    } else {   // the chunked scan prepares its rows itself
-      if (cr_status s = gdn_chunk_scan(g, P, bf, algo == CR_GDN_CHUNK_TC, stream)) return s;
-    }
+  };
+  auto gate = [&](cudaStream_t st) -> cr_status {
     const unsigned gg = (unsigned)(((long long)P.a.R * g->gdn_vheads + 7) / 8);
-    if (bf) gdn_gate_kernel<true><<<gg, 256, 0, stream>>>(P); else gdn_gate_kernel<false><<<gg, 256, 0, stream>>>(P);
+    if (bf) gdn_gate_kernel<true><<<gg, 256, 0, st>>>(P); else gdn_gate_kernel<false><<<gg, 256, 0, st>>>(P);
     CR_LAUNCH_CHECK("gdn_gate_kernel");
+    return CR_OK;
+  };
+  if (algo == CR_GDN_CHUNK_TC && a.R > kGdnPartRows && !profiling()) {
+    // Pipeline over parts on two internal streams that fork from the caller's stream and join it again.  The
+    // scan of part p is enqueued before the local kernel of part p + 1 and on the stream of higher priority, so
+    // that its CTAs (one whole SM each) are placed while the SMs are empty; the local kernel then fills the rest.
+    PipeStreams* ps = pipe_streams();
+    CR_REQUIRE(ps, "cr_gdn_prefill: cannot create the internal streams");
+    std::lock_guard<std::mutex> lock(ps->mu);
+    CR_CUDA(cudaEventRecord(ps->fork, stream));
+    CR_CUDA(cudaStreamWaitEvent(ps->hi, ps->fork, 0));
+    CR_CUDA(cudaStreamWaitEvent(ps->lo, ps->fork, 0));
+    part_params(0, 0);
+    if (cr_status s = gdn_chunk_local_only(g, P, bf, ps->lo)) return s;
+    CR_CUDA(cudaEventRecord(ps->local_done[0], ps->lo));
+    int pi = 0;
+    for (int p0 = 0; p0 < a.R; p0 += kGdnPartRows, ++pi) {
+      const int buf = pi & 1;
+      part_params(p0, buf);
+      CR_CUDA(cudaStreamWaitEvent(ps->hi, ps->local_done[buf], 0));
+      if (cr_status s = gdn_chunk_scan_only(g, P, ps->hi)) return s;
+      if (cr_status s = gate(ps->hi)) return s;
+      CR_CUDA(cudaEventRecord(ps->part_done[buf], ps->hi));
+      if (p0 + kGdnPartRows < a.R) {   // local kernel of the next part, into the other workspace
+        if (pi >= 1) CR_CUDA(cudaStreamWaitEvent(ps->lo, ps->part_done[buf ^ 1], 0));   // its last reader has finished
+        part_params(p0 + kGdnPartRows, buf ^ 1);
+        if (cr_status s = gdn_chunk_local_only(g, P, bf, ps->lo)) return s;
+        CR_CUDA(cudaEventRecord(ps->local_done[buf ^ 1], ps->lo));
+      }
+    }
+    CR_CUDA(cudaStreamWaitEvent(stream, ps->part_done[(pi - 1) & 1], 0));
+    if (pi >= 2) CR_CUDA(cudaStreamWaitEvent(stream, ps->part_done[pi & 1], 0));
+  } else {
+    int pi = 0;
+    for (int p0 = 0; p0 < a.R; p0 += kGdnPartRows, ++pi) {
+      part_params(p0, a.R > kGdnPartRows ? (pi & 1) : 0);
+      if (algo == CR_GDN_SERIAL_F32) {
+        const dim3 pg((P.a.R + 15) / 16, g->gdn_kheads + g->gdn_vheads / 2 + 1);
+        if (bf) gdn_prep_kernel<true><<<pg, 256, 0, stream>>>(P); else gdn_prep_kernel<false><<<pg, 256, 0, stream>>>(P);
+        CR_LAUNCH_CHECK("gdn_prep_kernel");
+        gdn_scan_serial_kernel<<<g->gdn_vheads * 4, 256, 0, stream>>>(P);
+        CR_LAUNCH_CHECK("gdn_scan_serial_kernel");
+      } else {   // the chunked scan prepares its rows itself
+        if (cr_status s = gdn_chunk_scan(g, P, bf, algo == CR_GDN_CHUNK_TC, stream)) return s;
+      }
+      if (cr_status s = gate(stream)) return s;
+    }
   }
   P.a = a;
   const int C = 2 * g->gdn_kheads * 128 + g->gdn_vheads * 128;

@@ -4,10 +4,12 @@
 
 namespace cr {
 
-// Rows per internal part: 148 chunks.  The scan pays a fixed cost per launch (state load and store, pipeline
-// fill, about 40 us measured), so parts are long; 148 chunks x 16 key heads = 2368 local CTAs = eight full waves
-// of 2 CTAs on 148 SMs, and the part's intermediates (about 72 KB per row) take 0.7 GB.
-constexpr int kGdnPartRows = 148 * 64;
+// Rows per internal part: 74 chunks.  A long call runs as a pipeline over parts: the chunk-local kernel of part
+// p + 1 runs beside the scan of part p (the scan holds one SM per value head, the local kernel takes the rest), on
+// two workspaces used in turn.  The scan pays a fixed cost per launch (state load and store, pipeline fill, 15 to
+// 40 us measured), which argues for long parts; the first local kernel and the last scan have nothing to run
+// beside, which argues for short ones.  A part's intermediates take about 72 KB per row.
+constexpr int kGdnPartRows = 74 * 64;
 
 struct GdnPrefillParams {
   cr_gdn_args a;
@@ -25,5 +27,8 @@ struct GdnPrefillParams {
 bool gdn_chunk_available();
 size_t gdn_chunk_workspace_bytes(const cr_geometry* g, int rows);
 cr_status gdn_chunk_scan(const cr_geometry* g, const GdnPrefillParams& P, bool bf16_in, bool tcgen05, cudaStream_t stream);
+// The two halves of gdn_chunk_scan with the tcgen05 layouts, for callers that run them on different streams.
+cr_status gdn_chunk_local_only(const cr_geometry* g, const GdnPrefillParams& P, bool bf16_in, cudaStream_t stream);
+cr_status gdn_chunk_scan_only(const cr_geometry* g, const GdnPrefillParams& P, cudaStream_t stream);
 
 }  // namespace cr

@@ -200,3 +200,35 @@ def test_prefill_chunk_tc_full_geometry_against_serial_scan():
     _, st = ao.gdn_serial(q[:, h // 2], k[:, h // 2], v[:, h], glog[:, h], beta[:, h], np.zeros((128, 128)))
     assert rel_l2(s_c[h], st) < 1e-3
     assert rel_l2(s_s[h], st) < 1e-4
+
+
+def test_prefill_chunk_tc_pipelined_parts_match_serial_scan():
+    """One call longer than an internal part (4736 rows): the tensor-core path runs as a two-stream pipeline over
+    parts on two workspaces.  Its outputs and state agree with the serial fp32 scan of the same rows, and with the
+    same rows fed in calls short enough to stay single-part (which takes the one-stream path)."""
+    capi, layers, g, og, rng, wts, w = _setup(4, 2, 64, 21)
+    T = 2 * 4736 + 333                                    # three parts, the last one ragged
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    qkv = torch.randn(T, og.gdn_qkv_width, device="cuda", generator=gen).bfloat16()
+    z = torch.randn(T, og.gdn_value_width, device="cuda", generator=gen).bfloat16()
+    ab = torch.randn(T, 2 * 4, device="cuda", generator=gen).bfloat16()
+
+    def run(algo, piece):
+        ses = layers.GdnSession(g)
+        outs = []
+        for p0 in range(0, T, piece):
+            n = min(piece, T - p0)
+            plan = layers.GdnPrefillPlan(w, n, in_dtype=capi.IN_BF16)
+            outs.append(plan.run(ses, qkv[p0:p0 + n], z[p0:p0 + n], ab[p0:p0 + n], p0, algo).clone())
+        torch.cuda.synchronize()
+        return torch.cat(outs).cpu().numpy(), ses.state_view().cpu().numpy(), ses.hist.cpu().numpy()
+
+    o_pipe, s_pipe, h_pipe = run(capi.GDN_CHUNK_TC, T)
+    assert capi.lib.cr_device_status() == 0
+    o_single, s_single, h_single = run(capi.GDN_CHUNK_TC, 4736)
+    o_ser, s_ser, h_ser = run(capi.GDN_SERIAL_F32, T)
+    np.testing.assert_array_equal(o_pipe, o_single)       # same kernels on the same rows: bit-identical
+    np.testing.assert_array_equal(s_pipe, s_single)
+    np.testing.assert_array_equal(h_pipe, h_ser)
+    assert rel_l2(s_pipe, s_ser) < 1e-3
+    assert_close_attn(o_pipe, o_ser, max_abs=2e-2, cos=0.9995, what="pipelined chunk vs serial")
