@@ -129,10 +129,53 @@ class GdnPrefill32k:
 
     step_eager = step
 
+    PIECE = 4736                                            # rows per host piece: one internal part of the library
+
+    def _e2e_setup(self):
+        torch = self.torch
+        self.s_in, self.s_out = torch.cuda.Stream(), torch.cuda.Stream()
+        self.piece_plans = [self.layers.GdnPrefillPlan(self.w, self.PIECE, in_dtype=self.capi.IN_BF16, fmt=self.capi.OUT_RAW_BF16)
+                            for _ in range(2)]
+        n = (self.T + self.PIECE - 1) // self.PIECE
+        self.ev_in = [torch.cuda.Event() for _ in range(n)]
+        self.ev_c = [torch.cuda.Event() for _ in range(n)]
+        self.ev_out = [torch.cuda.Event() for _ in range(n)]
+
     def step_e2e(self):
-        self.qkv.copy_(self.h_qkv, non_blocking=True); self.z.copy_(self.h_z, non_blocking=True); self.ab_in.copy_(self.h_ab, non_blocking=True)
-        out = self.step()
-        self.h_out.copy_(out, non_blocking=True)
+        """Host buffers in, host buffer out, as a caller with a long prompt would drive the C ABI: the rows go to
+        the device in pieces on a copy stream, each piece is one cr_gdn_prefill call (the state carries), and its
+        output returns on a third stream, so the PCIe transfers in both directions overlap the kernels."""
+        torch = self.torch
+        if not hasattr(self, "s_in"):
+            self._e2e_setup()
+        cur = torch.cuda.current_stream()
+        self.ses.state.zero_()
+        self.s_in.wait_stream(cur)
+        self.s_out.wait_stream(cur)
+        for i, p0 in enumerate(range(0, self.T, self.PIECE)):
+            n = min(self.PIECE, self.T - p0)
+            sl = slice(p0, p0 + n)
+            with torch.cuda.stream(self.s_in):
+                self.qkv[sl].copy_(self.h_qkv[sl], non_blocking=True)
+                self.z[sl].copy_(self.h_z[sl], non_blocking=True)
+                self.ab_in[sl].copy_(self.h_ab[sl], non_blocking=True)
+                self.ev_in[i].record()
+            cur.wait_event(self.ev_in[i])
+            if i >= 2:
+                cur.wait_event(self.ev_out[i - 2])             # the output buffer of this plan has been read back
+            plan = self.piece_plans[i & 1]
+            if n == self.PIECE:
+                out = plan.run(self.ses, self.qkv[sl], self.z[sl], self.ab_in[sl], p0, self.algo)
+            else:
+                if not hasattr(self, "tail_plan"):
+                    self.tail_plan = self.layers.GdnPrefillPlan(self.w, n, in_dtype=self.capi.IN_BF16, fmt=self.capi.OUT_RAW_BF16)
+                out = self.tail_plan.run(self.ses, self.qkv[sl], self.z[sl], self.ab_in[sl], p0, self.algo)
+            self.ev_c[i].record()
+            with torch.cuda.stream(self.s_out):
+                self.s_out.wait_event(self.ev_c[i])
+                self.h_out[sl].copy_(out, non_blocking=True)
+                self.ev_out[i].record()
+        cur.wait_stream(self.s_out)
 
     def config(self):
         return {"workload": self.name, "seq_len": self.T, "gdn_heads": "16qk/32v x128", "chunk": 64, "sessions_per_gpu": 1,
