@@ -41,8 +41,9 @@ cr_status check_geometry(const cr_geometry* g);
 
 // ---- device math ---------------------------------------------------------------------------------
 __device__ __forceinline__ float round_h(float v) { return __half2float(__float2half_rn(v)); }
-__device__ __forceinline__ float sigmoidf_(float v) { return 1.f / (1.f + __expf(-v)); }
-__device__ __forceinline__ float siluf_(float v) { return v / (1.f + __expf(-v)); }
+// __fdividef: reciprocal + multiply (2 ulp), instead of the IEEE division sequence; the denominators lie in [1, inf].
+__device__ __forceinline__ float sigmoidf_(float v) { return __fdividef(1.f, 1.f + __expf(-v)); }
+__device__ __forceinline__ float siluf_(float v) { return __fdividef(v, 1.f + __expf(-v)); }
 __device__ __forceinline__ float bf16_bits_to_float(uint16_t u) { return __uint_as_float((uint32_t)u << 16); }
 
 // Round to tf32 (10-bit mantissa, nearest, ties away): the tensor-core unit ignores the low 13 bits of an

@@ -17,20 +17,23 @@ constexpr int kRawRows = 67;                               // 64 rows + 3 halo r
 constexpr int kStageBytes = kRawRows * 128 * 2;            // one 128-channel bf16 tile (or 64 fp32 channels)
 constexpr size_t kLocalSmem = (size_t)(64 * kLdK + 64 * kLdX + 64 * kLdM + 9 * 64 + 64 * 4 + 3 * 256) * sizeof(float) + kStageBytes + 256;
 
-// Stages rows row0-3 .. row0+63 of channels [ch0, ch0+CH) into dst[67][CH] (element type of the input).
-// Rows before the call come from the input itself (halo_in: a later part of one call), the ring, or zero.
+// Starts the copy of rows row0-3 .. row0+63 of channels [ch0, ch0+CH) into dst[67][CH] (element type of the input)
+// as one cp.async group; rows past the end of the call are zero-filled.  Rows before the call come from the input
+// itself (halo_in: a later part of one call), or, with plain stores, from the ring or zero.
 template <bool BF16, int CH>
-__device__ __forceinline__ void stage_raw(const GdnPrefillParams& P, int C, int row0, int ch0, void* dst) {
+__device__ __forceinline__ void stage_issue(const GdnPrefillParams& P, int C, int row0, int ch0, void* dst) {
   constexpr int EPV = BF16 ? 8 : 4;                        // elements per 16-byte piece
   constexpr int PPR = CH / EPV;                            // pieces per row
   const cr_gdn_args& a = P.a;
   for (int i = threadIdx.x; i < kRawRows * PPR; i += 256) {
     const int rr = i / PPR, pc = i % PPR, r = row0 - 3 + rr, ch = ch0 + pc * EPV;
-    uint4 v = make_uint4(0u, 0u, 0u, 0u);
-    if (r < a.R) {
-      if (r >= 0 || P.halo_in) {
-        v = *reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(a.qkv) + ((long long)r * C + ch) * (BF16 ? 2 : 4));
-      } else if (a.pos0 + r >= 0) {
+    uint4* d = reinterpret_cast<uint4*>(dst) + i;
+    if (r >= 0 || P.halo_in) {
+      const bool valid = r < a.R;
+      cp_async16(d, reinterpret_cast<const char*>(a.qkv) + (valid ? ((long long)r * C + ch) * (BF16 ? 2 : 4) : 0ll), valid);
+    } else {
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (a.pos0 + r >= 0) {
         const float* hs = a.hist + (size_t)((a.pos0 + r) & 15) * C + ch;
         if constexpr (BF16) {
           __nv_bfloat162 b[4];
@@ -41,9 +44,15 @@ __device__ __forceinline__ void stage_raw(const GdnPrefillParams& P, int C, int 
           v = *reinterpret_cast<const uint4*>(hs);
         }
       }
+      *d = v;
     }
-    reinterpret_cast<uint4*>(dst)[i] = v;
   }
+  cp_async_commit();
+}
+template <bool BF16, int CH>
+__device__ __forceinline__ void stage_raw(const GdnPrefillParams& P, int C, int row0, int ch0, void* dst) {
+  stage_issue<BF16, CH>(P, C, row0, ch0, dst);
+  cp_async_wait_all();
 }
 template <bool BF16>
 __device__ __forceinline__ float2 staged_pair(const void* buf, int CH, int rr, int ch) {
@@ -134,40 +143,58 @@ __global__ void __launch_bounds__(256, 2) gdn_chunk_local_kernel(GdnPrefillParam
   constexpr int CH = BF16 ? 128 : 64;   // channels per staging round
   constexpr int PAIRS = CH / 2, RSEG = 256 / PAIRS, RPT = 64 / RSEG;
 
-  // ---- 1. q and k of the key head
+  // ---- 1. q and k of the key head.  With bf16 inputs a whole 128-channel tile is one staging round: q goes to the
+  // staging tile and k to the (still unused) L tile, both in flight at once; the first v tile follows as soon as
+  // the staging tile is free, so its latency hides behind the Gram products.
+  char* RB2 = reinterpret_cast<char*>(LT);
+  if constexpr (BF16) {
+    stage_issue<true, 128>(P, C, r0, kh * 128, RB);
+    stage_issue<true, 128>(P, C, r0, KW + kh * 128, RB2);
+  }
   for (int part = 0; part < 2; ++part) {
     float* dst = part ? Ks : Qs;
     for (int round = 0; round < 128 / CH; ++round) {
-      __syncthreads();                  // staging tile free
-      stage_raw<BF16, CH>(P, C, r0, (part ? KW : 0) + kh * 128 + round * CH, RB);
-      __syncthreads();
+      const char* src = RB;
+      if constexpr (BF16) {
+        if (part == 0) cp_async_wait_but_one(); else cp_async_wait_all();
+        __syncthreads();
+        src = part ? RB2 : RB;
+      } else {
+        __syncthreads();                // staging tile free
+        stage_raw<BF16, CH>(P, C, r0, (part ? KW : 0) + kh * 128 + round * CH, RB);
+        __syncthreads();
+      }
       const int cp = t % PAIRS, seg = t / PAIRS, chl = 2 * cp, chg = (part ? KW : 0) + kh * 128 + round * CH + chl;
       const float4 w0 = *reinterpret_cast<const float4*>(a.conv + (size_t)chg * 4);
       const float4 w1 = *reinterpret_cast<const float4*>(a.conv + (size_t)(chg + 1) * 4);
       const int rb = seg * RPT;         // first chunk row of this thread; staged row index = chunk row + 3
-      float2 x0 = staged_pair<BF16>(RB, CH, rb, chl), x1 = staged_pair<BF16>(RB, CH, rb + 1, chl), x2 = staged_pair<BF16>(RB, CH, rb + 2, chl);
+      float2 x0 = staged_pair<BF16>(src, CH, rb, chl), x1 = staged_pair<BF16>(src, CH, rb + 1, chl), x2 = staged_pair<BF16>(src, CH, rb + 2, chl);
 #pragma unroll
       for (int i = 0; i < RPT; ++i) {
-        const float2 x3 = staged_pair<BF16>(RB, CH, rb + 3 + i, chl);
+        const float2 x3 = staged_pair<BF16>(src, CH, rb + 3 + i, chl);
         float c0 = w0.x * x0.x, c1 = w1.x * x0.y;
         c0 = fmaf(w0.y, x1.x, c0); c1 = fmaf(w1.y, x1.y, c1);
         c0 = fmaf(w0.z, x2.x, c0); c1 = fmaf(w1.z, x2.y, c1);
         c0 = fmaf(w0.w, x3.x, c0); c1 = fmaf(w1.w, x3.y, c1);
         const bool live = rb + i < valid;
-        const float v0 = live ? siluf_(c0) : 0.f, v1 = live ? siluf_(c1) : 0.f;
-        *reinterpret_cast<float2*>(dst + (rb + i) * kLdK + round * CH + chl) = make_float2(v0, v1);
-        const float s = warp_sum(v0 * v0 + v1 * v1);     // a warp covers 64 channels of one row
-        if (l == 0) red[(rb + i) * 4 + part * 2 + (BF16 ? (w & 1) : round)] = s;
+        *reinterpret_cast<float2*>(dst + (rb + i) * kLdK + round * CH + chl) = make_float2(live ? siluf_(c0) : 0.f, live ? siluf_(c1) : 0.f);
         x0 = x1; x1 = x2; x2 = x3;
       }
     }
   }
   __syncthreads();
-  for (int i = t; i < 64 * 32; i += 256) {   // normalise and round to tf32
+  if constexpr (BF16) stage_issue<true, 128>(P, C, r0, 2 * KW + kh * rep * 128, RB);   // v of the first value head
+  for (int i = t; i < 64 * 32; i += 256) {   // L2 norms (a warp holds one row), scale, round to tf32
     const int row = i >> 5, c4 = (i & 31) * 4;
-    const float sq = rsqrtf(red[row * 4] + red[row * 4 + 1] + kEps) * kInvSqrt128;
-    const float sk = rsqrtf(red[row * 4 + 2] + red[row * 4 + 3] + kEps);
     float4 q = *reinterpret_cast<float4*>(Qs + row * kLdK + c4), k = *reinterpret_cast<float4*>(Ks + row * kLdK + c4);
+    float sq = q.x * q.x + q.y * q.y + q.z * q.z + q.w * q.w, sk = k.x * k.x + k.y * k.y + k.z * k.z + k.w * k.w;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      sq += __shfl_xor_sync(0xffffffffu, sq, o);
+      sk += __shfl_xor_sync(0xffffffffu, sk, o);
+    }
+    sq = rsqrtf(sq + kEps) * kInvSqrt128;
+    sk = rsqrtf(sk + kEps);
     q = make_float4(tf32r(q.x * sq), tf32r(q.y * sq), tf32r(q.z * sq), tf32r(q.w * sq));
     k = make_float4(tf32r(k.x * sk), tf32r(k.y * sk), tf32r(k.z * sk), tf32r(k.w * sk));
     *reinterpret_cast<float4*>(Qs + row * kLdK + c4) = q;
@@ -267,9 +294,10 @@ __global__ void __launch_bounds__(256, 2) gdn_chunk_local_kernel(GdnPrefillParam
       const float e = ev[row];
       *reinterpret_cast<float4*>(Qs + row * kLdX + c4) = make_float4(tf32r(e * kv.x), tf32r(e * kv.y), tf32r(e * kv.z), tf32r(e * kv.w));
     }
-    // raw v rows of value head h, 128 channels per round with bf16 inputs, 64 with fp32 inputs
+    // raw v rows of value head h, 128 channels per round with bf16 inputs (already in flight), 64 with fp32 inputs
     constexpr int VCH = BF16 ? 128 : 64;
-    stage_raw<BF16, VCH>(P, C, r0, 2 * KW + h * 128, RB);
+    if constexpr (BF16) cp_async_wait_all();
+    else stage_raw<BF16, VCH>(P, C, r0, 2 * KW + h * 128, RB);
     __syncthreads();
     invert_unit_lower_64(LT, Ms);
     for (int i = t; i < 64 * 64; i += 256) {
@@ -321,6 +349,9 @@ __global__ void __launch_bounds__(256, 2) gdn_chunk_local_kernel(GdnPrefillParam
       }
     }
     __syncthreads();
+    if constexpr (BF16) {   // staging tile consumed: start the next value head's rows
+      if (vi + 1 < rep) stage_issue<true, 128>(P, C, r0, 2 * KW + (h + 1) * 128, RB);
+    }
     {   // Ut = T X  (stored fp32: it is added, not multiplied, in the scan)
       float acc[8][4];
 #pragma unroll
