@@ -15,7 +15,7 @@ namespace cr {
 
 constexpr int kRawRows = 67;                               // 64 rows + 3 halo rows
 constexpr int kStageBytes = kRawRows * 128 * 2;            // one 128-channel bf16 tile (or 64 fp32 channels)
-constexpr size_t kLocalSmem = (size_t)(64 * kLdK + 64 * kLdX + 64 * kLdM + 9 * 64 + 64 * 4 + 3 * 256) * sizeof(float) + kStageBytes + 256;
+constexpr size_t kLocalSmem = (size_t)(64 * kLdK + 64 * kLdX + 64 * kLdM + 15 * 64 + 3 * 256) * sizeof(float) + kStageBytes + 256;
 
 // Starts the copy of rows row0-3 .. row0+63 of channels [ch0, ch0+CH) into dst[67][CH] (element type of the input)
 // as one cp.async group; rows past the end of the call are zero-filled.  Rows before the call come from the input
@@ -90,32 +90,51 @@ __device__ __forceinline__ void invert_unit_lower_64(float* LT, float* Ms) {
   }
   __syncthreads();
   for (int a = 1; a < 4; ++a) {          // block row a: its L blocks are still untouched
-    for (int b = 0; b < a; ++b) {        // M_ab = sum_{c=b}^{a-1} L_ac T_cb
-      float m0 = 0.f, m1 = 0.f, m2 = 0.f, m3 = 0.f;
-      for (int cb = b; cb < a; ++cb) {
-        const float* Lr = LT + (16 * a + i) * kLdM + 16 * cb;
-        const float* Tc = LT + (16 * cb) * kLdM + 16 * b + j;
+    float macc[3] = {0.f, 0.f, 0.f};     // M_ab = sum_{c=b}^{a-1} L_ac T_cb for b = 0 .. a-1; L_ac[i][m] is read once
 #pragma unroll
-        for (int m = 0; m < 16; m += 4) {
-          m0 = fmaf(Lr[m], Tc[m * kLdM], m0);
-          m1 = fmaf(Lr[m + 1], Tc[(m + 1) * kLdM], m1);
-          m2 = fmaf(Lr[m + 2], Tc[(m + 2) * kLdM], m2);
-          m3 = fmaf(Lr[m + 3], Tc[(m + 3) * kLdM], m3);
+    for (int cb = 0; cb < 3; ++cb) {
+      if (cb < a) {
+        const float* Lr = LT + (16 * a + i) * kLdM + 16 * cb;
+#pragma unroll
+        for (int m4 = 0; m4 < 16; m4 += 4) {
+          const float4 lv = *reinterpret_cast<const float4*>(Lr + m4);
+          const float lm[4] = {lv.x, lv.y, lv.z, lv.w};
+#pragma unroll
+          for (int mm = 0; mm < 4; ++mm) {
+            const float* Tc = LT + (16 * cb + m4 + mm) * kLdM + j;
+#pragma unroll
+            for (int b = 0; b < 3; ++b)
+              if (b <= cb) macc[b] = fmaf(lm[mm], Tc[16 * b], macc[b]);
+          }
         }
       }
-      Ms[b * 256 + t] = (m0 + m1) + (m2 + m3);
     }
-    __syncthreads();
-    for (int b = 0; b < a; ++b) {        // T_ab = -T_aa M_ab  (T_aa lower triangular: m <= i)
-      const float* Tr = LT + (16 * a + i) * kLdM + 16 * a;
-      const float* Mc = Ms + b * 256 + j;
-      float m0 = 0.f, m1 = 0.f;
 #pragma unroll
-      for (int m = 0; m < 16; m += 2) {
-        m0 = fmaf(m <= i ? Tr[m] : 0.f, Mc[m * 16], m0);
-        m1 = fmaf(m + 1 <= i ? Tr[m + 1] : 0.f, Mc[(m + 1) * 16], m1);
+    for (int b = 0; b < 3; ++b)
+      if (b < a) Ms[b * 256 + t] = macc[b];
+    __syncthreads();
+    {                                    // T_ab = -T_aa M_ab  (T_aa lower triangular: m <= i); the T_aa row is read once
+      const float* Tr = LT + (16 * a + i) * kLdM + 16 * a;
+      float tr[16];
+#pragma unroll
+      for (int m4 = 0; m4 < 16; m4 += 4) {
+        const float4 v = *reinterpret_cast<const float4*>(Tr + m4);
+        tr[m4] = m4 <= i ? v.x : 0.f; tr[m4 + 1] = m4 + 1 <= i ? v.y : 0.f;
+        tr[m4 + 2] = m4 + 2 <= i ? v.z : 0.f; tr[m4 + 3] = m4 + 3 <= i ? v.w : 0.f;
       }
-      LT[(16 * a + i) * kLdM + 16 * b + j] = -(m0 + m1);
+#pragma unroll
+      for (int b = 0; b < 3; ++b) {
+        if (b < a) {
+          const float* Mc = Ms + b * 256 + j;
+          float m0 = 0.f, m1 = 0.f;
+#pragma unroll
+          for (int m = 0; m < 16; m += 2) {
+            m0 = fmaf(tr[m], Mc[m * 16], m0);
+            m1 = fmaf(tr[m + 1], Mc[(m + 1) * 16], m1);
+          }
+          LT[(16 * a + i) * kLdM + 16 * b + j] = -(m0 + m1);
+        }
+      }
     }
     __syncthreads();
   }
@@ -133,8 +152,9 @@ __global__ void __launch_bounds__(256, 2) gdn_chunk_local_kernel(GdnPrefillParam
   float* Gs = LT + 64 * kLdM;           // [3][64] cumulative log decay per value head
   float* bs = Gs + 3 * 64;              // [3][64] beta
   float* es = bs + 3 * 64;              // [3][64] beta * exp(G)
-  float* red = es + 3 * 64;             // [64][4] partial sums of squares: q halves, k halves
-  float* Ms = red + 64 * 4;             // [3][256] scratch of the blocked inverse
+  float* egs = es + 3 * 64;             // [3][64] exp(G)
+  float* scs = egs + 3 * 64;            // [3][64] exp(G_end - G)
+  float* Ms = scs + 3 * 64;             // [3][256] scratch of the blocked inverse
   const cr_gdn_args& a = P.a;
   const int c = blockIdx.x, kh = blockIdx.y;
   const int t = threadIdx.x, w = t >> 5, l = t & 31, g = l >> 2, tq = l & 3;
@@ -227,7 +247,10 @@ __global__ void __launch_bounds__(256, 2) gdn_chunk_local_kernel(GdnPrefillParam
     const float G1 = s, G0 = s - gv[1];
     float* Gw = Gs + w * 64; float* bw = bs + w * 64; float* ew = es + w * 64;
     Gw[2 * l] = G0; Gw[2 * l + 1] = G1; bw[2 * l] = bv[0]; bw[2 * l + 1] = bv[1];
-    ew[2 * l] = bv[0] * __expf(G0); ew[2 * l + 1] = bv[1] * __expf(G1);
+    const float e0 = __expf(G0), e1 = __expf(G1), Gend = __shfl_sync(0xffffffffu, G1, 31);
+    ew[2 * l] = bv[0] * e0; ew[2 * l + 1] = bv[1] * e1;
+    egs[w * 64 + 2 * l] = e0; egs[w * 64 + 2 * l + 1] = e1;
+    scs[w * 64 + 2 * l] = __expf(Gend - G0); scs[w * 64 + 2 * l + 1] = __expf(Gend - G1);
     float* Gg = ws.G + ((size_t)h * ws.chunks + c) * 64;
     Gg[2 * l] = G0; Gg[2 * l + 1] = G1;
   }
@@ -238,20 +261,18 @@ __global__ void __launch_bounds__(256, 2) gdn_chunk_local_kernel(GdnPrefillParam
     // Qt = e^G Q, K-major over keys
     for (int vi = 0; vi < rep; ++vi) {
       float* kt = ws.Kt + ((size_t)(kh * rep + vi) * ws.chunks + c) * 8192;
-      const float* Gv = Gs + vi * 64;
-      const float Ge = Gv[63];
       for (int i = t; i < 16 * 128; i += 256) {
         const int key = i & 127, tc = i >> 7;
-        const float4 gq = *reinterpret_cast<const float4*>(Gv + 4 * tc);
+        const float4 sc = *reinterpret_cast<const float4*>(scs + vi * 64 + 4 * tc);
         *reinterpret_cast<float4*>(kt + (size_t)i * 4) =
-            make_float4(tf32r(__expf(Ge - gq.x) * Ks[(4 * tc) * kLdK + key]), tf32r(__expf(Ge - gq.y) * Ks[(4 * tc + 1) * kLdK + key]),
-                        tf32r(__expf(Ge - gq.z) * Ks[(4 * tc + 2) * kLdK + key]), tf32r(__expf(Ge - gq.w) * Ks[(4 * tc + 3) * kLdK + key]));
+            make_float4(tf32r(sc.x * Ks[(4 * tc) * kLdK + key]), tf32r(sc.y * Ks[(4 * tc + 1) * kLdK + key]),
+                        tf32r(sc.z * Ks[(4 * tc + 2) * kLdK + key]), tf32r(sc.w * Ks[(4 * tc + 3) * kLdK + key]));
       }
       float* qt = ws.WQ + ((size_t)(kh * rep + vi) * ws.chunks + c) * 16384;
       for (int i = t; i < 32 * 64; i += 256) {
         const int row = i & 63, kc = i >> 6;
         const float4 q = *reinterpret_cast<const float4*>(Qs + row * kLdK + kc * 4);
-        const float e = __expf(Gs[vi * 64 + row]);
+        const float e = egs[vi * 64 + row];
         *reinterpret_cast<float4*>(qt + (size_t)(kc * 128 + 64 + row) * 4) = make_float4(tf32r(e * q.x), tf32r(e * q.y), tf32r(e * q.z), tf32r(e * q.w));
       }
     }
