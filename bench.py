@@ -129,7 +129,7 @@ class GdnPrefill32k:
 
     step_eager = step
 
-    PIECE = 4736                                            # rows per host piece: one internal part of the library
+    PIECE = 4736                                            # rows per host piece (each piece is a single-part call)
 
     def _e2e_setup(self):
         torch = self.torch

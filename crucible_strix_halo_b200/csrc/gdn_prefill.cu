@@ -225,10 +225,20 @@ size_t gdn_workspace_layout(const cr_geometry* g, int rows, GdnPrefillParams* P,
   return off;
 }
 
+int gdn_part_rows() {
+  static const int rows = [] {
+    const char* e = getenv("CR_GDN_PART_CHUNKS");
+    const int c = e ? atoi(e) : 0;
+    return c >= 1 && c <= 4096 ? c * 64 : kGdnPartRowsDefault;
+  }();
+  return rows;
+}
+
 // Internal streams and events of the part pipeline, one set per device, created on first use.  Calls on one
 // device are serialised while they enqueue (the events are shared).
 struct PipeStreams {
-  cudaStream_t hi = nullptr, lo = nullptr;
+  cudaStream_t hi = nullptr, lo = nullptr, mid = nullptr;
+  cudaEvent_t scan_done[2] = {nullptr, nullptr};
   cudaEvent_t fork = nullptr, local_done[2] = {nullptr, nullptr}, part_done[2] = {nullptr, nullptr};
   std::mutex mu;
 };
@@ -244,10 +254,12 @@ static PipeStreams* pipe_streams() {
     bool ok = cudaDeviceGetStreamPriorityRange(&lo_pri, &hi_pri) == cudaSuccess;
     ok = ok && cudaStreamCreateWithPriority(&ps->hi, cudaStreamNonBlocking, hi_pri) == cudaSuccess;
     ok = ok && cudaStreamCreateWithPriority(&ps->lo, cudaStreamNonBlocking, lo_pri) == cudaSuccess;
+    ok = ok && cudaStreamCreateWithPriority(&ps->mid, cudaStreamNonBlocking, lo_pri) == cudaSuccess;
     ok = ok && cudaEventCreateWithFlags(&ps->fork, cudaEventDisableTiming) == cudaSuccess;
     for (int i = 0; i < 2 && ok; ++i) {
       ok = ok && cudaEventCreateWithFlags(&ps->local_done[i], cudaEventDisableTiming) == cudaSuccess;
       ok = ok && cudaEventCreateWithFlags(&ps->part_done[i], cudaEventDisableTiming) == cudaSuccess;
+      ok = ok && cudaEventCreateWithFlags(&ps->scan_done[i], cudaEventDisableTiming) == cudaSuccess;
     }
     if (!ok) { delete ps; return nullptr; }
     per_dev[dev] = ps;
@@ -259,8 +271,8 @@ static PipeStreams* pipe_streams() {
 
 extern "C" size_t cr_gdn_prefill_workspace_bytes(const cr_geometry* g, int rows) {
   if (!g || rows < 1) return 0;
-  const size_t part = cr::gdn_workspace_layout(g, rows < cr::kGdnPartRows ? rows : cr::kGdnPartRows, nullptr, nullptr);
-  return rows > cr::kGdnPartRows ? 2 * part : part;   // a call of several parts works on two workspaces in turn
+  const size_t part = cr::gdn_workspace_layout(g, rows < cr::gdn_part_rows() ? rows : cr::gdn_part_rows(), nullptr, nullptr);
+  return rows > cr::gdn_part_rows() ? 2 * part : part;   // a call of several parts works on two workspaces in turn
 }
 
 extern "C" int cr_gdn_algo_available(cr_gdn_algo algo) {
@@ -284,9 +296,9 @@ extern "C" cr_status cr_gdn_prefill(const cr_geometry* g, const cr_gdn_prefill_a
   CR_REQUIRE(fmt != CR_OUT_EXL3_WHT || a.suh_out, "cr_gdn_prefill: suh_out needed for the EXL3 output");
   CR_REQUIRE(fmt == CR_OUT_EXL3_WHT || a.pack_rows == 0, "cr_gdn_prefill: packed layout only with the EXL3 output");
   CR_REQUIRE(algo == CR_GDN_SERIAL_F32 || algo == CR_GDN_CHUNK_TC || algo == CR_GDN_CHUNK_MMA, "cr_gdn_prefill: unknown algorithm");
-  const int part_rows = a.R < kGdnPartRows ? a.R : kGdnPartRows;
+  const int part_rows = a.R < gdn_part_rows() ? a.R : gdn_part_rows();
   const size_t part_bytes = gdn_workspace_layout(g, part_rows, nullptr, nullptr);
-  const size_t need = a.R > kGdnPartRows ? 2 * part_bytes : part_bytes;
+  const size_t need = a.R > gdn_part_rows() ? 2 * part_bytes : part_bytes;
   CR_REQUIRE(args->workspace && args->workspace_bytes >= need, "cr_gdn_prefill: workspace of %zu bytes needed, %zu given",
              need, args->workspace_bytes);
   CR_REQUIRE(((uintptr_t)args->workspace & 255) == 0, "cr_gdn_prefill: workspace must be 256-byte aligned");
@@ -295,14 +307,14 @@ extern "C" cr_status cr_gdn_prefill(const cr_geometry* g, const cr_gdn_prefill_a
   const size_t in_elt = bf ? 2 : 4, out_elt = fmt == CR_OUT_RAW_F32 ? 4 : 2;
   const size_t Cw = 2 * (size_t)g->gdn_kheads * 128 + (size_t)g->gdn_vheads * 128, VWs = (size_t)g->gdn_vheads * 128;
   GdnPrefillParams P;
-  // The call runs in parts of kGdnPartRows rows; the state carries from part to part.
+  // The call runs in parts of gdn_part_rows() rows; the state carries from part to part.
   auto part_params = [&](int p0, int buf) {
     P.a = a;
     P.a.qkv = (const char*)a.qkv + (size_t)p0 * Cw * in_elt;
     P.a.z = (const char*)a.z + (size_t)p0 * VWs * in_elt;
     if (a.pack_rows) P.a.pack_off = a.pack_off + p0; else P.a.out = (char*)a.out + (size_t)p0 * VWs * out_elt;
     P.a.pos0 = a.pos0 + p0;
-    P.a.R = a.R - p0 < kGdnPartRows ? a.R - p0 : kGdnPartRows;
+    P.a.R = a.R - p0 < gdn_part_rows() ? a.R - p0 : gdn_part_rows();
     P.a.commit = P.a.R;
     P.ab_logits = (const char*)args->ab_logits + (size_t)p0 * 2 * g->gdn_vheads * in_elt;
     P.Hv = g->gdn_vheads; P.Hk = g->gdn_kheads; P.fmt = (int)fmt;
@@ -317,7 +329,7 @@ extern "C" cr_status cr_gdn_prefill(const cr_geometry* g, const cr_gdn_prefill_a
     CR_LAUNCH_CHECK("gdn_gate_kernel");
     return CR_OK;
   };
-  if (algo == CR_GDN_CHUNK_TC && a.R > kGdnPartRows && !profiling()) {
+  if (algo == CR_GDN_CHUNK_TC && a.R > gdn_part_rows() && !profiling()) {
     // Pipeline over parts on two internal streams that fork from the caller's stream and join it again.  The
     // scan of part p is enqueued before the local kernel of part p + 1 and on the stream of higher priority, so
     // that its CTAs (one whole SM each) are placed while the SMs are empty; the local kernel then fills the rest.
@@ -327,30 +339,34 @@ extern "C" cr_status cr_gdn_prefill(const cr_geometry* g, const cr_gdn_prefill_a
     CR_CUDA(cudaEventRecord(ps->fork, stream));
     CR_CUDA(cudaStreamWaitEvent(ps->hi, ps->fork, 0));
     CR_CUDA(cudaStreamWaitEvent(ps->lo, ps->fork, 0));
+    CR_CUDA(cudaStreamWaitEvent(ps->mid, ps->fork, 0));
     part_params(0, 0);
     if (cr_status s = gdn_chunk_local_only(g, P, bf, ps->lo)) return s;
     CR_CUDA(cudaEventRecord(ps->local_done[0], ps->lo));
     int pi = 0;
-    for (int p0 = 0; p0 < a.R; p0 += kGdnPartRows, ++pi) {
+    for (int p0 = 0; p0 < a.R; p0 += gdn_part_rows(), ++pi) {
       const int buf = pi & 1;
       part_params(p0, buf);
       CR_CUDA(cudaStreamWaitEvent(ps->hi, ps->local_done[buf], 0));
       if (cr_status s = gdn_chunk_scan_only(g, P, ps->hi)) return s;
-      if (cr_status s = gate(ps->hi)) return s;
-      CR_CUDA(cudaEventRecord(ps->part_done[buf], ps->hi));
-      if (p0 + kGdnPartRows < a.R) {   // local kernel of the next part, into the other workspace
+      // the gated readout runs on a third stream, so the next scan does not queue behind it
+      CR_CUDA(cudaEventRecord(ps->scan_done[buf], ps->hi));
+      CR_CUDA(cudaStreamWaitEvent(ps->mid, ps->scan_done[buf], 0));
+      if (cr_status s = gate(ps->mid)) return s;
+      CR_CUDA(cudaEventRecord(ps->part_done[buf], ps->mid));
+      if (p0 + gdn_part_rows() < a.R) {   // local kernel of the next part, into the other workspace
         if (pi >= 1) CR_CUDA(cudaStreamWaitEvent(ps->lo, ps->part_done[buf ^ 1], 0));   // its last reader has finished
-        part_params(p0 + kGdnPartRows, buf ^ 1);
+        part_params(p0 + gdn_part_rows(), buf ^ 1);
         if (cr_status s = gdn_chunk_local_only(g, P, bf, ps->lo)) return s;
         CR_CUDA(cudaEventRecord(ps->local_done[buf ^ 1], ps->lo));
       }
     }
-    CR_CUDA(cudaStreamWaitEvent(stream, ps->part_done[(pi - 1) & 1], 0));
-    if (pi >= 2) CR_CUDA(cudaStreamWaitEvent(stream, ps->part_done[pi & 1], 0));
+    CR_CUDA(cudaStreamWaitEvent(stream, ps->part_done[(pi - 1) & 1], 0));   // the last gate: everything before it on
+    CR_CUDA(cudaStreamWaitEvent(stream, ps->scan_done[(pi - 1) & 1], 0));   // its stream, and the last scan, are done
   } else {
     int pi = 0;
-    for (int p0 = 0; p0 < a.R; p0 += kGdnPartRows, ++pi) {
-      part_params(p0, a.R > kGdnPartRows ? (pi & 1) : 0);
+    for (int p0 = 0; p0 < a.R; p0 += gdn_part_rows(), ++pi) {
+      part_params(p0, a.R > gdn_part_rows() ? (pi & 1) : 0);
       if (algo == CR_GDN_SERIAL_F32) {
         const dim3 pg((P.a.R + 15) / 16, g->gdn_kheads + g->gdn_vheads / 2 + 1);
         if (bf) gdn_prep_kernel<true><<<pg, 256, 0, stream>>>(P); else gdn_prep_kernel<false><<<pg, 256, 0, stream>>>(P);

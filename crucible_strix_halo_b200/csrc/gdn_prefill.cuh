@@ -4,12 +4,13 @@
 
 namespace cr {
 
-// Rows per internal part: 74 chunks.  A long call runs as a pipeline over parts: the chunk-local kernel of part
+// Rows per internal part: 111 chunks.  A long call runs as a pipeline over parts: the chunk-local kernel of part
 // p + 1 runs beside the scan of part p (the scan holds one SM per value head, the local kernel takes the rest), on
 // two workspaces used in turn.  The scan pays a fixed cost per launch (state load and store, pipeline fill, 15 to
 // 40 us measured), which argues for long parts; the first local kernel and the last scan have nothing to run
 // beside, which argues for short ones.  A part's intermediates take about 72 KB per row.
-constexpr int kGdnPartRows = 74 * 64;
+constexpr int kGdnPartRowsDefault = 111 * 64;
+int gdn_part_rows();   // kGdnPartRowsDefault, or 64 x CR_GDN_PART_CHUNKS from the environment (read once; for tuning)
 
 struct GdnPrefillParams {
   cr_gdn_args a;

@@ -203,11 +203,11 @@ def test_prefill_chunk_tc_full_geometry_against_serial_scan():
 
 
 def test_prefill_chunk_tc_pipelined_parts_match_serial_scan():
-    """One call longer than an internal part (4736 rows): the tensor-core path runs as a two-stream pipeline over
+    """One call longer than an internal part (7104 rows): the tensor-core path runs as a two-stream pipeline over
     parts on two workspaces.  Its outputs and state agree with the serial fp32 scan of the same rows, and with the
     same rows fed in calls short enough to stay single-part (which takes the one-stream path)."""
     capi, layers, g, og, rng, wts, w = _setup(4, 2, 64, 21)
-    T = 2 * 4736 + 333                                    # three parts, the last one ragged
+    T = 2 * 7104 + 333                                    # three parts, the last one ragged
     gen = torch.Generator(device="cuda").manual_seed(3)
     qkv = torch.randn(T, og.gdn_qkv_width, device="cuda", generator=gen).bfloat16()
     z = torch.randn(T, og.gdn_value_width, device="cuda", generator=gen).bfloat16()
@@ -225,7 +225,7 @@ def test_prefill_chunk_tc_pipelined_parts_match_serial_scan():
 
     o_pipe, s_pipe, h_pipe = run(capi.GDN_CHUNK_TC, T)
     assert capi.lib.cr_device_status() == 0
-    o_single, s_single, h_single = run(capi.GDN_CHUNK_TC, 4736)
+    o_single, s_single, h_single = run(capi.GDN_CHUNK_TC, 7104)
     o_ser, s_ser, h_ser = run(capi.GDN_SERIAL_F32, T)
     np.testing.assert_array_equal(o_pipe, o_single)       # same kernels on the same rows: bit-identical
     np.testing.assert_array_equal(s_pipe, s_single)
