@@ -27,6 +27,15 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 GDN_BYTES_PER_TOKEN = (8192 + 4096) * 2 + 4096 * 2 + 2 * 32 * 4      # bf16 qkv + z in, bf16 out, fp32 a/b logits
+# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of one launch from the ncu captures summarised under
+# profiles/, per unit of work (GDN: per token of a 7,104-token part; decode: per step of 4 sessions), scaled to
+# the launch by the units it processes (traffic grows in proportion to them).
+NCU_TRAFFIC = {
+    "gdn_chunk_scan_tc_kernel": ("token", (526.546e6 + 102.534e6) / 7104), "gdn_chunk_local_kernel": ("token", (120.665e6 + 465.678e6) / 7104),
+    "gdn_gate_kernel": ("token", (174.600e6 + 39.643e6) / 7104),
+    "qsa_score_kernel": ("step", 134.26e6 + 4.22e6), "qsa_attn_split_kernel": ("step", 16.88e6), "qsa_topk_cluster_kernel": ("step", 1.07e6),
+    "qsa_merge_kernel": ("step", 2.20e6), "qsa_prep_kernel": ("step", 0.13e6), "gdn_step_kernel": ("step", 9.47e6),
+}
 DECODE_BYTES_PER_SESSION = 65536 * 512 + 2051 * 2048 + 2 * 2097152   # pool scan + K/V gather + GDN state in/out
 
 
@@ -455,6 +464,10 @@ def main():
     launches_per_step = dom_calls / args.steps if dom_calls else 1
     dominant_bytes = wl.kernel_bytes.get(dominant, wl.alg_bytes)
     achieved = (dominant_bytes / launches_per_step) / (per_launch_ms * 1e-3) / 1e9 if per_launch_ms else None
+    traffic = None
+    if dominant in NCU_TRAFFIC:
+        per, val = NCU_TRAFFIC[dominant]
+        traffic = val * (wl.units_per_step if per == "token" else 1.0) / launches_per_step
     launches = sum(v[1] for v in prof.values())   # library kernels per timed region (graph replays launch the same kernels)
     total_units = wl.units_per_step * world * args.steps
     line = {
@@ -467,7 +480,7 @@ def main():
         "clocks": clocks,
         "roofline": {"bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": (achieved / peak) if achieved else None, "peak_source": peak_kind + " (of measured copy bandwidth)"
-                     if peak_kind == "measured" else "fallback", "traffic": None,
+                     if peak_kind == "measured" else "fallback", "traffic": traffic,
                      "algorithmic_bytes_per_launch": dominant_bytes / launches_per_step, "step_algorithmic_bytes": wl.alg_bytes,
                      "step_frac_of_hbm_roofline": (wl.alg_bytes / peak / 1e9) / (ms / args.steps * 1e-3), "kernel_ms_per_launch": per_launch_ms,
                      "kernels": {k: {"ms_per_step": v[0] / args.steps, "launches_per_step": v[1] / args.steps} for k, v in prof.items()}},
