@@ -8,7 +8,34 @@
 #include <cstdarg>
 #include "../../include/crucible_attn.h"
 
+#include <utility>
+#include <cstdlib>
+
 namespace cr {
+
+// ---- programmatic dependent launch ---------------------------------------------------------------------------
+// A kernel launched with launch_pdl may be scheduled while the kernel before it on the stream is still running;
+// it calls pdl_wait() before it touches anything that kernel (or any earlier one) wrote, which returns once the
+// earlier grid has completed and its writes are visible.  Every kernel of a chain calls pdl_release() at its top so
+// that its successor's launch latency and CTA placement overlap its own execution.  Both are no-ops in a kernel
+// launched the plain way.  CR_NO_PDL=1 in the environment turns the launch attribute off.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_release() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+inline bool pdl_enabled() {
+  static const bool on = getenv("CR_NO_PDL") == nullptr;
+  return on;
+}
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(std::forward<Args>(args))...);
+}
+
 
 constexpr float kEps = 1e-6f;                         // every norm epsilon
 constexpr float kInvSqrt128 = 0.08838834764831845f;   // 1/sqrt(128)

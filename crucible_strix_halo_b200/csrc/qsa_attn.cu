@@ -1,162 +1,215 @@
 // QSA attention over the attended positions for sm_100a (decode, verify, and the row-wise prefill path).
 //
-// Split-KV gather (QsaGqaSplitKernel, engine/layers/qsa_long.h:399-456): one CTA per (split, row, KV head);
-// its warps are the query heads of the KV group and share every K/V row.  Positions are staged 32 at a time
-// as fp16 in shared memory with 128-bit loads (the next tile is prefetched into registers while the current
-// one is consumed).  QK^T runs position-parallel (lane = position, fp32 query broadcast from shared memory),
-// PV runs channel-parallel (lane = 8 channels), so the only shuffles are one max and one sum per tile.
-// Each CTA writes the partial (m, l, acc[256]) of its heads; the merge kernel (QsaMergeKernel,
-// qsa_long.h:458-499) combines them by log-sum-exp, applies the sigmoid gate and the output transform.
-// No CTA waits on another CTA.
+// Split-KV gather (QsaGqaSplitKernel, engine/layers/qsa_long.h:399-456): one CTA of four warps per (split, row,
+// KV head).  The query heads of the KV group are the M rows of a tensor-core tile (8..12 heads padded to 16), so
+// every K/V row fetched is used by all heads at once:
+//   S[16 x 32] = Q[16 x 256] K^T      mma.sync m16n8k16 f16, warp w owns positions 8w .. 8w+7 of the tile
+//   O[16 x 256] += P[16 x 32] V       warp w owns channels 64w .. 64w+63
+// K and V are fp16 in the cache.  Q and P are fp32 values: each is split into an fp16 head and an fp16 remainder
+// and multiplied twice, which keeps the products at fp32 accuracy (the remainder carries the bits fp16 drops).
+// Tiles of 32 positions are gathered with cp.async (zero fill for masked positions) into two shared-memory
+// stages, the next tile in flight while the current one is multiplied; row maxima and sums cross the four warps
+// through shared memory.  Each CTA writes the partial (m, l, acc[256]) of its heads; the merge kernel
+// (QsaMergeKernel, qsa_long.h:458-499) combines them by log-sum-exp, applies the sigmoid gate and the output
+// transform.  No CTA waits on another CTA.
 #include <climits>
 #include "qsa.cuh"
 
 namespace cr {
 
 constexpr int kTile = 32;            // positions per shared-memory tile
-constexpr int kKRow = 264;           // padded K row (halves): 528 B keeps 128-bit column reads conflict-free
-constexpr int kMaxGqa = 12;
+constexpr int kRowH = 264;           // padded row of 256 halves: 528 B keeps ldmatrix conflict-free
+constexpr int kPRowH = 40;           // padded row of the 16 x 32 probability tile (80 B)
+constexpr int kMaxSplitPos = 576;    // positions of one split: at most 65 tiles over >= 4 splits = 17 tiles = 544
+
+struct SplitSmem {
+  __half q[2][16][kRowH];            // head and remainder of the query rows
+  __half k[2][kTile][kRowH];         // two stages
+  __half v[2][kTile][kRowH];
+  __half p[2][16][kPRowH];           // head and remainder of the probabilities
+  float red[2][4][16];               // per-warp row maxima / row sums
+  int pos[kMaxSplitPos];             // cache position of every attended index of this split, -1 = masked
+};
 
 __device__ __forceinline__ int qsa_position(const int* sel, int t, int ns, int nb) {
   return ns < 0 ? t : (t < ns * 4 ? sel[t >> 2] * 4 + (t & 3) : nb * 4 + t - ns * 4);
 }
+__device__ __forceinline__ void cp_async_16(void* dst, const void* src, bool valid) {
+  const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+  const int bytes = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void ldsm_x4(unsigned (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"((unsigned)__cvta_generic_to_shared(p)));
+}
+__device__ __forceinline__ void ldsm_x4_trans(unsigned (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"((unsigned)__cvta_generic_to_shared(p)));
+}
+__device__ __forceinline__ void mma_f16(float (&d)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
 
-// grid (splits, Rmax * Hkv, spans); blockDim = 32 * gqa.
-__global__ void __launch_bounds__(384) qsa_attn_split_kernel(const __grid_constant__ QsaParams P, float* partials,
+// grid (splits, Rmax * Hkv, spans); 128 threads.
+__global__ void __launch_bounds__(128) qsa_attn_split_kernel(const __grid_constant__ QsaParams P, float* partials,
                                                              int splits, int p0, int p1) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  SplitSmem& sm = *reinterpret_cast<SplitSmem*>(smem_raw);
+  pdl_release();
+  pdl_wait();
   const cr_qsa_args& a = P.span[blockIdx.z];
   const int r = blockIdx.y / P.Hkv, g = blockIdx.y % P.Hkv;
   if (r >= a.R) return;
-  const int gqa = P.Hq / P.Hkv, nthr = 32 * gqa;
-  const int t = threadIdx.x, w = t >> 5, l = t & 31, h = g * gqa + w;
+  const int gqa = P.Hq / P.Hkv;
+  const int t = threadIdx.x, w = t >> 5, l = t & 31;
   const int split = blockIdx.x;
   const int p = a.pos0 + r, ns = a.nsel[r], nb = (p + 1) / 4;
   const int n = ns < 0 ? p + 1 : ns * 4 + (p + 1) % 4;
-  const int per = max(kTile, (n / splits) / kTile * kTile);   // decode: 64 per split, the last takes the rest
-  const int begin = split * per, end = split == splits - 1 ? n : min(begin + per, n);
+  // tiles of 32 attended indices are dealt evenly: the first (tiles % splits) splits take one more
+  const int tiles = (n + kTile - 1) / kTile, tb = tiles / splits, trem = tiles % splits;
+  const int begin = (split * tb + min(split, trem)) * kTile, end = min(begin + (tb + (split < trem ? 1 : 0)) * kTile, n);
+  const int cnt = min(max(end - begin, 0), kMaxSplitPos);     // n <= 2051 and splits >= 4: at most 17 tiles
   const int* sel = a.sel + (size_t)r * CR_SEL_BLOCKS;
 
-  __shared__ __align__(16) __half ksm[kTile][kKRow];
-  __shared__ __align__(16) __half vsm[kTile][256];
-  __shared__ __align__(16) float qsm[kMaxGqa][256];
-  __shared__ int psm[kTile];
+  for (int i = t; i < cnt; i += 128) {
+    int pos = qsa_position(sel, begin + i, ns, nb);
+    if (pos < p0 || pos >= p1) pos = -1;
+    sm.pos[i] = pos;
+  }
+  __syncthreads();
 
-  for (int i = t; i < gqa * 256; i += nthr) qsm[i >> 8][i & 255] = a.q[((size_t)r * P.Hq + g * gqa + (i >> 8)) * 512 + (i & 255)];
-
-  // Stage one tile: 32 positions x (32 K + 32 V) 16-byte pieces, spread over the CTA's threads.
-  const int pieces = kTile * 64;
-  const int ppt = (pieces + nthr - 1) / nthr;             // <= 8: the geometry check keeps gqa >= 8
-  constexpr int kMaxPieces = 8;    // 2048 pieces over >= 256 threads
-  uint4 stage[kMaxPieces];
   const __half* kc = reinterpret_cast<const __half*>(a.c.k);
   const __half* vc = reinterpret_cast<const __half*>(a.c.v);
-  auto fetch = [&](int tile0) {
-#pragma unroll
-    for (int i = 0; i < kMaxPieces; ++i) {
-      if (i >= ppt) break;
-      const int piece = t + i * nthr;
-      uint4 v = make_uint4(0u, 0u, 0u, 0u);
-      if (piece < pieces) {
-        const int j = piece >> 6, c = piece & 63;
-        const int ti = tile0 + j;
-        if (ti < end) {
-          const int pos = qsa_position(sel, ti, ns, nb);
-          if (pos >= p0 && pos < p1) {
-            const size_t off = ((size_t)pos * P.Hkv + g) * 256 + (c & 31) * 8;
-            v = *reinterpret_cast<const uint4*>((c < 32 ? kc : vc) + off);
-          }
-        }
-      }
-      stage[i] = v;
+  auto stage = [&](int tile, int buf) {   // 32 positions x (32 K + 32 V) 16-byte pieces
+    for (int piece = t; piece < kTile * 64; piece += 128) {
+      const int j = piece >> 6, c = piece & 63, idx = tile * kTile + j;
+      const int pos = idx < cnt ? sm.pos[idx] : -1;
+      const bool valid = pos >= 0;
+      const size_t off = valid ? ((size_t)pos * P.Hkv + g) * 256 + (c & 31) * 8 : 0;
+      cp_async_16(c < 32 ? &sm.k[buf][j][(c & 31) * 8] : &sm.v[buf][j][(c & 31) * 8], (c < 32 ? kc : vc) + off, valid);
     }
-  };
-  auto commit = [&](int tile0) {
-#pragma unroll
-    for (int i = 0; i < kMaxPieces; ++i) {
-      if (i >= ppt) break;
-      const int piece = t + i * nthr;
-      if (piece < pieces) {
-        const int j = piece >> 6, c = piece & 63;
-        if (c < 32) *reinterpret_cast<uint4*>(&ksm[j][c * 8]) = stage[i];
-        else *reinterpret_cast<uint4*>(&vsm[j][(c - 32) * 8]) = stage[i];
-      }
-    }
-    if (t < kTile) {
-      const int ti = tile0 + t;
-      int pos = -1;
-      if (ti < end) {
-        pos = qsa_position(sel, ti, ns, nb);
-        if (pos < p0 || pos >= p1) pos = -1;
-      }
-      psm[t] = pos;
-    }
+    asm volatile("cp.async.commit_group;\n" ::);
   };
 
-  float m = -INFINITY, lsum = 0.f, acc[8];
+  const int ntiles = (cnt + kTile - 1) / kTile;
+  const int row0 = l >> 2, cq = (l & 3) * 2;              // this thread's rows row0, row0 + 8; columns cq, cq + 1 of an n-tile
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  float O[8][4];
 #pragma unroll
-  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-  if (begin < end) fetch(begin);
-  for (int tile0 = begin; tile0 < end; tile0 += kTile) {
-    __syncthreads();                 // previous tile fully consumed (and qsm visible on the first pass)
-    commit(tile0);
-    __syncthreads();
-    if (tile0 + kTile < end) fetch(tile0 + kTile);
-    // QK^T: lane = position of the tile
-    float s = -INFINITY;
-    if (psm[l] >= 0) {
-      const __half* krow = &ksm[l][0];
-      const float* q = &qsm[w][0];
-      float d0 = 0.f, d1 = 0.f;
+  for (int i = 0; i < 8; ++i) O[i][0] = O[i][1] = O[i][2] = O[i][3] = 0.f;
+  if (ntiles > 0) stage(0, 0);
+  // the query rows are split into fp16 head + remainder while the first tile is in flight
+  for (int i = t; i < 16 * 64; i += 128) {
+    const int row = i >> 6, c = (i & 63) * 4;
+    float4 qv = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (row < gqa) qv = *reinterpret_cast<const float4*>(a.q + ((size_t)r * P.Hq + g * gqa + row) * 512 + c);
+    const __half2 h0 = __floats2half2_rn(qv.x, qv.y), h1 = __floats2half2_rn(qv.z, qv.w);
+    const float2 b0 = __half22float2(h0), b1 = __half22float2(h1);
+    *reinterpret_cast<__half2*>(&sm.q[0][row][c]) = h0;
+    *reinterpret_cast<__half2*>(&sm.q[0][row][c + 2]) = h1;
+    *reinterpret_cast<__half2*>(&sm.q[1][row][c]) = __floats2half2_rn(qv.x - b0.x, qv.y - b0.y);
+    *reinterpret_cast<__half2*>(&sm.q[1][row][c + 2]) = __floats2half2_rn(qv.z - b1.x, qv.w - b1.y);
+  }
+  for (int tile = 0; tile < ntiles; ++tile) {
+    const int buf = tile & 1;
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+    __syncthreads();                                      // tile visible; every warp is done with the previous one
+    if (tile + 1 < ntiles) stage(tile + 1, buf ^ 1);
+    // ---- S = Q K^T for positions 8w .. 8w+7
+    float s[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll 4
-      for (int c = 0; c < 256; c += 8) {
-        const uint4 kv = *reinterpret_cast<const uint4*>(krow + c);
-        const float4 qa = *reinterpret_cast<const float4*>(q + c);
-        const float4 qb = *reinterpret_cast<const float4*>(q + c + 4);
-        const __half2* kh = reinterpret_cast<const __half2*>(&kv);
-        const float2 k0 = __half22float2(kh[0]), k1 = __half22float2(kh[1]);
-        const float2 k2 = __half22float2(kh[2]), k3 = __half22float2(kh[3]);
-        d0 = fmaf(qa.x, k0.x, d0); d1 = fmaf(qa.y, k0.y, d1);
-        d0 = fmaf(qa.z, k1.x, d0); d1 = fmaf(qa.w, k1.y, d1);
-        d0 = fmaf(qb.x, k2.x, d0); d1 = fmaf(qb.y, k2.y, d1);
-        d0 = fmaf(qb.z, k3.x, d0); d1 = fmaf(qb.w, k3.y, d1);
+    for (int ks = 0; ks < 16; ks += 2) {                  // two k-steps of 16 channels per K fragment load
+      unsigned kb[4];
+      ldsm_x4(kb, &sm.k[buf][8 * w + (l & 7)][ks * 16 + (l >> 3) * 8]);
+#pragma unroll
+      for (int kk = 0; kk < 2; ++kk) {
+        unsigned ah[4], al[4];
+        ldsm_x4(ah, &sm.q[0][l & 15][(ks + kk) * 16 + (l >> 4) * 8]);
+        ldsm_x4(al, &sm.q[1][l & 15][(ks + kk) * 16 + (l >> 4) * 8]);
+        mma_f16(s, ah, kb[2 * kk], kb[2 * kk + 1]);
+        mma_f16(s, al, kb[2 * kk], kb[2 * kk + 1]);
       }
-      s = (d0 + d1) * 0.0625f;
     }
-    const float tmax = warp_max(s);
-    if (tmax > -INFINITY) {            // warp uniform
-      const float mn = fmaxf(m, tmax);
-      const float corr = __expf(m - mn);      // m = -inf on the first tile: exp(-inf) = 0
-      const float e = s > -INFINITY ? __expf(s - mn) : 0.f;
-      lsum = lsum * corr + warp_sum(e);
+    const int pi = tile * kTile + 8 * w + cq;
+    const bool v0 = pi < cnt && sm.pos[pi] >= 0, v1 = pi + 1 < cnt && sm.pos[pi + 1] >= 0;
+    s[0] = v0 ? s[0] * 0.0625f : -INFINITY; s[1] = v1 ? s[1] * 0.0625f : -INFINITY;
+    s[2] = v0 ? s[2] * 0.0625f : -INFINITY; s[3] = v1 ? s[3] * 0.0625f : -INFINITY;
+    float mx0 = fmaxf(s[0], s[1]), mx1 = fmaxf(s[2], s[3]);
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    if ((l & 3) == 0) { sm.red[0][w][row0] = mx0; sm.red[0][w][row0 + 8] = mx1; }
+    __syncthreads();
+    float mn[2], corr[2];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) acc[i] *= corr;
-      m = mn;
-      // PV: lane = channels 8l..8l+7
-#pragma unroll 4
-      for (int j = 0; j < kTile; ++j) {
-        const float pj = __shfl_sync(0xffffffffu, e, j);
-        const uint4 vv = *reinterpret_cast<const uint4*>(&vsm[j][l * 8]);
-        const __half2* vh = reinterpret_cast<const __half2*>(&vv);
+    for (int i = 0; i < 2; ++i) {
+      const int row = row0 + 8 * i;
+      const float tm = fmaxf(fmaxf(sm.red[0][0][row], sm.red[0][1][row]), fmaxf(sm.red[0][2][row], sm.red[0][3][row]));
+      mn[i] = fmaxf(m_run[i], tm);
+      corr[i] = m_run[i] > -INFINITY ? __expf(m_run[i] - mn[i]) : 0.f;   // nothing accumulated yet: factor irrelevant
+    }
+    float e[4];
+    e[0] = s[0] > -INFINITY ? __expf(s[0] - mn[0]) : 0.f; e[1] = s[1] > -INFINITY ? __expf(s[1] - mn[0]) : 0.f;
+    e[2] = s[2] > -INFINITY ? __expf(s[2] - mn[1]) : 0.f; e[3] = s[3] > -INFINITY ? __expf(s[3] - mn[1]) : 0.f;
+    float su0 = e[0] + e[1], su1 = e[2] + e[3];
+    su0 += __shfl_xor_sync(0xffffffffu, su0, 1); su1 += __shfl_xor_sync(0xffffffffu, su1, 1);
+    su0 += __shfl_xor_sync(0xffffffffu, su0, 2); su1 += __shfl_xor_sync(0xffffffffu, su1, 2);
+    if ((l & 3) == 0) { sm.red[1][w][row0] = su0; sm.red[1][w][row0 + 8] = su1; }
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float2 f = __half22float2(vh[i]);
-          acc[2 * i] = fmaf(pj, f.x, acc[2 * i]);
-          acc[2 * i + 1] = fmaf(pj, f.y, acc[2 * i + 1]);
-        }
+    for (int i = 0; i < 2; ++i) {                          // probabilities as fp16 head + remainder
+      const __half2 hi = __floats2half2_rn(e[2 * i], e[2 * i + 1]);
+      const float2 back = __half22float2(hi);
+      *reinterpret_cast<__half2*>(&sm.p[0][row0 + 8 * i][8 * w + cq]) = hi;
+      *reinterpret_cast<__half2*>(&sm.p[1][row0 + 8 * i][8 * w + cq]) = __floats2half2_rn(e[2 * i] - back.x, e[2 * i + 1] - back.y);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int row = row0 + 8 * i;
+      l_run[i] = l_run[i] * corr[i] + (sm.red[1][0][row] + sm.red[1][1][row]) + (sm.red[1][2][row] + sm.red[1][3][row]);
+      m_run[i] = mn[i];
+    }
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) { O[nt][0] *= corr[0]; O[nt][1] *= corr[0]; O[nt][2] *= corr[1]; O[nt][3] *= corr[1]; }
+    // ---- O += P V for channels 64w .. 64w+63
+#pragma unroll
+    for (int kk = 0; kk < 2; ++kk) {                      // 16 positions per k-step
+      unsigned ph[4], pl[4];
+      ldsm_x4(ph, &sm.p[0][l & 15][kk * 16 + (l >> 4) * 8]);
+      ldsm_x4(pl, &sm.p[1][l & 15][kk * 16 + (l >> 4) * 8]);
+#pragma unroll
+      for (int nt = 0; nt < 8; nt += 2) {                 // two n-tiles of 8 channels per V fragment load
+        unsigned vb[4];
+        ldsm_x4_trans(vb, &sm.v[buf][kk * 16 + (l & 7) + ((l >> 3) & 1) * 8][64 * w + nt * 8 + (l >> 4) * 8]);
+        mma_f16(O[nt], ph, vb[0], vb[1]);
+        mma_f16(O[nt], pl, vb[0], vb[1]);
+        mma_f16(O[nt + 1], ph, vb[2], vb[3]);
+        mma_f16(O[nt + 1], pl, vb[2], vb[3]);
       }
     }
   }
-  float* dst = partials + (((size_t)(P.base[blockIdx.z] + r) * P.Hq + h) * splits + split) * CR_QSA_PART;
-  if (l == 0) { dst[0] = m; dst[1] = lsum; }
-  // records are 8-byte aligned (258 floats): store pairs
+  // partial records of this split: rows row0 and row0 + 8 are heads g * gqa + row
 #pragma unroll
-  for (int i = 0; i < 8; i += 2) *reinterpret_cast<float2*>(dst + 2 + l * 8 + i) = make_float2(acc[i], acc[i + 1]);
+  for (int i = 0; i < 2; ++i) {
+    const int row = row0 + 8 * i;
+    if (row >= gqa) continue;
+    float* dst = partials + (((size_t)(P.base[blockIdx.z] + r) * P.Hq + g * gqa + row) * splits + split) * CR_QSA_PART;
+    if (w == 0 && (l & 3) == 0) { dst[0] = m_run[i]; dst[1] = l_run[i]; }
+    // records are 8-byte aligned (258 floats): store pairs
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt)
+      *reinterpret_cast<float2*>(dst + 2 + 64 * w + nt * 8 + cq) = make_float2(O[nt][2 * i], O[nt][2 * i + 1]);
+  }
 }
 
 // grid (Hq, Rmax, spans), 256 threads: thread d = output channel.
 // Partial p of (row, head) is at partials[(part_major ? (p * rows_total + row) * Hq + h : (row * Hq + h) * nparts + p) * 258].
 __global__ void __launch_bounds__(256) qsa_merge_kernel(const __grid_constant__ QsaParams P, const float* partials, int nparts,
                                                         int part_major, int rows_total, float* partial_out, int fmt) {
+  pdl_release();
+  pdl_wait();
   const cr_qsa_args& a = P.span[blockIdx.z];
   const int h = blockIdx.x, r = blockIdx.y, d = threadIdx.x;
   if (r >= a.R) return;
@@ -186,8 +239,16 @@ __global__ void __launch_bounds__(256) qsa_merge_kernel(const __grid_constant__ 
   __syncthreads();
   const float m = ml[0], lsum = ml[1];
   float o = 0.f;
+  if (nparts == 32) {   // the decode case: all 32 loads in flight at once
+    float v[32];
+#pragma unroll
+    for (int p = 0; p < 32; ++p) v[p] = __ldcg(rec(p) + 2 + d);
+#pragma unroll
+    for (int p = 0; p < 32; ++p) o = fmaf(v[p], fs[p], o);
+  } else {
 #pragma unroll 8
-  for (int p = 0; p < nparts; ++p) o = fmaf(rec(p)[2 + d], fs[p], o);
+    for (int p = 0; p < nparts; ++p) o = fmaf(rec(p)[2 + d], fs[p], o);
+  }
   if (partial_out) {      // shard mode: one merged partial per (row, head)
     float* dst = partial_out + ((size_t)row * P.Hq + h) * CR_QSA_PART;
     if (d == 0) { dst[0] = m; dst[1] = lsum; }
@@ -218,6 +279,7 @@ __global__ void __launch_bounds__(256) qsa_merge_kernel(const __grid_constant__ 
 cr_status qsa_attn_launch(const cr_geometry* g, const cr_qsa_args* spans, int n_spans, float* partials, int splits,
                           int p0, int p1, cudaStream_t stream) {
   use_stream(stream);
+  CR_REQUIRE(splits >= 4 && splits <= 64, "qsa attention: %d KV splits unsupported", splits);
   int row_base = 0;
   for (int s0 = 0; s0 < n_spans; s0 += kMaxSpans) {
     const int n = n_spans - s0 < kMaxSpans ? n_spans - s0 : kMaxSpans;
@@ -225,7 +287,12 @@ cr_status qsa_attn_launch(const cr_geometry* g, const cr_qsa_args* spans, int n_
     qsa_fill_params(P, g, spans + s0, n);
     for (int s = 0; s < n; ++s) P.base[s] += row_base;
     const int Rmax = qsa_max_rows(spans + s0, n);
-    qsa_attn_split_kernel<<<dim3(splits, Rmax * g->kv_heads, n), 32 * (g->q_heads / g->kv_heads), 0, stream>>>(P, partials, splits, p0, p1);
+    static bool configured = false;
+    if (!configured) {
+      CR_CUDA(cudaFuncSetAttribute(qsa_attn_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(SplitSmem)));
+      configured = true;
+    }
+    CR_CUDA(launch_pdl(qsa_attn_split_kernel, dim3(splits, Rmax * g->kv_heads, n), dim3(128), sizeof(SplitSmem), stream, P, partials, splits, p0, p1));
     CR_LAUNCH_CHECK("qsa_attn_split_kernel");
     for (int s = 0; s < n; ++s) row_base += spans[s0 + s].R;
   }
@@ -243,7 +310,7 @@ cr_status qsa_merge_launch(const cr_geometry* g, const cr_qsa_args* spans, int n
     qsa_fill_params(P, g, spans + s0, n);
     for (int s = 0; s < n; ++s) P.base[s] += row_base;
     const int Rmax = qsa_max_rows(spans + s0, n);
-    qsa_merge_kernel<<<dim3(g->q_heads, Rmax, n), 256, 0, stream>>>(P, partials, nparts, part_major ? 1 : 0, rows_total, partial_out, (int)fmt);
+    CR_CUDA(launch_pdl(qsa_merge_kernel, dim3(g->q_heads, Rmax, n), dim3(256), 0, stream, P, partials, nparts, part_major ? 1 : 0, rows_total, partial_out, (int)fmt));
     CR_LAUNCH_CHECK("qsa_merge_kernel");
     for (int s = 0; s < n; ++s) row_base += spans[s0 + s].R;
   }

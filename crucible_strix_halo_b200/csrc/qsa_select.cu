@@ -77,6 +77,8 @@ __global__ void __launch_bounds__(256) qsa_score_kernel(const __grid_constant__ 
 // The four lanes that share a block group add their partial dots with two shuffles.
 template <int RT>
 __global__ void __launch_bounds__(256) qsa_score4_kernel(const __grid_constant__ QsaParams P) {
+  pdl_release();
+  pdl_wait();
   const cr_qsa_args& a = P.span[blockIdx.z];
   const int rg0 = blockIdx.y * RT;
   if (rg0 >= a.R) return;
@@ -356,8 +358,8 @@ cr_status qsa_score_launch(const cr_geometry* g, const cr_qsa_args* spans, int n
     cr_status st;
     if (Rmax <= 2) {
       const dim3 grid((tiles + 7) / 8, 1, n);
-      if (Rmax == 1) qsa_score4_kernel<1><<<grid, 256, 0, stream>>>(P);
-      else qsa_score4_kernel<2><<<grid, 256, 0, stream>>>(P);
+      if (Rmax == 1) CR_CUDA(launch_pdl(qsa_score4_kernel<1>, grid, dim3(256), 0, stream, P));
+      else CR_CUDA(launch_pdl(qsa_score4_kernel<2>, grid, dim3(256), 0, stream, P));
       CR_LAUNCH_CHECK("qsa_score_kernel");
       st = CR_OK;
     }

@@ -17,6 +17,8 @@ constexpr int kClusterCtas = 8;
 
 template <int PT>
 __global__ void __cluster_dims__(kClusterCtas, 1, 1) __launch_bounds__(1024) qsa_topk_cluster_kernel(const __grid_constant__ QsaParams P) {
+  pdl_release();
+  pdl_wait();
   const cr_qsa_args& a = P.span[blockIdx.y];
   const int r = blockIdx.x / kClusterCtas;
   if (r >= a.R) return;                                   // uniform over the cluster
@@ -139,9 +141,9 @@ __global__ void __cluster_dims__(kClusterCtas, 1, 1) __launch_bounds__(1024) qsa
 cr_status qsa_topk_cluster_launch(const QsaParams& P, int Rmax, int n, int nb_max, cudaStream_t stream) {
   const dim3 grid(kClusterCtas * Rmax, n);
   const int per = (((nb_max + kClusterCtas - 1) / kClusterCtas + 31) / 32 * 32 + 1023) / 1024;
-  if (per <= 8) qsa_topk_cluster_kernel<8><<<grid, 1024, 0, stream>>>(P);
-  else if (per <= 16) qsa_topk_cluster_kernel<16><<<grid, 1024, 0, stream>>>(P);
-  else if (per <= 32) qsa_topk_cluster_kernel<32><<<grid, 1024, 0, stream>>>(P);
+  if (per <= 8) CR_CUDA(launch_pdl(qsa_topk_cluster_kernel<8>, grid, dim3(1024), 0, stream, P));
+  else if (per <= 16) CR_CUDA(launch_pdl(qsa_topk_cluster_kernel<16>, grid, dim3(1024), 0, stream, P));
+  else if (per <= 32) CR_CUDA(launch_pdl(qsa_topk_cluster_kernel<32>, grid, dim3(1024), 0, stream, P));
   else { set_error("qsa top-k: %d blocks exceed the cluster select's range", nb_max); return CR_ERR_UNSUPPORTED; }
   CR_LAUNCH_CHECK("qsa_topk_cluster_kernel");
   return CR_OK;
