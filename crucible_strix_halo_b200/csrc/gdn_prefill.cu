@@ -151,37 +151,65 @@ __global__ void __launch_bounds__(256) gdn_scan_serial_kernel(GdnPrefillParams P
 }
 
 // ---- gated readout -----------------------------------------------------------------------------------
-// One warp per (row, head); lane l holds columns 4l..4l+3 (the WHT layout).
+// One warp per four consecutive (row, head) units; lane l holds columns 4l..4l+3 of each (the WHT layout).  All
+// loads of the four units are issued before anything is consumed: the kernel is a stream, and bytes in flight per
+// thread are what its bandwidth depends on.
+constexpr int kGateUnits = 4;
 template <bool BF16>
 __global__ void __launch_bounds__(256) gdn_gate_kernel(GdnPrefillParams P) {
   const cr_gdn_args& a = P.a;
-  const int VW = P.Hv * 128;
-  const long long unit = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (unit >= (long long)a.R * P.Hv) return;
-  const int r = (int)(unit / P.Hv), h = (int)(unit % P.Hv), l = threadIdx.x & 31;
-  const size_t base = (size_t)r * VW + h * 128 + l * 4;
-  const float4 y4 = *reinterpret_cast<const float4*>(P.yraw + base);
-  const float y[4] = {y4.x, y4.y, y4.z, y4.w};
-  const float ss = warp_sum(y[0] * y[0] + y[1] * y[1] + y[2] * y[2] + y[3] * y[3]);
-  const float rs = rsqrtf(ss * (1.f / 128.f) + kEps);
-  float o[4];
+  const int VW = P.Hv * 128, l = threadIdx.x & 31;
+  const long long total = (long long)a.R * P.Hv;
+  const long long unit0 = ((long long)blockIdx.x * 8 + (threadIdx.x >> 5)) * kGateUnits;
+  if (unit0 >= total) return;
+  float4 y4[kGateUnits], z4[kGateUnits];
 #pragma unroll
-  for (int i = 0; i < 4; ++i) o[i] = y[i] * rs * a.gamma[l * 4 + i] * sigmoidf_(load_in<BF16>(a.z, base + i));
-  if (P.fmt == CR_OUT_RAW_F32) {
-    *reinterpret_cast<float4*>(reinterpret_cast<float*>(a.out) + base) = make_float4(o[0], o[1], o[2], o[3]);
-  } else if (P.fmt == CR_OUT_RAW_BF16) {
-    __nv_bfloat162* dst = reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<__nv_bfloat16*>(a.out) + base);
-    dst[0] = __floats2bfloat162_rn(o[0], o[1]);
-    dst[1] = __floats2bfloat162_rn(o[2], o[3]);
-  } else {
-    const __half* suh = reinterpret_cast<const __half*>(a.suh_out) + h * 128 + l * 4;
+  for (int u = 0; u < kGateUnits; ++u) {
+    y4[u] = z4[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (unit0 + u < total) {
+      const size_t base = (size_t)(unit0 + u) * 128 + l * 4;   // (row, head) units are contiguous: r * VW + h * 128
+      y4[u] = *reinterpret_cast<const float4*>(P.yraw + base);
+      if constexpr (BF16) {
+        const uint2 zz = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(a.z) + base);
+        const float2 z0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&zz.x));
+        const float2 z1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&zz.y));
+        z4[u] = make_float4(z0.x, z0.y, z1.x, z1.y);
+      } else {
+        z4[u] = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.z) + base);
+      }
+    }
+  }
+  const float4 gm = *reinterpret_cast<const float4*>(a.gamma + l * 4);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) o[i] = round_h(round_h(o[i]) * __half2float(suh[i]));
-    wht128(o);
-    __half* dst = reinterpret_cast<__half*>(a.out);
+  for (int u = 0; u < kGateUnits; ++u) {
+    if (unit0 + u >= total) break;                          // warp uniform
+    const int r = (int)((unit0 + u) / P.Hv), h = (int)((unit0 + u) % P.Hv);
+    const size_t base = (size_t)r * VW + h * 128 + l * 4;
+    const float y[4] = {y4[u].x, y4[u].y, y4[u].z, y4[u].w};
+    const float z[4] = {z4[u].x, z4[u].y, z4[u].z, z4[u].w};
+    const float g4[4] = {gm.x, gm.y, gm.z, gm.w};
+    const float ss = warp_sum(y[0] * y[0] + y[1] * y[1] + y[2] * y[2] + y[3] * y[3]);
+    const float rs = rsqrtf(ss * (1.f / 128.f) + kEps);
+    float o[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
-      dst[out_index(r, h * 128 + l * 4 + i, VW, a.pack_rows, a.pack_off)] = __float2half(o[i] * kHadNorm);
+    for (int i = 0; i < 4; ++i) o[i] = y[i] * rs * g4[i] * sigmoidf_(z[i]);
+    if (P.fmt == CR_OUT_RAW_F32) {
+      *reinterpret_cast<float4*>(reinterpret_cast<float*>(a.out) + base) = make_float4(o[0], o[1], o[2], o[3]);
+    } else if (P.fmt == CR_OUT_RAW_BF16) {
+      const __nv_bfloat162 lo = __floats2bfloat162_rn(o[0], o[1]), hi = __floats2bfloat162_rn(o[2], o[3]);
+      uint2 pk;
+      pk.x = *reinterpret_cast<const unsigned*>(&lo); pk.y = *reinterpret_cast<const unsigned*>(&hi);
+      *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(a.out) + base) = pk;
+    } else {
+      const __half* suh = reinterpret_cast<const __half*>(a.suh_out) + h * 128 + l * 4;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) o[i] = round_h(round_h(o[i]) * __half2float(suh[i]));
+      wht128(o);
+      __half* dst = reinterpret_cast<__half*>(a.out);
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        dst[out_index(r, h * 128 + l * 4 + i, VW, a.pack_rows, a.pack_off)] = __float2half(o[i] * kHadNorm);
+    }
   }
 }
 
@@ -324,7 +352,7 @@ extern "C" cr_status cr_gdn_prefill(const cr_geometry* g, const cr_gdn_prefill_a
     if (args->raw_y) P.yraw = args->raw_y + (size_t)p0 * VWs;
   };
   auto gate = [&](cudaStream_t st) -> cr_status {
-    const unsigned gg = (unsigned)(((long long)P.a.R * g->gdn_vheads + 7) / 8);
+    const unsigned gg = (unsigned)(((long long)P.a.R * g->gdn_vheads + 8 * kGateUnits - 1) / (8 * kGateUnits));
     if (bf) gdn_gate_kernel<true><<<gg, 256, 0, st>>>(P); else gdn_gate_kernel<false><<<gg, 256, 0, st>>>(P);
     CR_LAUNCH_CHECK("gdn_gate_kernel");
     return CR_OK;
