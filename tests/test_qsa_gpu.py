@@ -189,6 +189,36 @@ def test_prefill_part_matches_oracle(pos0, R):
         assert_close_attn(out[r], ref[o], max_abs=1e-3, cos=0.99999, what="row %d" % r)
 
 
+@pytest.mark.parametrize("pos0,R", [(0, 2048), (4093, 2047), (30720, 2048), (65531, 1031)])
+def test_prefill_part_reference_shapes(pos0, R):
+    """The full-size (pos0, R) shapes of tests/qsa_union_flash_test.hip:84-93: maximal parts, a part that starts
+    off the block grid, and parts deep in a long context (up to 16,640 blocks scored per row).  The caches are
+    brought to pos0 through cr_qsa_prefill_cache; a sample of rows (first, last, every 227th) is checked against
+    the oracle: selection where the score gap allows, then the gated output."""
+    capi, layers, g, og, rng, norms, suh, w = _setup(16, seed=5)
+    ctx = pos0 + R
+    ses, oc = layers.QsaSession(g, ctx), ao.QsaCache(og, ctx)
+    if pos0:
+        _fill_cache(layers, capi, g, og, w, ses, oc, norms, rng, pos0, part=2048)
+    ses.scores = torch.zeros(R, ses.sstride, device="cuda"); ses.sel = torch.zeros(R, 512, device="cuda", dtype=torch.int32)
+    ses.nsel = torch.zeros(R, device="cuda", dtype=torch.int32)
+    q, k, v, idx = _rows(rng, og, R)
+    sample = sorted(set(list(range(0, R, 227)) + [1, 2, 3, R - 2, R - 1]))
+    ref, sels, scs, _, _ = ao.qsa_rows(q, k, v, idx, norms, oc, pos0, og, return_detail=True, rows=sample)
+    plan = layers.QsaPrefillPlan(w, R)
+    out = plan.run(ses, dev(q), dev(k), dev(v), dev(idx), pos0).cpu().numpy()
+    checked = 0
+    for o, r in enumerate(sample):
+        if sels[o] is not None:
+            got = ses.sel[r].cpu().numpy()
+            assert ao.selection_agrees(scs[o], got, sels[o])
+            if not np.array_equal(got, sels[o]):
+                continue
+        assert_close_attn(out[r], ref[o], max_abs=1e-3, cos=0.99999, what="row %d" % r)
+        checked += 1
+    assert checked >= len(sample) // 2
+
+
 def test_c1_layer_seq4096_with_projections():
     """The CPU-runnable configuration of the path: one gated full-attention layer, causal prefill, batch 1, seq 4096,
     hidden 2048, 16 Q / 2 KV heads x 256, RoPE on the first 64 dims, sigmoid gate; activations ~ N(0,1), weights
