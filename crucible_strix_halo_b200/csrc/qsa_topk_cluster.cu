@@ -13,9 +13,9 @@ namespace cg = cooperative_groups;
 
 namespace cr {
 
-constexpr int kClusterCtas = 8;
-
-template <int PT>
+// kClusterCtas CTAs per row: 8 for the few rows of a decode / verify step (shortest latency per row), 2 for the
+// many rows of a prefill part (each CTA then holds 32 values per thread and more rows run at once).
+template <int kClusterCtas, int PT>
 __global__ void __cluster_dims__(kClusterCtas, 1, 1) __launch_bounds__(1024) qsa_topk_cluster_kernel(const __grid_constant__ QsaParams P) {
   pdl_release();
   pdl_wait();
@@ -137,16 +137,22 @@ __global__ void __cluster_dims__(kClusterCtas, 1, 1) __launch_bounds__(1024) qsa
   cluster.sync();                                          // no CTA exits while its totals may still be read
 }
 
-// nb_max in (8192, 262144]: PT = ceil(ceil(nb/8)/1024) rounded to 8 / 16 / 32.
-cr_status qsa_topk_cluster_launch(const QsaParams& P, int Rmax, int n, int nb_max, cudaStream_t stream) {
-  const dim3 grid(kClusterCtas * Rmax, n);
-  const int per = (((nb_max + kClusterCtas - 1) / kClusterCtas + 31) / 32 * 32 + 1023) / 1024;
-  if (per <= 8) CR_CUDA(launch_pdl(qsa_topk_cluster_kernel<8>, grid, dim3(1024), 0, stream, P));
-  else if (per <= 16) CR_CUDA(launch_pdl(qsa_topk_cluster_kernel<16>, grid, dim3(1024), 0, stream, P));
-  else if (per <= 32) CR_CUDA(launch_pdl(qsa_topk_cluster_kernel<32>, grid, dim3(1024), 0, stream, P));
+// nb_max in (8192, 262144]: PT = ceil(ceil(nb / ctas) / 1024) rounded to 8 / 16 / 32.
+template <int CTAS>
+static cr_status topk_cluster_launch_t(const QsaParams& P, int Rmax, int n, int nb_max, cudaStream_t stream) {
+  const dim3 grid(CTAS * Rmax, n);
+  const int per = (((nb_max + CTAS - 1) / CTAS + 31) / 32 * 32 + 1023) / 1024;
+  if (per <= 8) CR_CUDA(launch_pdl(qsa_topk_cluster_kernel<CTAS, 8>, grid, dim3(1024), 0, stream, P));
+  else if (per <= 16) CR_CUDA(launch_pdl(qsa_topk_cluster_kernel<CTAS, 16>, grid, dim3(1024), 0, stream, P));
+  else if (per <= 32) CR_CUDA(launch_pdl(qsa_topk_cluster_kernel<CTAS, 32>, grid, dim3(1024), 0, stream, P));
   else { set_error("qsa top-k: %d blocks exceed the cluster select's range", nb_max); return CR_ERR_UNSUPPORTED; }
   CR_LAUNCH_CHECK("qsa_topk_cluster_kernel");
   return CR_OK;
+}
+
+cr_status qsa_topk_cluster_launch(const QsaParams& P, int Rmax, int n, int nb_max, cudaStream_t stream) {
+  const bool many_rows = (long long)Rmax * n > 64 && nb_max <= 2 * 32 * 1024;
+  return many_rows ? topk_cluster_launch_t<2>(P, Rmax, n, nb_max, stream) : topk_cluster_launch_t<8>(P, Rmax, n, nb_max, stream);
 }
 
 }  // namespace cr
