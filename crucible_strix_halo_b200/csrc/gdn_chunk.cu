@@ -45,4 +45,5 @@ cr_status gdn_chunk_scan_only(const cr_geometry* g, const GdnPrefillParams& P, c
 
 }  // namespace cr
 
-extern "C" int cr_device_status(void) { return cr::gdn_scan_status_read(); }
+namespace cr { int qsa_score_status_read(); }
+extern "C" int cr_device_status(void) { return cr::gdn_scan_status_read() | (cr::qsa_score_status_read() << 1); }

@@ -100,7 +100,8 @@ cr_status cr_gdn_step(const cr_geometry* g, const cr_gdn_args* spans, int n_span
 typedef enum {
   CR_GDN_SERIAL_F32 = 0,  /* exact fp32 token-serial scan (the role of GdnPersistentColumnKernel,
                              engine/layers/kernels/prefill_gdn.h:285-315) */
-  CR_GDN_CHUNK_TC = 1,    /* chunk-64 WY form, scan on tcgen05 tensor cores with TMEM accumulators
+  CR_GDN_CHUNK_TC = 1,    /* chunk-64 WY form, scan on tcgen05 tensor cores with the recurrent operands and the
+                             accumulators in tensor memory
                              (LaunchGdnPrefill / LaunchGdnMicro, engine/layers/kernels/prefill_gdn.h:1229-1279) */
   CR_GDN_CHUNK_MMA = 2    /* the same algebra with warp-level mma.sync in the scan (kept as the comparison point) */
 } cr_gdn_algo;
@@ -116,6 +117,8 @@ typedef struct {
   float* raw_y;             /* optional fp32 [R][Hv*128] un-gated readout, for validation; may be NULL */
 } cr_gdn_prefill_args;
 
+/* Scratch for one call of `rows` rows: the intermediates of one internal part (7,104 rows, about 72 KB per row),
+ * twice that when the call is longer than a part (consecutive parts work on two workspaces in turn). */
 size_t cr_gdn_prefill_workspace_bytes(const cr_geometry* g, int rows);
 /* 1 when this build of the library carries the algorithm. */
 int cr_gdn_algo_available(cr_gdn_algo algo);
@@ -123,7 +126,11 @@ int cr_gdn_algo_available(cr_gdn_algo algo);
 /* Replaces LaunchGdnScanGate / LaunchGdnLanes / LaunchGdnPrefill / LaunchGdnMicro + GdnPrefillHistoryKernel
  * (engine/layers/kernels/prefill_gdn.h:1206-1216, :1161, :1229-1279, :274-282): rows pos0..pos0+R-1 of one
  * layer from the carried state; writes the gated output, the new state and the raw-row ring.
- * Any R >= 1 is accepted (the engine calls it with parts of <= 2048 rows). */
+ * Any R >= 1 is accepted (the engine calls it with parts of <= 2048 rows).
+ * With CR_GDN_CHUNK_TC a call longer than one internal part runs its kernels on three library-owned streams
+ * (created on first use, one set per device) that fork from `stream` and join it again with events before the
+ * call returns: to the caller the work is still asynchronous on `stream`, and it can be captured into a graph.
+ * Calls on one device are serialised while they enqueue.  With stage timing on everything stays on `stream`. */
 cr_status cr_gdn_prefill(const cr_geometry* g, const cr_gdn_prefill_args* a, cr_gdn_algo algo,
                          cr_out_format fmt, void* stream);
 

@@ -189,6 +189,34 @@ def test_prefill_part_matches_oracle(pos0, R):
         assert_close_attn(out[r], ref[o], max_abs=1e-3, cos=0.99999, what="row %d" % r)
 
 
+@pytest.mark.parametrize("pos0,R", [(2100, 33), (3001, 200), (9000, 257)])
+def test_prefill_scores_tensor_core_path(pos0, R):
+    """Parts of 32 rows or more compute the indexer scores on tcgen05 tensor cores (fp16 head + remainder, three
+    products, fp32 accumulation).  Every score of every row agrees to 2e-5 absolute with fp64 scores of the same
+    prepared operands (the 1e-3 gap within which selections may differ is 50 times wider), and the device status
+    word stays clear."""
+    capi, layers, g, og, rng, norms, suh, w = _setup(16, seed=9)
+    ctx = pos0 + R
+    ses, oc = layers.QsaSession(g, ctx), ao.QsaCache(og, ctx)
+    _fill_cache(layers, capi, g, og, w, ses, oc, norms, rng, pos0, part=1024)
+    ses.scores = torch.zeros(R, ses.sstride, device="cuda"); ses.sel = torch.zeros(R, 512, device="cuda", dtype=torch.int32)
+    ses.nsel = torch.zeros(R, device="cuda", dtype=torch.int32)
+    q, k, v, idx = _rows(rng, og, R)
+    plan = layers.QsaPrefillPlan(w, R)
+    idx_d = dev(idx)
+    plan.run(ses, dev(q), dev(k), dev(v), idx_d, pos0)
+    assert capi.lib.cr_device_status() == 0
+    # the arithmetic under test is the scoring alone: fp64 scores of the device's own prepared operands
+    iq = idx_d[:, :512].view(R, 4, 128).double().cpu().numpy()
+    pool = ses.pool_rows((pos0 + R) // 4).double().cpu().numpy()
+    got = ses.scores.cpu().numpy()
+    worst = 0.0
+    for r in range(R):
+        nb = (pos0 + r + 1) // 4
+        worst = max(worst, float(np.abs(got[r, :nb] - ao.qsa_scores(iq[r], pool[:nb])).max()))
+    assert worst < 2e-5, worst                                # measured 9e-6; the fp32 FMA kernel gives 4e-6
+
+
 @pytest.mark.parametrize("pos0,R", [(0, 2048), (4093, 2047), (30720, 2048), (65531, 1031)])
 def test_prefill_part_reference_shapes(pos0, R):
     """The full-size (pos0, R) shapes of tests/qsa_union_flash_test.hip:84-93: maximal parts, a part that starts
