@@ -22,10 +22,13 @@ constexpr int kRowH = 264;           // padded row of 256 halves: 528 B keeps ld
 constexpr int kPRowH = 40;           // padded row of the 16 x 32 probability tile (80 B)
 constexpr int kMaxSplitPos = 576;    // positions of one split: at most 65 tiles over >= 4 splits = 17 tiles = 544
 
+// STAGES = 2: the next tile is gathered while the current one is multiplied (a step: few CTAs, latency counts).
+// STAGES = 1: 55 KB per CTA, four CTAs per SM keep more gathers in flight (a prefill part: thousands of CTAs).
+template <int STAGES>
 struct SplitSmem {
   __half q[2][16][kRowH];            // head and remainder of the query rows
-  __half k[2][kTile][kRowH];         // two stages
-  __half v[2][kTile][kRowH];
+  __half k[STAGES][kTile][kRowH];
+  __half v[STAGES][kTile][kRowH];
   __half p[2][16][kPRowH];           // head and remainder of the probabilities
   float red[2][4][16];               // per-warp row maxima / row sums
   int pos[kMaxSplitPos];             // cache position of every attended index of this split, -1 = masked
@@ -54,10 +57,11 @@ __device__ __forceinline__ void mma_f16(float (&d)[4], const unsigned (&a)[4], u
 }
 
 // grid (splits, Rmax * Hkv, spans); 128 threads.
+template <int STAGES>
 __global__ void __launch_bounds__(128) qsa_attn_split_kernel(const __grid_constant__ QsaParams P, float* partials,
                                                              int splits, int p0, int p1) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  SplitSmem& sm = *reinterpret_cast<SplitSmem*>(smem_raw);
+  SplitSmem<STAGES>& sm = *reinterpret_cast<SplitSmem<STAGES>*>(smem_raw);
   pdl_release();
   pdl_wait();
   const cr_qsa_args& a = P.span[blockIdx.z];
@@ -100,7 +104,7 @@ __global__ void __launch_bounds__(128) qsa_attn_split_kernel(const __grid_consta
   float O[8][4];
 #pragma unroll
   for (int i = 0; i < 8; ++i) O[i][0] = O[i][1] = O[i][2] = O[i][3] = 0.f;
-  if (ntiles > 0) stage(0, 0);
+  if (STAGES == 2 && ntiles > 0) stage(0, 0);
   // the query rows are split into fp16 head + remainder while the first tile is in flight
   for (int i = t; i < 16 * 64; i += 128) {
     const int row = i >> 6, c = (i & 63) * 4;
@@ -114,10 +118,14 @@ __global__ void __launch_bounds__(128) qsa_attn_split_kernel(const __grid_consta
     *reinterpret_cast<__half2*>(&sm.q[1][row][c + 2]) = __floats2half2_rn(qv.z - b1.x, qv.w - b1.y);
   }
   for (int tile = 0; tile < ntiles; ++tile) {
-    const int buf = tile & 1;
+    const int buf = STAGES == 2 ? (tile & 1) : 0;
+    if (STAGES == 1) {
+      __syncthreads();                                    // every warp is done with the previous tile (and q is visible)
+      stage(tile, 0);
+    }
     asm volatile("cp.async.wait_group 0;\n" ::: "memory");
     __syncthreads();                                      // tile visible; every warp is done with the previous one
-    if (tile + 1 < ntiles) stage(tile + 1, buf ^ 1);
+    if (STAGES == 2 && tile + 1 < ntiles) stage(tile + 1, buf ^ 1);
     // ---- S = Q K^T for positions 8w .. 8w+7
     float s[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll 4
@@ -289,10 +297,15 @@ cr_status qsa_attn_launch(const cr_geometry* g, const cr_qsa_args* spans, int n_
     const int Rmax = qsa_max_rows(spans + s0, n);
     static bool configured = false;
     if (!configured) {
-      CR_CUDA(cudaFuncSetAttribute(qsa_attn_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(SplitSmem)));
+      CR_CUDA(cudaFuncSetAttribute(qsa_attn_split_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(SplitSmem<1>)));
+      CR_CUDA(cudaFuncSetAttribute(qsa_attn_split_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(SplitSmem<2>)));
       configured = true;
     }
-    CR_CUDA(launch_pdl(qsa_attn_split_kernel, dim3(splits, Rmax * g->kv_heads, n), dim3(128), sizeof(SplitSmem), stream, P, partials, splits, p0, p1));
+    const dim3 grid(splits, Rmax * g->kv_heads, n);
+    if ((long long)grid.x * grid.y * grid.z > 1024)
+      CR_CUDA(launch_pdl(qsa_attn_split_kernel<1>, grid, dim3(128), sizeof(SplitSmem<1>), stream, P, partials, splits, p0, p1));
+    else
+      CR_CUDA(launch_pdl(qsa_attn_split_kernel<2>, grid, dim3(128), sizeof(SplitSmem<2>), stream, P, partials, splits, p0, p1));
     CR_LAUNCH_CHECK("qsa_attn_split_kernel");
     for (int s = 0; s < n; ++s) row_base += spans[s0 + s].R;
   }
