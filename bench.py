@@ -7,6 +7,7 @@ A step is one pass of the hot path over one batch of synthetic input.  Workloads
   gdn_prefill_32k  one Gated DeltaNet layer, chunked prefill, batch 1, seq 32768, 16 QK x 128 / 32 V x 128 heads,
                    bf16 inputs, fp32 state (the default: the config the headline metric is quoted on)
   decode_262k      QSA sparse attention decode + GDN recurrent update, 4 sessions x 262,144-token fp16 KV cache
+  qsa_prefill_262k one QSA layer, the last 2,048-row part of a 262,144-token prefill (scores, top-512, attention)
 Under torchrun (N > 1) every rank runs the same workload on its own sequences / sessions (weak scaling, no
 data-path collective); time is the max over ranks, value the whole-job throughput.
 Prints ONE JSON line (rank 0).  --impl reference times the CPU restatement of the reference's algorithm
@@ -31,10 +32,12 @@ GDN_BYTES_PER_TOKEN = (8192 + 4096) * 2 + 4096 * 2 + 2 * 32 * 4      # bf16 qkv 
 # profiles/, per unit of work (GDN: per token of a 7,104-token part; decode: per step of 4 sessions), scaled to
 # the launch by the units it processes (traffic grows in proportion to them).
 NCU_TRAFFIC = {
-    "gdn_chunk_scan_tc_kernel": ("token", (526.546e6 + 102.534e6) / 7104), "gdn_chunk_local_kernel": ("token", (120.665e6 + 465.678e6) / 7104),
-    "gdn_gate_kernel": ("token", (174.600e6 + 39.643e6) / 7104),
-    "qsa_score_kernel": ("step", 134.26e6 + 4.22e6), "qsa_attn_split_kernel": ("step", 16.88e6), "qsa_topk_cluster_kernel": ("step", 1.07e6),
-    "qsa_merge_kernel": ("step", 2.20e6), "qsa_prep_kernel": ("step", 0.13e6), "gdn_step_kernel": ("step", 9.47e6),
+    "gdn_prefill_32k": {"gdn_chunk_scan_tc_kernel": ("token", (526.546e6 + 102.534e6) / 7104),
+                        "gdn_chunk_local_kernel": ("token", (120.665e6 + 465.678e6) / 7104),
+                        "gdn_gate_kernel": ("token", (174.600e6 + 39.643e6) / 7104)},
+    "decode_262k": {"qsa_score_kernel": ("step", 134.26e6 + 4.22e6), "qsa_attn_split_kernel": ("step", 16.88e6),
+                    "qsa_topk_cluster_kernel": ("step", 1.07e6), "qsa_merge_kernel": ("step", 2.20e6), "qsa_prep_kernel": ("step", 0.13e6),
+                    "gdn_step_kernel": ("step", 9.47e6)},
 }
 DECODE_BYTES_PER_SESSION = 65536 * 512 + 2051 * 2048 + 2 * 2097152   # pool scan + K/V gather + GDN state in/out
 
@@ -316,7 +319,60 @@ class Decode262k:
                 "l2": "per-step traffic (168 MB) exceeds the 126 MB L2"}
 
 
-WORKLOADS = {"gdn_prefill_32k": GdnPrefill32k, "decode_262k": Decode262k}
+class QsaPrefill262k:
+    """The last 2,048-row part of a 262,144-token prefill of one QSA layer (configs[3], attention stage with i.i.d.
+    selections): cache K,V fp16 ~ N(0,1) and pooled keys ~ N(0,1) for positions < 260,096; the part's rows
+    q [R,16,512], k,v [R,512], idx [R,640] ~ N(0,1) fp32.  Per row: scores over up to 65,536 blocks, exact top-512,
+    attention over 2,051 positions for 16 heads; all rows are causal within the part."""
+    name = "qsa_prefill_262k"
+    POS0, R = 262144 - 2048, 2048
+    unit, metric, dtype = "tokens/s", "qsa_layer_prefill_tokens_per_s_at_262k", "fp16 kv / fp32 q / fp16x2 tensor-core products"
+
+    def __init__(self, rank, algo):
+        import torch
+        from crucible_strix_halo_b200 import capi, layers
+        self.torch, self.capi, self.layers = torch, capi, layers
+        g = capi.GEOM_BENCH
+        gen = torch.Generator(device="cuda").manual_seed(3000 + rank)
+        rn = lambda *s, std=1.0: torch.randn(*s, device="cuda", generator=gen) * std
+        R, ctx = self.R, self.POS0 + self.R
+        self.w = layers.QsaWeights(g, 1 + rn(256, std=0.1), 1 + rn(256, std=0.1), 1 + rn(128, std=0.1), 1 + rn(128, std=0.1))
+        self.ses = layers.QsaSession(g, ctx, max_rows=R)
+        self.ses.k.copy_(rn(ctx, 2, 256).half()); self.ses.v.copy_(rn(ctx, 2, 256).half())
+        self.ses.ik_pool.copy_(rn(self.ses.ik_pool.numel())); self.ses.ik_raw.copy_(rn(ctx, 128))
+        self.plan = layers.QsaPrefillPlan(self.w, R, fmt=capi.OUT_RAW_BF16)
+        self.inp = rn(R, 8192 + 512 + 512 + 640)
+        self.work = torch.empty_like(self.inp)               # q and idx are normalised in place: a fresh copy per step
+        self.h_in = self.inp.cpu().pin_memory()
+        self.h_out = torch.empty(R, 4096, dtype=torch.bfloat16).pin_memory()
+        self.h2d, self.d2h = self.h_in.numel() * 4, self.h_out.numel() * 2
+        self.units_per_step = R
+        # gathered K/V rows of every query row + one pass over the pooled keys + the rows in and out
+        self.alg_bytes = R * 2051 * 2048 + 65536 * 512 + self.h2d + self.d2h
+        self.kernel_bytes = {"qsa_attn_split_kernel": R * 2051 * 2048}
+
+    def _run(self, src):
+        R = self.R
+        q, k = src[:, :8192].view(R, 16, 512), src[:, 8192:8704]
+        v, idx = src[:, 8704:9216], src[:, 9216:]
+        return self.plan.run(self.ses, q, k, v, idx, self.POS0)
+
+    def step(self):
+        self.work.copy_(self.inp)
+        return self._run(self.work)
+
+    step_eager = step
+
+    def step_e2e(self):
+        self.work.copy_(self.h_in, non_blocking=True)
+        self.h_out.copy_(self._run(self.work), non_blocking=True)
+
+    def config(self):
+        return {"workload": self.name, "context": self.POS0 + self.R, "part_rows": self.R, "qsa_heads": "16q/2kv x256", "block": 4,
+                "top_k_blocks": 512, "selections": "i.i.d. (random indexer)", "l2": "the K/V cache (0.5 GB) exceeds the 126 MB L2"}
+
+
+WORKLOADS = {"gdn_prefill_32k": GdnPrefill32k, "decode_262k": Decode262k, "qsa_prefill_262k": QsaPrefill262k}
 
 
 # ------------------------------------------------------------------------------------------------------------
@@ -364,6 +420,18 @@ def cpu_baseline(workload, seconds_hint=10.0):
     conv, A_log = f32(rng.normal(size=(Cw, 4)) * 0.5), f32(np.clip(rng.normal(-1, 1.5, Hv), -5, 1.5))
     dtb, gamma = f32(rng.normal(size=Hv) * 0.5), f32(1 + 0.1 * rng.normal(size=128))
     state, gout = f32(rng.normal(size=(Hv, 128, 128)) * 0.05), np.zeros((1, Hv * 128), np.float32)
+    if workload == "qsa_prefill_262k":      # a prefill row costs what a decode row costs: score, select, attend
+        t0 = time.perf_counter()
+        reps = 0
+        while True:
+            lib.oracle_qsa_decode_row(ptr(qn), ptr(gate), ptr(iq), ctx - 1 - reps % 2048, ptr(kc), ptr(vc), ptr(pool), ptr(out), ptr(sel),
+                                      ptr(nsel), Hq, Hkv)
+            reps += 1
+            if time.perf_counter() - t0 > seconds_hint or reps >= 2048:
+                break
+        dt = time.perf_counter() - t0
+        return {"value": reps / dt, "unit": "tokens/s", "cores": cores, "kind": "port",
+                "sample": "%d rows of the 2,048-row part at 262,144 context (score, top-512, attention), %.1f s" % (reps, dt)}
     t0 = time.perf_counter()
     reps = 0
     while True:
@@ -481,8 +549,8 @@ def main():
     dominant_bytes = wl.kernel_bytes.get(dominant, wl.alg_bytes)
     achieved = (dominant_bytes / launches_per_step) / (per_launch_ms * 1e-3) / 1e9 if per_launch_ms else None
     traffic = None
-    if dominant in NCU_TRAFFIC:
-        per, val = NCU_TRAFFIC[dominant]
+    if dominant in NCU_TRAFFIC.get(args.workload, {}):
+        per, val = NCU_TRAFFIC[args.workload][dominant]
         traffic = val * (wl.units_per_step if per == "token" else 1.0) / launches_per_step
     launches = sum(v[1] for v in prof.values())   # library kernels per timed region (graph replays launch the same kernels)
     total_units = wl.units_per_step * world * args.steps

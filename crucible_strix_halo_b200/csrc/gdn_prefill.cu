@@ -8,7 +8,10 @@
 //   gdn_gate   y * rsqrt(mean y^2 + eps) * gamma * sigmoid(z), output transform
 //   gdn_ring   last 16 raw rows -> hist ring (GdnPrefillHistoryKernel, prefill_gdn.h:274-282)
 #include "common.cuh"
+#include <algorithm>
 #include <mutex>
+#include <utility>
+#include <vector>
 #include "gdn_prefill.cuh"
 
 namespace cr {
@@ -262,6 +265,31 @@ int gdn_part_rows() {
   return rows;
 }
 
+// Row ranges of the parts of a pipelined call.  The first local kernel and the last scan run with nothing beside
+// them, so the first part is short and the parts at the end halve (each scan then ends soon after the local
+// kernel that follows it): [32 chunks] [equal parts of at most P chunks] [P/2] [P/4] ... [>= 16 chunks].
+static std::vector<std::pair<int, int>> part_schedule(int R, int part_rows) {
+  std::vector<int> rows;
+  const int chunks = (R + 63) / 64, P = part_rows / 64;
+  std::vector<int> tail;
+  int left = chunks;
+  const int first = chunks > 2 * P ? 32 : 0;
+  left -= first;
+  for (int t = P / 2; t >= 16 && left - t >= P; t /= 2) { tail.push_back(t); left -= t; }
+  const int mid = (left + P - 1) / P;
+  if (first) rows.push_back(first);
+  for (int i = 0; i < mid; ++i) rows.push_back(left / mid + (i < left % mid ? 1 : 0));
+  for (int t : tail) rows.push_back(t);
+  std::vector<std::pair<int, int>> out;
+  int p0 = 0;
+  for (int c : rows) {
+    const int n = std::min(c * 64, R - p0);
+    if (n > 0) out.push_back({p0, n});
+    p0 += n;
+  }
+  return out;
+}
+
 // Internal streams and events of the part pipeline, one set per device, created on first use.  Calls on one
 // device are serialised while they enqueue (the events are shared).
 struct PipeStreams {
@@ -336,13 +364,13 @@ extern "C" cr_status cr_gdn_prefill(const cr_geometry* g, const cr_gdn_prefill_a
   const size_t Cw = 2 * (size_t)g->gdn_kheads * 128 + (size_t)g->gdn_vheads * 128, VWs = (size_t)g->gdn_vheads * 128;
   GdnPrefillParams P;
   // The call runs in parts of gdn_part_rows() rows; the state carries from part to part.
-  auto part_params = [&](int p0, int buf) {
+  auto part_params = [&](int p0, int buf, int rows = 0) {
     P.a = a;
     P.a.qkv = (const char*)a.qkv + (size_t)p0 * Cw * in_elt;
     P.a.z = (const char*)a.z + (size_t)p0 * VWs * in_elt;
     if (a.pack_rows) P.a.pack_off = a.pack_off + p0; else P.a.out = (char*)a.out + (size_t)p0 * VWs * out_elt;
     P.a.pos0 = a.pos0 + p0;
-    P.a.R = a.R - p0 < gdn_part_rows() ? a.R - p0 : gdn_part_rows();
+    P.a.R = rows ? rows : (a.R - p0 < gdn_part_rows() ? a.R - p0 : gdn_part_rows());
     P.a.commit = P.a.R;
     P.ab_logits = (const char*)args->ab_logits + (size_t)p0 * 2 * g->gdn_vheads * in_elt;
     P.Hv = g->gdn_vheads; P.Hk = g->gdn_kheads; P.fmt = (int)fmt;
@@ -368,13 +396,15 @@ extern "C" cr_status cr_gdn_prefill(const cr_geometry* g, const cr_gdn_prefill_a
     CR_CUDA(cudaStreamWaitEvent(ps->hi, ps->fork, 0));
     CR_CUDA(cudaStreamWaitEvent(ps->lo, ps->fork, 0));
     CR_CUDA(cudaStreamWaitEvent(ps->mid, ps->fork, 0));
-    part_params(0, 0);
+    const std::vector<std::pair<int, int>> parts = part_schedule(a.R, gdn_part_rows());
+    const int np = (int)parts.size();
+    part_params(parts[0].first, 0, parts[0].second);
     if (cr_status s = gdn_chunk_local_only(g, P, bf, ps->lo)) return s;
     CR_CUDA(cudaEventRecord(ps->local_done[0], ps->lo));
     int pi = 0;
-    for (int p0 = 0; p0 < a.R; p0 += gdn_part_rows(), ++pi) {
+    for (; pi < np; ++pi) {
       const int buf = pi & 1;
-      part_params(p0, buf);
+      part_params(parts[pi].first, buf, parts[pi].second);
       CR_CUDA(cudaStreamWaitEvent(ps->hi, ps->local_done[buf], 0));
       if (cr_status s = gdn_chunk_scan_only(g, P, ps->hi)) return s;
       // the gated readout runs on a third stream, so the next scan does not queue behind it
@@ -382,9 +412,9 @@ extern "C" cr_status cr_gdn_prefill(const cr_geometry* g, const cr_gdn_prefill_a
       CR_CUDA(cudaStreamWaitEvent(ps->mid, ps->scan_done[buf], 0));
       if (cr_status s = gate(ps->mid)) return s;
       CR_CUDA(cudaEventRecord(ps->part_done[buf], ps->mid));
-      if (p0 + gdn_part_rows() < a.R) {   // local kernel of the next part, into the other workspace
+      if (pi + 1 < np) {   // local kernel of the next part, into the other workspace
         if (pi >= 1) CR_CUDA(cudaStreamWaitEvent(ps->lo, ps->part_done[buf ^ 1], 0));   // its last reader has finished
-        part_params(p0 + gdn_part_rows(), buf ^ 1);
+        part_params(parts[pi + 1].first, buf ^ 1, parts[pi + 1].second);
         if (cr_status s = gdn_chunk_local_only(g, P, bf, ps->lo)) return s;
         CR_CUDA(cudaEventRecord(ps->local_done[buf ^ 1], ps->lo));
       }

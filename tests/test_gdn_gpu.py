@@ -232,3 +232,35 @@ def test_prefill_chunk_tc_pipelined_parts_match_serial_scan():
     np.testing.assert_array_equal(h_pipe, h_ser)
     assert rel_l2(s_pipe, s_ser) < 1e-3
     assert_close_attn(o_pipe, o_ser, max_abs=2e-2, cos=0.9995, what="pipelined chunk vs serial")
+
+
+def test_prefill_pipelined_call_can_be_captured_in_a_graph():
+    """A multi-part call forks onto the library's internal streams and joins the caller's stream again, so it can be
+    captured into a CUDA graph; the replayed graph reproduces the eager result bit for bit."""
+    capi, layers, g, og, rng, wts, w = _setup(4, 2, 64, 22)
+    T = 7104 + 900
+    gen = torch.Generator(device="cuda").manual_seed(4)
+    qkv = torch.randn(T, og.gdn_qkv_width, device="cuda", generator=gen).bfloat16()
+    z = torch.randn(T, og.gdn_value_width, device="cuda", generator=gen).bfloat16()
+    ab = torch.randn(T, 2 * 4, device="cuda", generator=gen).bfloat16()
+    ses = layers.GdnSession(g)
+    plan = layers.GdnPrefillPlan(w, T, in_dtype=capi.IN_BF16)
+    eager = plan.run(ses, qkv, z, ab, 0, capi.GDN_CHUNK_TC).clone()
+    st_eager = ses.state.clone()
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        ses.state.zero_(); ses.hist.zero_()
+        plan.run(ses, qkv, z, ab, 0, capi.GDN_CHUNK_TC)          # warm-up on the capture stream
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        ses.state.zero_(); ses.hist.zero_()
+        with torch.cuda.graph(graph, stream=side):
+            plan.run(ses, qkv, z, ab, 0, capi.GDN_CHUNK_TC)
+    torch.cuda.synchronize()
+    ses.state.zero_(); ses.hist.zero_(); plan.out.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    assert capi.lib.cr_device_status() == 0
+    assert torch.equal(plan.out, eager)
+    assert torch.equal(ses.state, st_eager)
