@@ -40,7 +40,7 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
 constexpr float kEps = 1e-6f;                         // every norm epsilon
 constexpr float kInvSqrt128 = 0.08838834764831845f;   // 1/sqrt(128)
 constexpr float kHadNorm = 0.088388347648f;           // ExLlamaV3's 1/sqrt(128) constant
-constexpr int kMaxSpans = 32;                         // spans per launch (kernel-parameter budget)
+constexpr int kMaxSpans = 32;                         // spans per launch (they travel as kernel parameters: 4 KB in all)
 
 // ---- host-side error plumbing -------------------------------------------------------------------
 void set_error(const char* fmt, ...);

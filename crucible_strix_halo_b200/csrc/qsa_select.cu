@@ -371,7 +371,7 @@ cr_status qsa_score_launch(const cr_geometry* g, const cr_qsa_args* spans, int n
   return CR_OK;
 }
 
-// Picks the register budget from the largest block count of the launch.
+// Picks the values held per thread from the largest block count of the launch.
 template <typename F>
 static cr_status topk_dispatch(int nb_max, F&& launch) {
   if (nb_max <= 8192) return launch(std::integral_constant<int, 8>{}, std::true_type{});
