@@ -171,6 +171,38 @@ __global__ void __launch_bounds__(256, 2) gdn_chunk_local_kernel(GdnPrefillParam
     stage_issue<true, 128>(P, C, r0, kh * 128, RB);
     stage_issue<true, 128>(P, C, r0, KW + kh * 128, RB2);
   }
+  // Gates while the first tiles are in flight: g = -exp(A_log) softplus(a + dt_bias), beta = sigmoid(b), prefix sum of
+  // g inside the chunk; one warp per value head.  The tables are read after later barriers.
+  if (w < rep) {
+    const int h = kh * rep + w;
+    const float A = -expf(a.A_log[h]), dtb = a.dt_bias[h];
+    float gv[2], bv[2];
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int i = 2 * l + k;
+      gv[k] = 0.f; bv[k] = 0.f;
+      if (i < valid) {
+        const float sp = load_in<BF16>(P.ab_logits, (long long)(r0 + i) * 2 * P.Hv + h) + dtb;
+        gv[k] = A * (sp > 20.f ? sp : log1pf(expf(sp)));
+        bv[k] = sigmoidf_(load_in<BF16>(P.ab_logits, (long long)(r0 + i) * 2 * P.Hv + P.Hv + h));
+      }
+    }
+    float s = gv[0] + gv[1];
+#pragma unroll
+    for (int step = 1; step < 32; step <<= 1) {
+      const float v = __shfl_up_sync(0xffffffffu, s, step);
+      if (l >= step) s += v;
+    }
+    const float G1 = s, G0 = s - gv[1];
+    float* Gw = Gs + w * 64; float* bw = bs + w * 64; float* ew = es + w * 64;
+    Gw[2 * l] = G0; Gw[2 * l + 1] = G1; bw[2 * l] = bv[0]; bw[2 * l + 1] = bv[1];
+    const float e0 = __expf(G0), e1 = __expf(G1), Gend = __shfl_sync(0xffffffffu, G1, 31);
+    ew[2 * l] = bv[0] * e0; ew[2 * l + 1] = bv[1] * e1;
+    egs[w * 64 + 2 * l] = e0; egs[w * 64 + 2 * l + 1] = e1;
+    scs[w * 64 + 2 * l] = __expf(Gend - G0); scs[w * 64 + 2 * l + 1] = __expf(Gend - G1);
+    float* Gg = ws.G + ((size_t)h * ws.chunks + c) * 64;
+    Gg[2 * l] = G0; Gg[2 * l + 1] = G1;
+  }
   for (int part = 0; part < 2; ++part) {
     float* dst = part ? Ks : Qs;
     for (int round = 0; round < 128 / CH; ++round) {
@@ -223,36 +255,6 @@ __global__ void __launch_bounds__(256, 2) gdn_chunk_local_kernel(GdnPrefillParam
       *reinterpret_cast<float4*>(P.qn + ((size_t)(r0 + row) * P.Hk + kh) * 128 + c4) = q;
       *reinterpret_cast<float4*>(P.kn + ((size_t)(r0 + row) * P.Hk + kh) * 128 + c4) = k;
     }
-  }
-  if (w < rep) {   // g = -exp(A_log) softplus(a + dt_bias), beta = sigmoid(b); prefix sum; one warp per value head
-    const int h = kh * rep + w;
-    const float A = -expf(a.A_log[h]), dtb = a.dt_bias[h];
-    float gv[2], bv[2];
-#pragma unroll
-    for (int k = 0; k < 2; ++k) {
-      const int i = 2 * l + k;
-      gv[k] = 0.f; bv[k] = 0.f;
-      if (i < valid) {
-        const float sp = load_in<BF16>(P.ab_logits, (long long)(r0 + i) * 2 * P.Hv + h) + dtb;
-        gv[k] = A * (sp > 20.f ? sp : log1pf(expf(sp)));
-        bv[k] = sigmoidf_(load_in<BF16>(P.ab_logits, (long long)(r0 + i) * 2 * P.Hv + P.Hv + h));
-      }
-    }
-    float s = gv[0] + gv[1];
-#pragma unroll
-    for (int step = 1; step < 32; step <<= 1) {
-      const float v = __shfl_up_sync(0xffffffffu, s, step);
-      if (l >= step) s += v;
-    }
-    const float G1 = s, G0 = s - gv[1];
-    float* Gw = Gs + w * 64; float* bw = bs + w * 64; float* ew = es + w * 64;
-    Gw[2 * l] = G0; Gw[2 * l + 1] = G1; bw[2 * l] = bv[0]; bw[2 * l + 1] = bv[1];
-    const float e0 = __expf(G0), e1 = __expf(G1), Gend = __shfl_sync(0xffffffffu, G1, 31);
-    ew[2 * l] = bv[0] * e0; ew[2 * l + 1] = bv[1] * e1;
-    egs[w * 64 + 2 * l] = e0; egs[w * 64 + 2 * l + 1] = e1;
-    scs[w * 64 + 2 * l] = __expf(Gend - G0); scs[w * 64 + 2 * l + 1] = __expf(Gend - G1);
-    float* Gg = ws.G + ((size_t)h * ws.chunks + c) * 64;
-    Gg[2 * l] = G0; Gg[2 * l + 1] = G1;
   }
   __syncthreads();
   if constexpr (UM) {
