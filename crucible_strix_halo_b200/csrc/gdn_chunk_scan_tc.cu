@@ -39,12 +39,13 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 
 __global__ void __launch_bounds__(kScanThreads, 1) gdn_chunk_scan_tc_kernel(GdnPrefillParams P, ChunkWs ws) {
   extern __shared__ __align__(128) float sm[];
-  __shared__ __align__(8) uint64_t bars[10];
+  __shared__ __align__(8) uint64_t bars[12];
   __shared__ uint32_t tmem_slot;
   __shared__ volatile int dead;
   uint64_t* full = &bars[0];                               // one per stage: all three tiles of a chunk
   uint64_t *d1 = &bars[4], *d2 = &bars[5], *d3 = &bars[6];
   uint64_t *uReady = &bars[8], *sReady = &bars[9];
+  uint64_t* empty = &bars[10];                             // one per stage: every MMA that read the stage has completed
   uint64_t* yDone = &bars[2];                              // one per D1 accumulator
   const int t = threadIdx.x, w = t >> 5, l = t & 31;
   constexpr int kIssuer = 4 * kWG, kLoader = kIssuer + 1;
@@ -57,6 +58,8 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_chunk_scan_tc_kernel(GdnP
     umma::mbar_init(d1, 1);
     umma::mbar_init(d2, 1);
     umma::mbar_init(d3, 1);
+    umma::mbar_init(&empty[0], 1);
+    umma::mbar_init(&empty[1], 1);
     umma::mbar_init(uReady, 4 * kWG);                      // one arrival per compute warp
     umma::mbar_init(sReady, 4 * kWG);
     umma::mbar_init(&yDone[0], 4 * kWG);
@@ -115,8 +118,11 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_chunk_scan_tc_kernel(GdnP
       for (int c = 0; c < 2 + kLead; ++c) prefetch(c);
       load(0);
       if (nch > 1) load(1);
-      for (int c = 0; c + 2 < nch; ++c) {   // the stage of chunk c is free once every MMA of chunk c has completed
-        wait(d3, c & 1);
+      // The stage of chunk c is free once every MMA of chunk c has completed.  Each stage has its own barrier, which
+      // completes once per use of the stage and cannot complete again before this warp has refilled the stage: a
+      // loader that falls behind never sees a phase it was not waiting for.
+      for (int c = 0; c + 2 < nch; ++c) {
+        wait(&empty[c & 1], (c >> 1) & 1);
         load(c + 2);
         prefetch(c + 2 + kLead);
       }
@@ -146,6 +152,7 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_chunk_scan_tc_kernel(GdnP
 #pragma unroll
         for (int s8 = 0; s8 < 8; ++s8) umma::mma_tf32_ts(tm + cD1 + 64, tm + cD1 + 8 * s8, dQK + (uint64_t)(s8 * 128), idesc64, 1u);
         umma::commit(d3);
+        umma::commit(&empty[s]);
         if (c + 1 < nch) {   // off the chain: the next tiles arrive early, and Y of chunk c - 1 left its accumulator long ago
           wait(&full[(c + 1) & 1], ((c + 1) >> 1) & 1);
           if (c > 0) wait(&yDone[(c + 1) & 1], (((c + 1) >> 1) - 1) & 1);

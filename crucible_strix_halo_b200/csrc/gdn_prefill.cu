@@ -377,6 +377,7 @@ extern "C" cr_status cr_gdn_prefill(const cr_geometry* g, const cr_gdn_prefill_a
     P.tf32 = 0;
     P.halo_in = p0 > 0;
 
+
     gdn_workspace_layout(g, part_rows, &P, (char*)args->workspace + (size_t)buf * part_bytes);
     if (args->raw_y) P.yraw = args->raw_y + (size_t)p0 * VWs;
   };

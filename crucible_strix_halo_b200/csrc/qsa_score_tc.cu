@@ -212,8 +212,17 @@ cr_status qsa_score_tc_launch(const QsaParams& P, int Rmax, int n, cudaStream_t 
   int sm_count = 148;
   int dev = 0;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
-  int splits = sm_count / (row_tiles * n);                 // one CTA per SM (192 KB of shared memory, all of TMEM)
-  splits = splits < 1 ? 1 : (splits > 64 ? 64 : splits);
+  // One CTA per SM (192 KB of shared memory, all of TMEM).  The pool tiles of a row tile are dealt to `splits` CTAs;
+  // with w waves of CTAs the kernel lasts about w / splits of one row tile's work: take the best of 1 to 3 waves.
+  int splits = 1;
+  double best = 1e30;
+  for (int wv = 1; wv <= 3; ++wv) {
+    int sp = wv * sm_count / (row_tiles * n);
+    sp = sp < 1 ? 1 : (sp > 64 ? 64 : sp);
+    const int waves = (row_tiles * n * sp + sm_count - 1) / sm_count;
+    const double cost = (double)waves / sp;
+    if (cost < best - 1e-9) { best = cost; splits = sp; }
+  }
   qsa_score_tc_kernel<<<dim3(row_tiles, splits, n), kScThreads, kScoreSmem, stream>>>(P);
   CR_LAUNCH_CHECK("qsa_score_tc_kernel");
   return CR_OK;
