@@ -34,7 +34,7 @@ GDN_BYTES_PER_TOKEN = (8192 + 4096) * 2 + 4096 * 2 + 2 * 32 * 4      # bf16 qkv 
 NCU_TRAFFIC = {
     "gdn_prefill_32k": {"gdn_chunk_scan_tc_kernel": ("token", (526.546e6 + 102.534e6) / 7104),
                         "gdn_chunk_local_kernel": ("token", (120.665e6 + 465.678e6) / 7104),
-                        "gdn_gate_kernel": ("token", (174.600e6 + 39.643e6) / 7104)},
+                        "gdn_gate_kernel": ("token", (174.630e6 + 38.259e6) / 7104)},
     "decode_262k": {"qsa_score_kernel": ("step", 134.26e6 + 4.22e6), "qsa_attn_split_kernel": ("step", 16.88e6),
                     "qsa_topk_cluster_kernel": ("step", 1.07e6), "qsa_merge_kernel": ("step", 2.20e6), "qsa_prep_kernel": ("step", 0.13e6),
                     "gdn_step_kernel": ("step", 9.47e6)},

@@ -21,6 +21,16 @@ namespace cr {
 // launched the plain way.  CR_NO_PDL=1 in the environment turns the launch attribute off.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_release() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+// True the first time it is called for the current device with a given flag set: function attributes such as the
+// dynamic shared-memory limit belong to a device, so launchers set them once per device, not once per process.
+struct PerDeviceOnce { bool done[64] = {}; };
+inline bool first_use_on_device(PerDeviceOnce& f) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return true;
+  if (f.done[dev]) return false;
+  f.done[dev] = true;
+  return true;
+}
 inline bool pdl_enabled() {
   static const bool on = getenv("CR_NO_PDL") == nullptr;
   return on;

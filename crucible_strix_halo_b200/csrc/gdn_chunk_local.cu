@@ -403,13 +403,12 @@ __global__ void __launch_bounds__(256, 2) gdn_chunk_local_kernel(GdnPrefillParam
 
 cr_status gdn_chunk_local_launch(const cr_geometry* g, const GdnPrefillParams& P, const ChunkWs& ws, bool bf16_in, bool umma_layout,
                                  cudaStream_t stream) {
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;
+  if (first_use_on_device(configured)) {
     CR_CUDA(cudaFuncSetAttribute(gdn_chunk_local_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kLocalSmem));
     CR_CUDA(cudaFuncSetAttribute(gdn_chunk_local_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kLocalSmem));
     CR_CUDA(cudaFuncSetAttribute(gdn_chunk_local_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kLocalSmem));
     CR_CUDA(cudaFuncSetAttribute(gdn_chunk_local_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kLocalSmem));
-    configured = true;
   }
   const dim3 grid(ws.chunks, g->gdn_kheads);
   if (bf16_in && umma_layout) gdn_chunk_local_kernel<true, true><<<grid, 256, kLocalSmem, stream>>>(P, ws);

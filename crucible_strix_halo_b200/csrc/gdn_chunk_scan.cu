@@ -160,10 +160,9 @@ __global__ void __launch_bounds__(256) gdn_chunk_scan_kernel(GdnPrefillParams P,
 // slice width: CR_GDN_SCAN_NC=32|64 overrides (for experiments).  32 is the default: twice the CTAs on a chain
 // that is latency-bound measured faster (1.8 ms against 2.6 ms for 32768 tokens) than halving the operand re-reads.
 cr_status gdn_chunk_scan_launch(const cr_geometry* g, const GdnPrefillParams& P, const ChunkWs& ws, cudaStream_t stream) {
-  static int nc = 0;
-  if (!nc) {
-    const char* e = getenv("CR_GDN_SCAN_NC");
-    nc = (e && atoi(e) == 64) ? 64 : 32;
+  static const int nc = [] { const char* e = getenv("CR_GDN_SCAN_NC"); return (e && atoi(e) == 64) ? 64 : 32; }();
+  static PerDeviceOnce configured;
+  if (first_use_on_device(configured)) {
     CR_CUDA(cudaFuncSetAttribute(gdn_chunk_scan_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ScanSmem<32>::kBytes));
     CR_CUDA(cudaFuncSetAttribute(gdn_chunk_scan_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ScanSmem<64>::kBytes));
   }

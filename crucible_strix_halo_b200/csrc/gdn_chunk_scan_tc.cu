@@ -237,10 +237,9 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_chunk_scan_tc_kernel(GdnP
 }
 
 cr_status gdn_chunk_scan_tc_launch(const cr_geometry* g, const GdnPrefillParams& P, const ChunkWs& ws, cudaStream_t stream) {
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;
+  if (first_use_on_device(configured)) {
     CR_CUDA(cudaFuncSetAttribute(gdn_chunk_scan_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kScanSmem));
-    configured = true;
   }
   gdn_chunk_scan_tc_kernel<<<g->gdn_vheads, kScanThreads, kScanSmem, stream>>>(P, ws);
   CR_LAUNCH_CHECK("gdn_chunk_scan_tc_kernel");

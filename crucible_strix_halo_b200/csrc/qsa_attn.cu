@@ -295,11 +295,10 @@ cr_status qsa_attn_launch(const cr_geometry* g, const cr_qsa_args* spans, int n_
     qsa_fill_params(P, g, spans + s0, n);
     for (int s = 0; s < n; ++s) P.base[s] += row_base;
     const int Rmax = qsa_max_rows(spans + s0, n);
-    static bool configured = false;
-    if (!configured) {
+    static PerDeviceOnce configured;
+    if (first_use_on_device(configured)) {
       CR_CUDA(cudaFuncSetAttribute(qsa_attn_split_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(SplitSmem<1>)));
       CR_CUDA(cudaFuncSetAttribute(qsa_attn_split_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(SplitSmem<2>)));
-      configured = true;
     }
     const dim3 grid(splits, Rmax * g->kv_heads, n);
     if ((long long)grid.x * grid.y * grid.z > 1024)

@@ -203,10 +203,9 @@ __global__ void __launch_bounds__(kScThreads, 1) qsa_score_tc_kernel(const __gri
 }
 
 cr_status qsa_score_tc_launch(const QsaParams& P, int Rmax, int n, cudaStream_t stream) {
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;
+  if (first_use_on_device(configured)) {
     CR_CUDA(cudaFuncSetAttribute(qsa_score_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kScoreSmem));
-    configured = true;
   }
   const int row_tiles = (Rmax + kScRows - 1) / kScRows;
   int sm_count = 148;
