@@ -1,5 +1,5 @@
-// Chunk-64 WY Gated DeltaNet scan: workspace layout and launch order (kernels in gdn_chunk_local.cu and
-// gdn_chunk_scan.cu).
+// Chunk-64 WY Gated DeltaNet scan: workspace layout and launch order (kernels in gdn_chunk_local.cu,
+// gdn_chunk_scan_tc.cu and gdn_chunk_scan.cu).
 #include "gdn_chunk.cuh"
 
 namespace cr {

@@ -1,4 +1,4 @@
-// Shared pieces of the chunk-64 WY Gated DeltaNet scan (gdn_chunk_local.cu, gdn_chunk_scan.cu).
+// Shared pieces of the chunk-64 WY Gated DeltaNet scan (gdn_chunk_local.cu, gdn_chunk_scan_tc.cu, gdn_chunk_scan.cu).
 //
 // The algebra is the reference's chunked form (ref/prefill_ref.py:16-34;
 // engine/layers/kernels/prefill_gdn.h:111-249).  Per chunk of 64 tokens and value head, with G the cumulative

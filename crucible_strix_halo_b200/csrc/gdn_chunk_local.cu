@@ -1,14 +1,17 @@
 // gdn_chunk_local_kernel: everything of the chunk-64 WY scan that does not depend on the carried state, fully
 // parallel over (chunk, key head).  Per CTA:
-//   1. raw projection rows of the key head's q and k channels are staged in shared memory with 128-bit loads
-//      (3 halo rows from the previous rows, the ring, or zero), then conv(4) + SiLU + L2 norm -> qhat, khat (tf32);
+//   1. raw projection rows of the key head's q and k channels are staged in shared memory with cp.async (3 halo rows
+//      from the previous rows, the ring, or zero; with bf16 inputs the next tile is always in flight while the
+//      current one is used), then conv(4) + SiLU + L2 norm -> qhat, khat (tf32); the gates (log-decay prefix G, beta
+//      and their exponential tables) of the value heads are computed while the first tiles arrive;
 //   2. Gram matrices K K^T and Q K^T on tensor cores, kept in accumulator registers for all value heads;
-//   3. per value head: log-decay prefix G and beta, L = tril(beta K K^T e^{dG}, -1), QKd = tril(Q K^T e^{dG}), and
+//   3. per value head: K'^T = (e^{G_end - G} K)^T and e^G Q tiles, L = tril(beta K K^T e^{dG}, -1), QKd = tril(Q K^T e^{dG}), and
 //      T = (I + L)^-1 by an exact fp32 blocked inverse (16 x 16 diagonal blocks by substitution, off-diagonal blocks
 //      in block-row order), then W = T (beta e^G K) and Ut = T (beta V) on tensor cores with tf32 operands; the
 //      v columns run conv + SiLU from the staged raw rows.
 // Outputs go straight into the layouts the scan consumes (K-major tiles for the tcgen05 scan).
-// Two CTAs fit per SM (106 KB of shared memory each), so one CTA's loads hide behind the other's math.
+// Two CTAs fit per SM (110 KB of shared memory, 128 registers x 256 threads each), so one CTA's barriers and loads
+// hide behind the other's math.
 #include "gdn_chunk.cuh"
 
 namespace cr {
