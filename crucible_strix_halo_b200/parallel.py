@@ -1,7 +1,7 @@
 """Multi-GPU partitioning of the attention path: one process per GPU, torch.distributed for the exchange.
 
 Natural shards need no exchange: sessions (decode / verify) and sequences (prefill) are independent, GDN value
-heads are independent recurrences.  One long sequence of the QSA layer is split over the KV positions:
+heads are independent recurrences (GdnHeadShard).  One long sequence of the QSA layer is split over the KV positions:
 
     rank g owns positions [lo_g, hi_g)  (whole 4-token blocks; the newest rows belong to the last rank)
     1. local scores + top-512 candidates over the owned blocks          cr_qsa_shard_candidates
@@ -33,6 +33,40 @@ def kv_block_range(total_positions, world, rank, block=4):
     if rank == world - 1:
         p1 = 1 << 30
     return (b0, b1), (p0, p1)
+
+
+class GdnHeadShard:
+    """Value heads of a GDN layer dealt to ranks with no exchange: each value head is an independent recurrence, and
+    the rep = Hv / Hk value heads that share a key head stay together (engine/layers/ops.h:258).  The shard is
+    itself a GDN layer of vheads x kheads heads: `qkv_columns` picks its channels out of a projection row
+    [q heads | k heads | v heads], `value_columns` its slice of z / output rows, `head_slice` its entries of the
+    per-head vectors (A_log, dt_bias, a/b logits) and of the state; conv weights follow `qkv_columns`."""
+
+    def __init__(self, vheads, kheads, world, rank, dim=128):
+        assert vheads % kheads == 0 and kheads >= world, "need at least one key head per rank"
+        rep = vheads // kheads
+        k0, k1 = shard_range(kheads, world, rank)
+        self.k0, self.k1, self.v0, self.v1 = k0, k1, k0 * rep, k1 * rep
+        self.kheads, self.vheads, self.dim = k1 - k0, (k1 - k0) * rep, dim
+        self._full = (vheads, kheads)
+
+    @property
+    def head_slice(self):
+        return slice(self.v0, self.v1)
+
+    @property
+    def value_columns(self):
+        return slice(self.v0 * self.dim, self.v1 * self.dim)
+
+    @property
+    def qkv_columns(self):
+        """Channel indices (ascending) of this shard in a full [q | k | v] row."""
+        vheads, kheads = self._full
+        d = self.dim
+        q = range(self.k0 * d, self.k1 * d)
+        k = range(kheads * d + self.k0 * d, kheads * d + self.k1 * d)
+        v = range(2 * kheads * d + self.v0 * d, 2 * kheads * d + self.v1 * d)
+        return list(q) + list(k) + list(v)
 
 
 class SplitKvQsa:

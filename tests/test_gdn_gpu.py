@@ -264,3 +264,33 @@ def test_prefill_pipelined_call_can_be_captured_in_a_graph():
     assert capi.lib.cr_device_status() == 0
     assert torch.equal(plan.out, eager)
     assert torch.equal(ses.state, st_eager)
+
+
+def test_prefill_head_shards_reproduce_the_full_layer():
+    """GDN value heads shard across GPUs with no exchange (parallel.GdnHeadShard).  Two ranks are emulated one after
+    the other on this device: each runs the tcgen05 prefill on its own heads; outputs and states, put side by side,
+    are bit-identical to the layer run whole."""
+    from crucible_strix_halo_b200 import parallel as par
+    capi, layers, g, og, rng, wts, w = _setup(8, 4, 64, 23)
+    T = 700
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    qkv = torch.randn(T, og.gdn_qkv_width, device="cuda", generator=gen).bfloat16()
+    z = torch.randn(T, og.gdn_value_width, device="cuda", generator=gen).bfloat16()
+    ab = torch.randn(T, 2 * 8, device="cuda", generator=gen).bfloat16()
+    ses = layers.GdnSession(g)
+    full = layers.GdnPrefillPlan(w, T, in_dtype=capi.IN_BF16).run(ses, qkv, z, ab, 0, capi.GDN_CHUNK_TC).clone()
+    full_state = ses.state_view().clone()
+    outs, states = [], []
+    for rank in range(2):
+        sh = par.GdnHeadShard(8, 4, 2, rank)
+        sg = capi.Geometry(64, 16, 2, sh.vheads, sh.kheads)
+        cols, hs = torch.tensor(sh.qkv_columns, device="cuda"), sh.head_slice
+        sw = layers.GdnWeights(sg, wts["conv"][sh.qkv_columns], wts["A_log"][hs], wts["dt_bias"][hs], wts["gamma"])
+        sses = layers.GdnSession(sg)
+        ab_s = torch.cat([ab[:, :8][:, hs], ab[:, 8:][:, hs]], 1).contiguous()
+        out = layers.GdnPrefillPlan(sw, T, in_dtype=capi.IN_BF16).run(sses, qkv[:, cols].contiguous(), z[:, sh.value_columns].contiguous(),
+                                                                   ab_s, 0, capi.GDN_CHUNK_TC)
+        outs.append(out.clone()); states.append(sses.state_view().clone())
+    assert capi.lib.cr_device_status() == 0
+    assert torch.equal(torch.cat(outs, 1), full)
+    assert torch.equal(torch.cat(states, 0), full_state)

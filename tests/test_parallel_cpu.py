@@ -121,3 +121,55 @@ def test_split_kv_two_ranks_equals_single_rank():
     g, cache, norms, rows, ctx0, R = _problem()
     ref = ao.qsa_rows(*rows, norms, cache, ctx0, g)
     np.testing.assert_allclose(out.reshape(R, -1), ref, rtol=1e-6, atol=1e-7)
+
+
+def _gdn_problem():
+    g = ao.Geometry(hidden=64, gdn_vheads=8, gdn_kheads=4)
+    rng = np.random.default_rng(11)
+    n, C = 70, g.gdn_qkv_width
+    return (g, rng.normal(size=(n, C)), rng.normal(size=(n, g.gdn_value_width)), rng.normal(size=(n, 8)), rng.normal(size=(n, 8)),
+            rng.normal(size=(C, 4)) * 0.5, np.clip(rng.normal(-1, 1.5, 8), -5, 1.5), rng.normal(size=8) * 0.5,
+            1 + 0.1 * rng.normal(size=128), rng.normal(size=(8, 128, 128)) * 0.05)
+
+
+def _gdn_worker(rank, world, port, q):
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    g, qkv, z, al, bl, conv, A_log, dtb, gamma, state = _gdn_problem()
+    sh = par.GdnHeadShard(g.gdn_vheads, g.gdn_kheads, world, rank)
+    sg = ao.Geometry(hidden=64, gdn_vheads=sh.vheads, gdn_kheads=sh.kheads)
+    cols, hs = sh.qkv_columns, sh.head_slice
+    out, st, _ = ao.gdn_layer(qkv[:, cols], z[:, sh.value_columns], al[:, hs], bl[:, hs], conv[cols], A_log[hs], dtb[hs], gamma,
+                              state[hs], sg)
+    outs = [torch.empty(len(out), sh.vheads * 128, dtype=torch.float64) for _ in range(world)]     # equal shards here
+    dist.all_gather(outs, torch.from_numpy(np.ascontiguousarray(out)))
+    sts = [torch.empty(sh.vheads, 128, 128, dtype=torch.float64) for _ in range(world)]
+    dist.all_gather(sts, torch.from_numpy(np.ascontiguousarray(st)))
+    if rank == 0:
+        q.put((torch.cat(outs, 1).numpy(), torch.cat(sts, 0).numpy()))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_gdn_head_shards_two_ranks_equal_the_full_layer():
+    """GDN value heads shard with no exchange: every rank runs the layer on its own heads (channels picked by
+    GdnHeadShard), outputs and states are concatenated in rank order."""
+    sh = [par.GdnHeadShard(32, 16, 8, r) for r in range(8)]
+    assert [s.vheads for s in sh] == [4] * 8 and sh[3].v0 == 12 and sh[3].k0 == 6
+    cols = sorted(c for s in sh for c in s.qkv_columns)
+    assert cols == list(range(2 * 16 * 128 + 32 * 128))                       # every channel owned exactly once
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_gdn_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    out, st = q.get(timeout=120)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    g, qkv, z, al, bl, conv, A_log, dtb, gamma, state = _gdn_problem()
+    ref, ref_st, _ = ao.gdn_layer(qkv, z, al, bl, conv, A_log, dtb, gamma, state, g)
+    np.testing.assert_allclose(out, ref, rtol=1e-12, atol=1e-12)
+    np.testing.assert_allclose(st, ref_st, rtol=1e-12, atol=1e-12)
