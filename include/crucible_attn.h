@@ -264,7 +264,9 @@ cr_status cr_qsa_merge_partials(const cr_geometry* g, const cr_qsa_args* a, int 
  * ------------------------------------------------------------------------------------------------- */
 const char* cr_last_error(void);   /* text of the last error on this thread */
 int cr_version(void);
-/* 0, or non-zero if a bounded device-side wait gave up since the library was loaded (synchronises the device). */
+/* 0, or non-zero if a bounded device-side wait gave up since the library was loaded (synchronises the device):
+ * bit 0 = in the tcgen05 GDN scan, bit 1 = in the tcgen05 QSA scoring kernel.  No counterpart in the reference,
+ * whose kernels have no waits that can give up. */
 int cr_device_status(void);
 /* Number of kernels this library has launched in this process (for launch accounting in benches). */
 unsigned long long cr_kernel_launches(void);
