@@ -35,6 +35,8 @@ def build_library(force=False, verbose=False):
     os.makedirs(OBJ, exist_ok=True)
     sources = sorted(glob.glob(os.path.join(CSRC, "*.cu")))
     headers = glob.glob(os.path.join(CSRC, "*.cuh")) + glob.glob(os.path.join(ROOT, "include", "*.h"))
+    if not force and _newer(LIB, sources + headers):      # a shipped library that is newer than every source
+        return LIB
     jobs = []
     for src in sources:
         obj = os.path.join(OBJ, os.path.basename(src)[:-3] + ".o")
