@@ -73,6 +73,7 @@ _protos = {
     "cr_gdn_step": (C.c_int, [G, C.POINTER(GdnArgs), C.c_int, C.c_int, C.c_int, P]),
     "cr_gdn_prefill_workspace_bytes": (C.c_size_t, [G, C.c_int]),
     "cr_gdn_algo_available": (C.c_int, [C.c_int]),
+    "cr_gdn_prefill_parts": (C.c_int, [C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int), C.c_int]),
     "cr_gdn_prefill": (C.c_int, [G, C.POINTER(GdnPrefillArgs), C.c_int, C.c_int, P]),
     "cr_gdn_materialize": (C.c_int, [G, C.POINTER(P), C.c_int, P]),
     "cr_qsa_scratch_bytes": (C.c_size_t, [G, C.c_int]),

@@ -331,6 +331,18 @@ extern "C" size_t cr_gdn_prefill_workspace_bytes(const cr_geometry* g, int rows)
   return rows > cr::gdn_part_rows() ? 2 * part : part;   // a call of several parts works on two workspaces in turn
 }
 
+extern "C" int cr_gdn_prefill_parts(int rows, int* first_row, int* n_rows, int max_parts) {
+  if (rows < 1) return 0;
+  std::vector<std::pair<int, int>> parts;
+  if (rows > cr::gdn_part_rows()) parts = cr::part_schedule(rows, cr::gdn_part_rows());
+  else parts.push_back({0, rows});
+  for (int i = 0; i < (int)parts.size() && i < max_parts; ++i) {
+    if (first_row) first_row[i] = parts[i].first;
+    if (n_rows) n_rows[i] = parts[i].second;
+  }
+  return (int)parts.size();
+}
+
 extern "C" int cr_gdn_algo_available(cr_gdn_algo algo) {
   return algo == CR_GDN_SERIAL_F32 || ((algo == CR_GDN_CHUNK_TC || algo == CR_GDN_CHUNK_MMA) && cr::gdn_chunk_available());
 }

@@ -122,6 +122,11 @@ typedef struct {
 size_t cr_gdn_prefill_workspace_bytes(const cr_geometry* g, int rows);
 /* 1 when this build of the library carries the algorithm. */
 int cr_gdn_algo_available(cr_gdn_algo algo);
+/* The internal parts a CR_GDN_CHUNK_TC call of `rows` rows runs in: writes up to max_parts (first row, row count)
+ * pairs and returns the number of parts (host only, no device work).  Every part but the last is a multiple of 64
+ * rows and none exceeds the part the workspace is sized for.  No counterpart in the reference, whose callers
+ * cut the sequence into 2,048-row parts themselves. */
+int cr_gdn_prefill_parts(int rows, int* first_row, int* n_rows, int max_parts);
 
 /* Replaces LaunchGdnScanGate / LaunchGdnLanes / LaunchGdnPrefill / LaunchGdnMicro + GdnPrefillHistoryKernel
  * (engine/layers/kernels/prefill_gdn.h:1206-1216, :1161, :1229-1279, :274-282): rows pos0..pos0+R-1 of one

@@ -65,3 +65,26 @@ def test_sizing_helpers(capi):
     assert capi.lib.cr_qsa_cache_bytes(C.byref(g), 0, 0, out) == capi.ERR_INVALID
     assert capi.lib.cr_qsa_scratch_bytes(C.byref(g), 1) == 16 * 32 * 258 * 4          # QsaScratchFloats, qsa_long.h:396
     assert capi.lib.cr_gdn_prefill_workspace_bytes(C.byref(g), 2048) > 0
+
+
+def test_gdn_prefill_part_schedule_covers_every_row():
+    """cr_gdn_prefill_parts is host-only: the parts of a long call tile the rows exactly, every part but the last is a
+    whole number of 64-row chunks, none exceeds the part the workspace is sized for, the first is short and the
+    last ones shrink."""
+    import ctypes as C
+    from crucible_strix_halo_b200 import capi
+    part = 111 * 64
+    for rows in (1, 63, 64, 7104, 7105, 8004, 14541, 32768, 100000, 262144):
+        first, n = (C.c_int * 64)(), (C.c_int * 64)()
+        k = capi.lib.cr_gdn_prefill_parts(rows, first, n, 64)
+        assert 1 <= k <= 64
+        assert first[0] == 0 and sum(n[:k]) == rows
+        for i in range(k):
+            assert 1 <= n[i] <= part
+            if i + 1 < k:
+                assert n[i] % 64 == 0 and first[i + 1] == first[i] + n[i]
+        if rows <= part:
+            assert k == 1
+        if rows >= 32768:
+            assert n[0] == 32 * 64 and n[k - 1] <= n[k - 2] <= n[k - 3]
+    assert capi.lib.cr_gdn_prefill_parts(0, None, None, 0) == 0
