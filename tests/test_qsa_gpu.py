@@ -285,3 +285,44 @@ def test_c1_layer_seq4096_with_projections():
             if not np.array_equal(got, sels[o]):
                 continue
         assert_close_attn(out[2048 + r], ref1[o], max_abs=2e-3, cos=0.9999, what="row %d" % (2048 + r))
+
+
+def test_select_long_caches_mixed_spans():
+    """One- and two-row spans over long caches (40,003 and 20,001 blocks) in one cr_qsa_select launch together with
+    a dense span (no scores) and a short sparse one: scores against fp64 dot products of the device's own pool,
+    nothing written past a row's blocks, exact selection on the device's scores."""
+    capi, layers, g, og, rng, norms, suh, w = _setup()
+    shapes = [(4 * 40003 + 1, 2), (1000, 1), (4 * 20001 + 2, 1), (2052, 2)]
+    sess, args, keep = [], (capi.QsaArgs * len(shapes))(), []
+    gen = torch.Generator(device="cuda").manual_seed(7)
+    for i, (pos0, R) in enumerate(shapes):
+        s = layers.QsaSession(g, pos0 + R + 64, max_rows=2)
+        s.ik_pool.copy_(torch.randn(s.ik_pool.shape, device="cuda", generator=gen))
+        q = torch.zeros(R, 16, 512, device="cuda"); kv = torch.zeros(R, 512, device="cuda")
+        idx = torch.randn(R, 640, device="cuda", generator=gen)
+        out = torch.empty(R, 16 * 256, device="cuda")
+        args[i] = layers.qsa_args(w, s, q, kv, kv, idx, out, pos0)
+        sess.append(s); keep.append((q, kv, idx, out))
+
+    def run():
+        for s in sess:
+            s.scores.fill_(-7.0); s.sel.fill_(-3); s.nsel.fill_(-9)
+        capi.check(capi.lib.cr_qsa_select(C.byref(g), args, len(shapes), None, 0, None))
+        torch.cuda.synchronize()
+        return [(s.scores.clone(), s.sel.clone(), s.nsel.clone()) for s in sess]
+
+    got = run()
+    assert capi.lib.cr_device_status() == 0
+    for i, (pos0, R) in enumerate(shapes):
+        sc, sel, nsel = got[i]
+        for r in range(R):
+            nb = (pos0 + r + 1) // 4
+            if nb <= 512:
+                assert int(nsel[r]) == -1
+                continue
+            iq = keep[i][2][r, :512].view(4, 128).double()
+            want = (sess[i].pool_rows(nb).double() @ iq.T).clamp_min(0).sum(-1) * 0.08838834764831845
+            assert (sc[r, :nb].double() - want).abs().max().item() < 2e-4
+            assert (sc[r, nb:] == -7.0).all()                       # nothing written past the row's blocks
+            assert int(nsel[r]) == 512
+            np.testing.assert_array_equal(sel[r].cpu().numpy(), _reference_topk(sc[r, :nb].cpu().numpy()))
