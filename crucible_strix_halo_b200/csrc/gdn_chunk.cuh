@@ -69,6 +69,36 @@ __device__ __forceinline__ void warp_gemm(float (&acc)[NT][4], const float* A, i
   }
 }
 
+// Two products with a lower-triangular A (64 x 64, row-major, lda % 32 == 4) at once: acc_hi = A[rows of block
+// m_hi] B and acc_lo = A[rows of block m_lo] B for 8 NT columns of B ([k][n], ldb % 32 == 8), m_lo < m_hi.  Row
+// block m only needs k < 16 (m + 1), and the B fragments of the common k range are loaded once.  Pairing blocks
+// (3, 0) and (2, 1) gives every warp ten k steps.
+template <int NT>
+__device__ __forceinline__ void warp_gemm_tril_pair(float (&acc_hi)[NT][4], float (&acc_lo)[NT][4], const float* A, int lda,
+                                                    int m_hi, int m_lo, const float* B, int ldb) {
+  const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const float* Ah = A + m_hi * 16 * lda;
+  const float* Al = A + m_lo * 16 * lda;
+  const int k_hi = 2 * (m_hi + 1), k_lo = 2 * (m_lo + 1);
+#pragma unroll 2
+  for (int kk = 0; kk < k_hi; ++kk) {
+    const bool both = kk < k_lo;
+    float ah[4], al[4] = {0.f, 0.f, 0.f, 0.f};
+    ah[0] = Ah[g * lda + kk * 8 + t];       ah[1] = Ah[(g + 8) * lda + kk * 8 + t];
+    ah[2] = Ah[g * lda + kk * 8 + t + 4];   ah[3] = Ah[(g + 8) * lda + kk * 8 + t + 4];
+    if (both) {
+      al[0] = Al[g * lda + kk * 8 + t];     al[1] = Al[(g + 8) * lda + kk * 8 + t];
+      al[2] = Al[g * lda + kk * 8 + t + 4]; al[3] = Al[(g + 8) * lda + kk * 8 + t + 4];
+    }
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+      const float b0 = B[(kk * 8 + t) * ldb + n * 8 + g], b1 = B[(kk * 8 + t + 4) * ldb + n * 8 + g];
+      mma_tf32(acc_hi[n], ah, b0, b1);
+      if (both) mma_tf32(acc_lo[n], al, b0, b1);
+    }
+  }
+}
+
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
   const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
   const int bytes = valid ? 16 : 0;

@@ -331,24 +331,30 @@ __global__ void __launch_bounds__(256, 2) gdn_chunk_local_kernel(GdnPrefillParam
       *p = tf32r(*p);
     }
     __syncthreads();
-    const int nh = w >> 2;
+    // T is lower triangular: row block m needs k < 16 (m + 1).  A warp takes 32 columns of two row blocks, (3, 0) or
+    // (2, 1), ten k steps either way.
+    const int qn = w & 3, m_hi = w < 4 ? 3 : 2, m_lo = w < 4 ? 0 : 1;
     {   // W = T X
-      float acc[8][4];
+      float acc[2][4][4];
 #pragma unroll
-      for (int n = 0; n < 8; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
-      warp_gemm<8, 8, false, false>(acc, LT + mt * 16 * kLdM, kLdM, Qs + nh * 64, kLdX);
+      for (int k = 0; k < 2; ++k)
+#pragma unroll
+        for (int n = 0; n < 4; ++n) acc[k][n][0] = acc[k][n][1] = acc[k][n][2] = acc[k][n][3] = 0.f;
+      warp_gemm_tril_pair<4>(acc[0], acc[1], LT, kLdM, m_hi, m_lo, Qs + qn * 32, kLdX);
       float* dst = UM ? ws.WQ + unit * 16384 : ws.W + unit * 8192;
 #pragma unroll
-      for (int n = 0; n < 8; ++n) {
-        const int col = nh * 64 + n * 8 + 2 * tq, r_lo = mt * 16 + g;
-        if constexpr (UM) {
-          *reinterpret_cast<float2*>(dst + ((col >> 2) * 128 + r_lo) * 4 + (col & 3)) = make_float2(tf32r(acc[n][0]), tf32r(acc[n][1]));
-          *reinterpret_cast<float2*>(dst + ((col >> 2) * 128 + r_lo + 8) * 4 + (col & 3)) = make_float2(tf32r(acc[n][2]), tf32r(acc[n][3]));
-        } else {
-          *reinterpret_cast<float2*>(dst + r_lo * 128 + col) = make_float2(tf32r(acc[n][0]), tf32r(acc[n][1]));
-          *reinterpret_cast<float2*>(dst + (r_lo + 8) * 128 + col) = make_float2(tf32r(acc[n][2]), tf32r(acc[n][3]));
+      for (int k = 0; k < 2; ++k)
+#pragma unroll
+        for (int n = 0; n < 4; ++n) {
+          const int col = qn * 32 + n * 8 + 2 * tq, r_lo = (k ? m_lo : m_hi) * 16 + g;
+          if constexpr (UM) {
+            *reinterpret_cast<float2*>(dst + ((col >> 2) * 128 + r_lo) * 4 + (col & 3)) = make_float2(tf32r(acc[k][n][0]), tf32r(acc[k][n][1]));
+            *reinterpret_cast<float2*>(dst + ((col >> 2) * 128 + r_lo + 8) * 4 + (col & 3)) = make_float2(tf32r(acc[k][n][2]), tf32r(acc[k][n][3]));
+          } else {
+            *reinterpret_cast<float2*>(dst + r_lo * 128 + col) = make_float2(tf32r(acc[k][n][0]), tf32r(acc[k][n][1]));
+            *reinterpret_cast<float2*>(dst + (r_lo + 8) * 128 + col) = make_float2(tf32r(acc[k][n][2]), tf32r(acc[k][n][3]));
+          }
         }
-      }
     }
     __syncthreads();                    // X = beta e^G K consumed
     for (int round = 0; round < 128 / VCH; ++round) {   // X = beta SiLU(conv(v)) from the staged raw rows
@@ -379,25 +385,31 @@ __global__ void __launch_bounds__(256, 2) gdn_chunk_local_kernel(GdnPrefillParam
       if (vi + 1 < rep) stage_issue<true, 128>(P, C, r0, 2 * KW + (h + 1) * 128, RB);
     }
     {   // Ut = T X  (stored fp32: it is added, not multiplied, in the scan)
-      float acc[8][4];
+      float acc[2][4][4];
 #pragma unroll
-      for (int n = 0; n < 8; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
-      warp_gemm<8, 8, false, false>(acc, LT + mt * 16 * kLdM, kLdM, Qs + nh * 64, kLdX);
-      if constexpr (UM) {   // [token / 16][(token % 16) / 4][column][token % 4]: a scan thread owns a column and reads
-                            // four tokens per 128-bit load, a warp 512 contiguous bytes
-        float* dst = ws.Ut + unit * 8192 + (size_t)mt * 2048;
+      for (int k = 0; k < 2; ++k)
 #pragma unroll
-        for (int n = 0; n < 8; ++n) {
-          const int col = nh * 64 + n * 8 + 2 * tq;
-          float* d = dst + (g >> 2) * 512 + col * 4 + (g & 3);
-          d[0] = acc[n][0]; d[4] = acc[n][1]; d[1024] = acc[n][2]; d[1028] = acc[n][3];
-        }
-      } else {
-        float* dst = ws.Ut + (unit * 64 + mt * 16) * 128 + nh * 64;
+        for (int n = 0; n < 4; ++n) acc[k][n][0] = acc[k][n][1] = acc[k][n][2] = acc[k][n][3] = 0.f;
+      warp_gemm_tril_pair<4>(acc[0], acc[1], LT, kLdM, m_hi, m_lo, Qs + qn * 32, kLdX);
 #pragma unroll
-        for (int n = 0; n < 8; ++n) {
-          *reinterpret_cast<float2*>(dst + g * 128 + n * 8 + 2 * tq) = make_float2(acc[n][0], acc[n][1]);
-          *reinterpret_cast<float2*>(dst + (g + 8) * 128 + n * 8 + 2 * tq) = make_float2(acc[n][2], acc[n][3]);
+      for (int k = 0; k < 2; ++k) {
+        const int mt2 = k ? m_lo : m_hi;
+        if constexpr (UM) {   // [token / 16][(token % 16) / 4][column][token % 4]: a scan thread owns a column and reads
+                              // four tokens per 128-bit load, a warp 512 contiguous bytes
+          float* dst = ws.Ut + unit * 8192 + (size_t)mt2 * 2048;
+#pragma unroll
+          for (int n = 0; n < 4; ++n) {
+            const int col = qn * 32 + n * 8 + 2 * tq;
+            float* d = dst + (g >> 2) * 512 + col * 4 + (g & 3);
+            d[0] = acc[k][n][0]; d[4] = acc[k][n][1]; d[1024] = acc[k][n][2]; d[1028] = acc[k][n][3];
+          }
+        } else {
+          float* dst = ws.Ut + (unit * 64 + mt2 * 16) * 128 + qn * 32;
+#pragma unroll
+          for (int n = 0; n < 4; ++n) {
+            *reinterpret_cast<float2*>(dst + g * 128 + n * 8 + 2 * tq) = make_float2(acc[k][n][0], acc[k][n][1]);
+            *reinterpret_cast<float2*>(dst + (g + 8) * 128 + n * 8 + 2 * tq) = make_float2(acc[k][n][2], acc[k][n][3]);
+          }
         }
       }
     }
