@@ -69,6 +69,43 @@ __device__ __forceinline__ void warp_gemm(float (&acc)[NT][4], const float* A, i
   }
 }
 
+// Four 8 x 4 pieces of tf32 values (8 rows of 16 bytes each) in one instruction: lane L passes the address of row
+// L % 8 of piece L / 8 and receives element (L / 4, L % 4) of every piece, which is the layout of the m16n8k8
+// fragments.  Rows must be 16-byte aligned.
+__device__ __forceinline__ void ldmatrix4(float (&v)[4], const float* row) {
+  unsigned r0, r1, r2, r3;
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"((unsigned)__cvta_generic_to_shared(row)));
+  v[0] = __uint_as_float(r0); v[1] = __uint_as_float(r1); v[2] = __uint_as_float(r2); v[3] = __uint_as_float(r3);
+}
+// Address of this lane's row for the A fragment of rows [0, 16) x k [k0, k0 + 8) of a row-major tile.
+__device__ __forceinline__ const float* ldm_a_row(const float* A, int lda, int k0) {
+  const int lane = threadIdx.x & 31, j = lane >> 3, r = lane & 7;
+  return A + ((j & 1) * 8 + r) * lda + k0 + (j >> 1) * 4;
+}
+
+// acc[16 x 8NT] += A B^T with A [16][8KT] and B [8NT][8KT] both row-major over k (strides % 32 == 4), fragments
+// by ldmatrix: one instruction for A and one per two column tiles of B per k step.  NT even.
+template <int NT, int KT>
+__device__ __forceinline__ void warp_gemm_nk_ldm(float (&acc)[NT][4], const float* A, int lda, const float* B, int ldb) {
+  const int lane = threadIdx.x & 31, j = lane >> 3, r = lane & 7;
+  const float* arow = ldm_a_row(A, lda, 0);
+  const float* brow = B + ((j >> 1) * 8 + r) * ldb + (j & 1) * 4;
+#pragma unroll
+  for (int kk = 0; kk < KT; ++kk) {
+    float a[4];
+    ldmatrix4(a, arow + kk * 8);
+#pragma unroll
+    for (int n = 0; n < NT; n += 2) {
+      float b[4];
+      ldmatrix4(b, brow + n * 8 * ldb + kk * 8);
+      mma_tf32(acc[n], a, b[0], b[1]);
+      mma_tf32(acc[n + 1], a, b[2], b[3]);
+    }
+  }
+}
+
 // Two products with a lower-triangular A (64 x 64, row-major, lda % 32 == 4) at once: acc_hi = A[rows of block
 // m_hi] B and acc_lo = A[rows of block m_lo] B for 8 NT columns of B ([k][n], ldb % 32 == 8), m_lo < m_hi.  Row
 // block m only needs k < 16 (m + 1), and the B fragments of the common k range are loaded once.  Pairing blocks
@@ -77,19 +114,15 @@ template <int NT>
 __device__ __forceinline__ void warp_gemm_tril_pair(float (&acc_hi)[NT][4], float (&acc_lo)[NT][4], const float* A, int lda,
                                                     int m_hi, int m_lo, const float* B, int ldb) {
   const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-  const float* Ah = A + m_hi * 16 * lda;
-  const float* Al = A + m_lo * 16 * lda;
+  const float* Ah = ldm_a_row(A + m_hi * 16 * lda, lda, 0);   // this lane's fragment rows
+  const float* Al = ldm_a_row(A + m_lo * 16 * lda, lda, 0);
   const int k_hi = 2 * (m_hi + 1), k_lo = 2 * (m_lo + 1);
 #pragma unroll 2
   for (int kk = 0; kk < k_hi; ++kk) {
     const bool both = kk < k_lo;
     float ah[4], al[4] = {0.f, 0.f, 0.f, 0.f};
-    ah[0] = Ah[g * lda + kk * 8 + t];       ah[1] = Ah[(g + 8) * lda + kk * 8 + t];
-    ah[2] = Ah[g * lda + kk * 8 + t + 4];   ah[3] = Ah[(g + 8) * lda + kk * 8 + t + 4];
-    if (both) {
-      al[0] = Al[g * lda + kk * 8 + t];     al[1] = Al[(g + 8) * lda + kk * 8 + t];
-      al[2] = Al[g * lda + kk * 8 + t + 4]; al[3] = Al[(g + 8) * lda + kk * 8 + t + 4];
-    }
+    ldmatrix4(ah, Ah + kk * 8);
+    if (both) ldmatrix4(al, Al + kk * 8);
 #pragma unroll
     for (int n = 0; n < NT; ++n) {
       const float b0 = B[(kk * 8 + t) * ldb + n * 8 + g], b1 = B[(kk * 8 + t + 4) * ldb + n * 8 + g];

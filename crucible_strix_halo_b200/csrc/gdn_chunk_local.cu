@@ -287,7 +287,7 @@ __global__ void __launch_bounds__(256, 2) gdn_chunk_local_kernel(GdnPrefillParam
   float gram[8][4];
 #pragma unroll
   for (int n = 0; n < 8; ++n) gram[n][0] = gram[n][1] = gram[n][2] = gram[n][3] = 0.f;
-  warp_gemm<8, 16, false, true>(gram, (w < 4 ? Ks : Qs) + mt * 16 * kLdK, kLdK, Ks, kLdK);
+  warp_gemm_nk_ldm<8, 16>(gram, (w < 4 ? Ks : Qs) + mt * 16 * kLdK, kLdK, Ks, kLdK);
 
   // ---- 3. per value head
   for (int vi = 0; vi < rep; ++vi) {
