@@ -109,8 +109,8 @@ __device__ __forceinline__ void warp_gemm_nk_ldm(float (&acc)[NT][4], const floa
 // Two products with a lower-triangular A (64 x 64, row-major, lda % 32 == 4) at once: acc_hi = A[rows of block
 // m_hi] B and acc_lo = A[rows of block m_lo] B for 8 NT columns of B ([k][n], ldb % 32 == 8), m_lo < m_hi.  Row
 // block m only needs k < 16 (m + 1), and the B fragments of the common k range are loaded once.  Pairing blocks
-// (3, 0) and (2, 1) gives every warp ten k steps.
-template <int NT>
+// (3, 0) and (2, 1) gives every warp ten k steps.  ROUND_A: A holds fp32 values that are rounded to tf32 as they are loaded.
+template <int NT, bool ROUND_A>
 __device__ __forceinline__ void warp_gemm_tril_pair(float (&acc_hi)[NT][4], float (&acc_lo)[NT][4], const float* A, int lda,
                                                     int m_hi, int m_lo, const float* B, int ldb) {
   const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
@@ -123,6 +123,10 @@ __device__ __forceinline__ void warp_gemm_tril_pair(float (&acc_hi)[NT][4], floa
     float ah[4], al[4] = {0.f, 0.f, 0.f, 0.f};
     ldmatrix4(ah, Ah + kk * 8);
     if (both) ldmatrix4(al, Al + kk * 8);
+    if constexpr (ROUND_A) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { ah[i] = tf32r(ah[i]); al[i] = tf32r(al[i]); }
+    }
 #pragma unroll
     for (int n = 0; n < NT; ++n) {
       const float b0 = B[(kk * 8 + t) * ldb + n * 8 + g], b1 = B[(kk * 8 + t + 4) * ldb + n * 8 + g];

@@ -325,12 +325,7 @@ __global__ void __launch_bounds__(256, 2) gdn_chunk_local_kernel(GdnPrefillParam
     if constexpr (BF16) cp_async_wait_all();
     else stage_raw<BF16, VCH>(P, C, r0, 2 * KW + h * 128, RB);
     __syncthreads();
-    invert_unit_lower_64(LT, Ms);
-    for (int i = t; i < 64 * 64; i += 256) {
-      float* p = LT + (i >> 6) * kLdM + (i & 63);
-      *p = tf32r(*p);
-    }
-    __syncthreads();
+    invert_unit_lower_64(LT, Ms);       // ends with a barrier; T stays fp32 and is rounded as the products load it
     // T is lower triangular: row block m needs k < 16 (m + 1).  A warp takes 32 columns of two row blocks, (3, 0) or
     // (2, 1), ten k steps either way.
     const int qn = w & 3, m_hi = w < 4 ? 3 : 2, m_lo = w < 4 ? 0 : 1;
@@ -340,7 +335,7 @@ __global__ void __launch_bounds__(256, 2) gdn_chunk_local_kernel(GdnPrefillParam
       for (int k = 0; k < 2; ++k)
 #pragma unroll
         for (int n = 0; n < 4; ++n) acc[k][n][0] = acc[k][n][1] = acc[k][n][2] = acc[k][n][3] = 0.f;
-      warp_gemm_tril_pair<4>(acc[0], acc[1], LT, kLdM, m_hi, m_lo, Qs + qn * 32, kLdX);
+      warp_gemm_tril_pair<4, true>(acc[0], acc[1], LT, kLdM, m_hi, m_lo, Qs + qn * 32, kLdX);
       float* dst = UM ? ws.WQ + unit * 16384 : ws.W + unit * 8192;
 #pragma unroll
       for (int k = 0; k < 2; ++k)
@@ -390,7 +385,7 @@ __global__ void __launch_bounds__(256, 2) gdn_chunk_local_kernel(GdnPrefillParam
       for (int k = 0; k < 2; ++k)
 #pragma unroll
         for (int n = 0; n < 4; ++n) acc[k][n][0] = acc[k][n][1] = acc[k][n][2] = acc[k][n][3] = 0.f;
-      warp_gemm_tril_pair<4>(acc[0], acc[1], LT, kLdM, m_hi, m_lo, Qs + qn * 32, kLdX);
+      warp_gemm_tril_pair<4, true>(acc[0], acc[1], LT, kLdM, m_hi, m_lo, Qs + qn * 32, kLdX);
 #pragma unroll
       for (int k = 0; k < 2; ++k) {
         const int mt2 = k ? m_lo : m_hi;
