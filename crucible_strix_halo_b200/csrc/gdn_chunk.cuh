@@ -88,7 +88,8 @@ __device__ __forceinline__ const float* ldm_a_row(const float* A, int lda, int k
 // acc[16 x 8NT] += A B^T with A [16][8KT] and B [8NT][8KT] both row-major over k (strides % 32 == 4), fragments
 // by ldmatrix: one instruction for A and one per two column tiles of B per k step.  NT even.
 template <int NT, int KT>
-__device__ __forceinline__ void warp_gemm_nk_ldm(float (&acc)[NT][4], const float* A, int lda, const float* B, int ldb) {
+__device__ __forceinline__ void warp_gemm_nk_ldm(float (&acc)[NT][4], const float* A, int lda, const float* B, int ldb,
+                                                 int n_used = NT) {   // column tiles [n_used, NT) are left untouched (n_used even)
   const int lane = threadIdx.x & 31, j = lane >> 3, r = lane & 7;
   const float* arow = ldm_a_row(A, lda, 0);
   const float* brow = B + ((j >> 1) * 8 + r) * ldb + (j & 1) * 4;
@@ -98,6 +99,7 @@ __device__ __forceinline__ void warp_gemm_nk_ldm(float (&acc)[NT][4], const floa
     ldmatrix4(a, arow + kk * 8);
 #pragma unroll
     for (int n = 0; n < NT; n += 2) {
+      if (n >= n_used) break;
       float b[4];
       ldmatrix4(b, brow + n * 8 * ldb + kk * 8);
       mma_tf32(acc[n], a, b[0], b[1]);

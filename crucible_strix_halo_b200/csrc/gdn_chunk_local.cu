@@ -287,7 +287,8 @@ __global__ void __launch_bounds__(256, 2) gdn_chunk_local_kernel(GdnPrefillParam
   float gram[8][4];
 #pragma unroll
   for (int n = 0; n < 8; ++n) gram[n][0] = gram[n][1] = gram[n][2] = gram[n][3] = 0.f;
-  warp_gemm_nk_ldm<8, 16>(gram, (w < 4 ? Ks : Qs) + mt * 16 * kLdK, kLdK, Ks, kLdK);
+  const int n_used = 2 * mt + 2;        // column tiles at or below the diagonal of row block mt; the rest is masked
+  warp_gemm_nk_ldm<8, 16>(gram, (w < 4 ? Ks : Qs) + mt * 16 * kLdK, kLdK, Ks, kLdK, n_used);
 
   // ---- 3. per value head
   for (int vi = 0; vi < rep; ++vi) {
@@ -302,6 +303,10 @@ __global__ void __launch_bounds__(256, 2) gdn_chunk_local_kernel(GdnPrefillParam
 #pragma unroll
         for (int hrow = 0; hrow < 2; ++hrow) {
           const int row = mt * 16 + g + 8 * hrow, col = n * 8 + 2 * tq;
+          if (n >= n_used) {            // above the diagonal: nothing reads L there, QKd is zero
+            if (w >= 4) *reinterpret_cast<float2*>(qkd + (UM ? ((col >> 2) * 64 + row) * 4 + (col & 3) : row * 64 + col)) = make_float2(0.f, 0.f);
+            continue;
+          }
           const float Gr = Gv[row];
           const float p0 = __expf(fminf(Gr - Gv[col], 0.f)), p1 = __expf(fminf(Gr - Gv[col + 1], 0.f));
           const float v0 = gram[n][2 * hrow], v1 = gram[n][2 * hrow + 1];
