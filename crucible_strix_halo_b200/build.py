@@ -14,7 +14,7 @@ CSRC = os.path.join(PKG, "csrc")
 OBJ = os.path.join(PKG, "build")
 LIB = os.path.join(PKG, "libcrucible_attn.so")
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-              "-Xcompiler", "-fPIC", "--use_fast_math" if False else "-Xptxas", "-v" if False else "-O3"]
+              "-Xcompiler", "-fPIC", "-Xptxas", "-O3"]
 
 
 def _newer(dst, srcs):
