@@ -11,7 +11,7 @@ A step is one pass of the hot path over one batch of synthetic input.  Workloads
 Under torchrun (N > 1) every rank runs the same workload on its own sequences / sessions (weak scaling, no
 data-path collective); time is the max over ranks, value the whole-job throughput.
 Prints ONE JSON line (rank 0).  --impl reference times the CPU restatement of the reference's algorithm
-(oracle/_ref/liboracle.so) on the host cores, on a bounded sample of the same workload.
+(oracle/_build/liboracle.so) on the host cores, on a bounded sample of the same workload.
 """
 import argparse
 import ctypes as C
@@ -382,8 +382,8 @@ WORKLOADS = {"gdn_prefill_32k": GdnPrefill32k, "decode_262k": Decode262k, "qsa_p
 # ------------------------------------------------------------------------------------------------------------
 
 def cpu_baseline(workload, seconds_hint=10.0):
-    from crucible_strix_halo_b200 import build
-    lib_path = build.build_oracle()
+    from oracle import build as oracle_build
+    lib_path = oracle_build.build_oracle()
     lib = C.CDLL(lib_path)
     lib.oracle_threads.restype = C.c_int
     lib.oracle_set_threads(C.c_int(len(os.sched_getaffinity(0))))   # every core this process may run on

@@ -1,4 +1,4 @@
-"""Builds libcrucible_attn.so (sm_100a) in-tree with nvcc, and the C oracle with gcc.
+"""Builds libcrucible_attn.so (sm_100a) in-tree with nvcc.
 
     python -m crucible_strix_halo_b200.build [--force]
 """
@@ -52,20 +52,6 @@ def build_library(force=False, verbose=False):
     return LIB
 
 
-def build_oracle(force=False):
-    """The C restatement used as the timed CPU baseline (oracle/attn_oracle_c.c -> oracle/_ref/liboracle.so)."""
-    src = os.path.join(ROOT, "oracle", "attn_oracle_c.c")
-    if not os.path.exists(src):
-        return None
-    out_dir = os.path.join(ROOT, "oracle", "_ref")
-    os.makedirs(out_dir, exist_ok=True)
-    lib = os.path.join(out_dir, "liboracle.so")
-    if force or not _newer(lib, [src]):
-        _run(["gcc", "-O3", "-march=x86-64-v3", "-fopenmp", "-shared", "-fPIC", "-o", lib, src, "-lm"])
-    return lib
-
-
 if __name__ == "__main__":
     force = "--force" in sys.argv
     print(build_library(force, verbose="-v" in sys.argv))
-    print(build_oracle(force))

@@ -8,7 +8,7 @@ LIB_PATH = os.path.join(_HERE, "libcrucible_attn.so")
 OK, ERR_INVALID, ERR_CUDA, ERR_UNSUPPORTED, ERR_TIMEOUT = range(5)
 OUT_RAW_F32, OUT_RAW_BF16, OUT_EXL3_WHT = range(3)
 IN_F32, IN_BF16 = range(2)
-GDN_SERIAL_F32, GDN_CHUNK_TC, GDN_CHUNK_MMA = range(3)
+GDN_SERIAL_F32, GDN_CHUNK_TC = range(2)
 PEND_FLOATS, QSA_PART, QSA_SPLITS, SEL_BLOCKS = 258, 258, 32, 512
 
 
@@ -31,6 +31,10 @@ GEOM_BENCH = Geometry(2048, 16, 2, 32, 16)
 GEOM_REF = Geometry(2560, 24, 2, 48, 16)
 
 P = C.c_void_p
+
+
+class Options(C.Structure):
+    _fields_ = [("gdn_part_chunks", C.c_int), ("pdl", C.c_int), ("qsa_score_simt", C.c_int), ("qsa_union_rows", C.c_int)]
 
 
 class GdnArgs(C.Structure):
@@ -97,6 +101,11 @@ _protos = {
     "cr_last_error": (C.c_char_p, []),
     "cr_version": (C.c_int, []),
     "cr_device_status": (C.c_int, []),
+    "cr_device_check": (C.c_int, []),
+    "cr_device_status_clear": (C.c_int, []),
+    "cr_get_options": (C.c_int, [C.POINTER(Options)]),
+    "cr_set_options": (C.c_int, [C.POINTER(Options)]),
+    "cr_debug_wait_timeout": (C.c_int, [P, C.c_uint, P]),
     "cr_kernel_launches": (C.c_ulonglong, []),
     "cr_profile_enable": (C.c_int, [C.c_int]),
     "cr_profile_begin": (C.c_int, [P]),
@@ -106,6 +115,22 @@ EXPORTS = tuple(_protos)
 for _name, (_res, _args) in _protos.items():
     _fn = getattr(lib, _name)        # AttributeError here = the library lacks a declared symbol
     _fn.restype, _fn.argtypes = _res, _args
+
+
+def get_options():
+    o = Options()
+    check(lib.cr_get_options(C.byref(o)))
+    return o
+
+
+def set_options(**kw):
+    """Changes the named fields of the process-wide options and returns the previous values."""
+    old = get_options()
+    new = Options(old.gdn_part_chunks, old.pdl, old.qsa_score_simt, old.qsa_union_rows)
+    for k, v in kw.items():
+        setattr(new, k, v)
+    check(lib.cr_set_options(C.byref(new)))
+    return old
 
 
 def check(status):

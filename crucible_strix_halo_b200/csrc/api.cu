@@ -53,6 +53,9 @@ void count_launch(const char* name) {
   if (g_profile.load(std::memory_order_relaxed)) mark(name);
 }
 
+static cr_options g_options = {kGdnPartChunksDefault, 1, 0, 0};
+const cr_options& options() { return g_options; }
+
 cr_status check_geometry(const cr_geometry* g) {
   CR_REQUIRE(g, "null geometry");
   CR_REQUIRE(g->hidden >= 8 && g->hidden % 8 == 0 && g->hidden <= 16384, "geometry: hidden=%d must be a multiple of 8 in 8..16384", g->hidden);
@@ -69,6 +72,46 @@ cr_status check_geometry(const cr_geometry* g) {
 extern "C" const char* cr_last_error(void) { return cr::g_error; }
 extern "C" int cr_version(void) { return 1; }
 extern "C" unsigned long long cr_kernel_launches(void) { return cr::g_launches.load(std::memory_order_relaxed); }
+
+extern "C" cr_status cr_get_options(cr_options* out) {
+  CR_REQUIRE(out, "cr_get_options: null argument");
+  *out = cr::g_options;
+  return CR_OK;
+}
+
+extern "C" cr_status cr_set_options(const cr_options* in) {
+  CR_REQUIRE(in, "cr_set_options: null argument");
+  CR_REQUIRE(in->gdn_part_chunks >= 32 && in->gdn_part_chunks <= 4096, "cr_set_options: gdn_part_chunks=%d outside 32..4096", in->gdn_part_chunks);
+  CR_REQUIRE(in->pdl == 0 || in->pdl == 1, "cr_set_options: pdl must be 0 or 1");
+  CR_REQUIRE(in->qsa_score_simt == 0 || in->qsa_score_simt == 1, "cr_set_options: qsa_score_simt must be 0 or 1");
+  CR_REQUIRE(in->qsa_union_rows == 0 || in->qsa_union_rows == 8 || in->qsa_union_rows == 16 || in->qsa_union_rows == -1,
+             "cr_set_options: qsa_union_rows must be 0 (automatic), 8, 16 or -1 (row-wise kernel)");
+  cr::g_options = *in;
+  return CR_OK;
+}
+
+extern "C" int cr_device_status(void) {
+  return cr::gdn_scan_status_read() | (cr::qsa_score_status_read() << 1) | (cr::qsa_flash_status_read() << 2) |
+         (cr::debug_wait_status_read() << 3);
+}
+
+extern "C" cr_status cr_device_check(void) {
+  const int st = cr_device_status();
+  if (st == 0) return CR_OK;
+  cr::set_error("a bounded device-side wait gave up (status word 0x%x:%s%s%s%s); the outputs of that launch are undefined",
+                st, st & 1 ? " gdn_chunk_scan_tc_kernel" : "", st & 2 ? " qsa_score_tc_kernel" : "", st & 4 ? " qsa_flash_tc_kernel" : "",
+                st & 8 ? " debug_wait_kernel" : "");
+  return CR_ERR_TIMEOUT;
+}
+
+extern "C" cr_status cr_device_status_clear(void) {
+  cr::gdn_scan_status_clear();
+  cr::qsa_score_status_clear();
+  cr::qsa_flash_status_clear();
+  cr::debug_wait_status_clear();
+  CR_CUDA(cudaGetLastError());
+  return CR_OK;
+}
 
 extern "C" cr_status cr_profile_enable(int on) { cr::g_profile.store(on ? 1 : 0); return CR_OK; }
 

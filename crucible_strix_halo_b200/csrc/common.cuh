@@ -8,6 +8,8 @@
 #include <cstdarg>
 #include "../../include/crucible_attn.h"
 
+#include <atomic>
+#include <mutex>
 #include <utility>
 #include <cstdlib>
 
@@ -18,23 +20,30 @@ namespace cr {
 // it calls pdl_wait() before it touches anything that kernel (or any earlier one) wrote, which returns once the
 // earlier grid has completed and its writes are visible.  Every kernel of a chain calls pdl_release() at its top so
 // that its successor's launch latency and CTA placement overlap its own execution.  Both are no-ops in a kernel
-// launched the plain way.  CR_NO_PDL=1 in the environment turns the launch attribute off.
+// launched the plain way.  cr_options.pdl = 0 turns the launch attribute off.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_release() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
-// True the first time it is called for the current device with a given flag set: function attributes such as the
-// dynamic shared-memory limit belong to a device, so launchers set them once per device, not once per process.
-struct PerDeviceOnce { bool done[64] = {}; };
-inline bool first_use_on_device(PerDeviceOnce& f) {
+// Work that belongs to a device rather than to the process (function attributes such as the dynamic shared-memory
+// limit): `fn` runs once per device, under a lock, and the device is marked done only after it returned CR_OK, so a
+// second host thread cannot launch before the attributes are set and a failed attempt is retried by the next call.
+struct PerDeviceOnce {
+  std::mutex mu;
+  std::atomic<bool> done[64] = {};
+};
+template <class F>
+inline cr_status once_per_device(PerDeviceOnce& f, F&& fn) {
   int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return true;
-  if (f.done[dev]) return false;
-  f.done[dev] = true;
-  return true;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return fn();
+  if (f.done[dev].load(std::memory_order_acquire)) return CR_OK;
+  std::lock_guard<std::mutex> lock(f.mu);
+  if (f.done[dev].load(std::memory_order_relaxed)) return CR_OK;
+  const cr_status s = fn();
+  if (s == CR_OK) f.done[dev].store(true, std::memory_order_release);
+  return s;
 }
-inline bool pdl_enabled() {
-  static const bool on = getenv("CR_NO_PDL") == nullptr;
-  return on;
-}
+// Process-wide tuning options (cr_get_options / cr_set_options); nothing is read from the environment.
+const cr_options& options();
+inline bool pdl_enabled() { return options().pdl != 0; }
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
   cudaLaunchConfig_t cfg = {};
@@ -50,6 +59,7 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
 constexpr float kEps = 1e-6f;                         // every norm epsilon
 constexpr float kInvSqrt128 = 0.08838834764831845f;   // 1/sqrt(128)
 constexpr float kHadNorm = 0.088388347648f;           // ExLlamaV3's 1/sqrt(128) constant
+constexpr int kGdnPartChunksDefault = 111;               // chunks per internal part of a long GDN prefill call
 constexpr int kMaxSpans = 32;                         // spans per launch (they travel as kernel parameters: 4 KB in all)
 
 // ---- host-side error plumbing -------------------------------------------------------------------
@@ -75,6 +85,17 @@ void use_stream(cudaStream_t stream);   // the stream the following launches go 
   } while (0)
 
 cr_status check_geometry(const cr_geometry* g);
+
+// A device status word of one translation unit with its host-side reader and clearer (both synchronise).  A bounded
+// wait that gives up stores 1 in it; api.cu assembles the words of all units into cr_device_status().
+#define CR_DEFINE_STATUS_WORD(name)                                                                        \
+  __device__ int g_##name##_status = 0;                                                                    \
+  int name##_status_read() { int v = 0; cudaMemcpyFromSymbol(&v, g_##name##_status, sizeof(int)); return v; } \
+  void name##_status_clear() { const int v = 0; cudaMemcpyToSymbol(g_##name##_status, &v, sizeof(int)); }
+int gdn_scan_status_read();   void gdn_scan_status_clear();
+int qsa_score_status_read();  void qsa_score_status_clear();
+int qsa_flash_status_read();  void qsa_flash_status_clear();
+int debug_wait_status_read(); void debug_wait_status_clear();
 
 // ---- device math ---------------------------------------------------------------------------------
 __device__ __forceinline__ float round_h(float v) { return __half2float(__float2half_rn(v)); }

@@ -1,4 +1,4 @@
-// Shared pieces of the chunk-64 WY Gated DeltaNet scan (gdn_chunk_local.cu, gdn_chunk_scan_tc.cu, gdn_chunk_scan.cu).
+// Shared pieces of the chunk-64 WY Gated DeltaNet scan (gdn_chunk_local.cu, gdn_chunk_scan_tc.cu).
 //
 // The algebra is the reference's chunked form (ref/prefill_ref.py:16-34;
 // engine/layers/kernels/prefill_gdn.h:111-249).  Per chunk of 64 tokens and value head, with G the cumulative
@@ -20,13 +20,11 @@ constexpr int kLdX = 136;   // [64][128] operand read as B stored [k][n], or as 
 constexpr int kLdM = 68;    // [64][64] operand read row-major as A
 
 struct ChunkWs {
-  float* W;    // [Hv][chunks][64][128]  tf32
-  float* Ut;   // [Hv][chunks][64][128]  fp32; for the tcgen05 scan [Hv][chunks][4][4][128][4] = [token / 16][(token % 16) / 4][column][token % 4]
-  float* QKd;  // [Hv][chunks][64][64]   tf32
-  float* G;    // [Hv][chunks][64]       cumulative log decay inside the chunk
-  float* WQ;   // [Hv][chunks][32][128][4] rows 0-63 W, rows 64-127 e^G Q, one K-major tile (tcgen05 scan only)
-  float* QKp;  // [Hv][chunks][16][64][4] QKd as a K-major tile (tcgen05 scan only)
-  float* Kt;   // [Hv][chunks][16][128][4] (e^{G_end - G} K)^T as a K-major tile (tcgen05 scan only)
+  float* Ut;   // [Hv][chunks][4][4][128][4] fp32 = [token / 16][(token % 16) / 4][column][token % 4]
+  float* G;    // [Hv][chunks][64]         cumulative log decay inside the chunk
+  float* WQ;   // [Hv][chunks][32][128][4] rows 0-63 W, rows 64-127 e^G Q, one K-major tf32 tile
+  float* QKp;  // [Hv][chunks][16][64][4]  QKd as a K-major tf32 tile
+  float* Kt;   // [Hv][chunks][16][128][4] (e^{G_end - G} K)^T as a K-major tf32 tile
   int chunks;
 };
 
@@ -147,11 +145,8 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;\n" ::: "memory"); }
 __device__ __forceinline__ void cp_async_wait_but_one() { asm volatile("cp.async.wait_group 1;\n" ::: "memory"); }
 
-cr_status gdn_chunk_local_launch(const cr_geometry* g, const GdnPrefillParams& P, const ChunkWs& ws, bool bf16_in, bool umma_layout,
-                                 cudaStream_t stream);
+cr_status gdn_chunk_local_launch(const cr_geometry* g, const GdnPrefillParams& P, const ChunkWs& ws, bool bf16_in, cudaStream_t stream);
 cr_status gdn_chunk_scan_tc_launch(const cr_geometry* g, const GdnPrefillParams& P, const ChunkWs& ws, cudaStream_t stream);
-int gdn_scan_status_read();
 size_t gdn_chunk_layout(const cr_geometry* g, int rows, ChunkWs* ws, char* base);
-cr_status gdn_chunk_scan_launch(const cr_geometry* g, const GdnPrefillParams& P, const ChunkWs& ws, cudaStream_t stream);
 
 }  // namespace cr

@@ -143,9 +143,8 @@ __device__ __forceinline__ void invert_unit_lower_64(float* LT, float* Ms) {
   }
 }
 
-// UM: operands for the tcgen05 scan are written as K-major tiles float[K/4][rows][4] (plus Qt = e^G Q and K^T);
-// otherwise row-major tiles and the prepared q/k rows for the mma.sync scan.
-template <bool BF16, bool UM>
+// Operands for the tcgen05 scan are written as K-major tiles float[K/4][rows][4] (plus Qt = e^G Q and K'^T).
+template <bool BF16>
 __global__ void __launch_bounds__(256, 2) gdn_chunk_local_kernel(GdnPrefillParams P, ChunkWs ws) {
   extern __shared__ __align__(16) float sm[];
   float* Ks = sm;                       // [64][132] khat (tf32)
@@ -254,13 +253,9 @@ __global__ void __launch_bounds__(256, 2) gdn_chunk_local_kernel(GdnPrefillParam
     k = make_float4(tf32r(k.x * sk), tf32r(k.y * sk), tf32r(k.z * sk), tf32r(k.w * sk));
     *reinterpret_cast<float4*>(Qs + row * kLdK + c4) = q;
     *reinterpret_cast<float4*>(Ks + row * kLdK + c4) = k;
-    if (!UM && row < valid) {
-      *reinterpret_cast<float4*>(P.qn + ((size_t)(r0 + row) * P.Hk + kh) * 128 + c4) = q;
-      *reinterpret_cast<float4*>(P.kn + ((size_t)(r0 + row) * P.Hk + kh) * 128 + c4) = k;
-    }
   }
   __syncthreads();
-  if constexpr (UM) {
+  {
     // per value head: K'^T = (e^{G_end - G} K)^T, K-major over tokens (unit (token / 4, key) holds 4 tokens of one
     // key; the decay towards the chunk end is folded into K so that the scan multiplies U itself), and
     // Qt = e^G Q, K-major over keys
@@ -297,14 +292,14 @@ __global__ void __launch_bounds__(256, 2) gdn_chunk_local_kernel(GdnPrefillParam
     const float* Gv = Gs + vi * 64; const float* bv = bs + vi * 64; const float* ev = es + vi * 64;
     __syncthreads();                    // previous head done with LT and the staging tile; qhat no longer needed
     {   // L (warps 0-3) and QKd (warps 4-7) straight from the Gram fragments
-      float* qkd = UM ? ws.QKp + unit * 4096 : ws.QKd + unit * 64 * 64;
+      float* qkd = ws.QKp + unit * 4096;
 #pragma unroll
       for (int n = 0; n < 8; ++n)
 #pragma unroll
         for (int hrow = 0; hrow < 2; ++hrow) {
           const int row = mt * 16 + g + 8 * hrow, col = n * 8 + 2 * tq;
           if (n >= n_used) {            // above the diagonal: nothing reads L there, QKd is zero
-            if (w >= 4) *reinterpret_cast<float2*>(qkd + (UM ? ((col >> 2) * 64 + row) * 4 + (col & 3) : row * 64 + col)) = make_float2(0.f, 0.f);
+            if (w >= 4) *reinterpret_cast<float2*>(qkd + ((col >> 2) * 64 + row) * 4 + (col & 3)) = make_float2(0.f, 0.f);
             continue;
           }
           const float Gr = Gv[row];
@@ -314,7 +309,7 @@ __global__ void __launch_bounds__(256, 2) gdn_chunk_local_kernel(GdnPrefillParam
             const float b = bv[row];
             *reinterpret_cast<float2*>(LT + row * kLdM + col) = make_float2(col < row ? b * v0 * p0 : 0.f, col + 1 < row ? b * v1 * p1 : 0.f);
           } else {
-            const int at = UM ? ((col >> 2) * 64 + row) * 4 + (col & 3) : row * 64 + col;
+            const int at = ((col >> 2) * 64 + row) * 4 + (col & 3);
             *reinterpret_cast<float2*>(qkd + at) = make_float2(col <= row ? tf32r(v0 * p0) : 0.f, col + 1 <= row ? tf32r(v1 * p1) : 0.f);
           }
         }
@@ -341,19 +336,14 @@ __global__ void __launch_bounds__(256, 2) gdn_chunk_local_kernel(GdnPrefillParam
 #pragma unroll
         for (int n = 0; n < 4; ++n) acc[k][n][0] = acc[k][n][1] = acc[k][n][2] = acc[k][n][3] = 0.f;
       warp_gemm_tril_pair<4, true>(acc[0], acc[1], LT, kLdM, m_hi, m_lo, Qs + qn * 32, kLdX);
-      float* dst = UM ? ws.WQ + unit * 16384 : ws.W + unit * 8192;
+      float* dst = ws.WQ + unit * 16384;
 #pragma unroll
       for (int k = 0; k < 2; ++k)
 #pragma unroll
         for (int n = 0; n < 4; ++n) {
           const int col = qn * 32 + n * 8 + 2 * tq, r_lo = (k ? m_lo : m_hi) * 16 + g;
-          if constexpr (UM) {
-            *reinterpret_cast<float2*>(dst + ((col >> 2) * 128 + r_lo) * 4 + (col & 3)) = make_float2(tf32r(acc[k][n][0]), tf32r(acc[k][n][1]));
-            *reinterpret_cast<float2*>(dst + ((col >> 2) * 128 + r_lo + 8) * 4 + (col & 3)) = make_float2(tf32r(acc[k][n][2]), tf32r(acc[k][n][3]));
-          } else {
-            *reinterpret_cast<float2*>(dst + r_lo * 128 + col) = make_float2(tf32r(acc[k][n][0]), tf32r(acc[k][n][1]));
-            *reinterpret_cast<float2*>(dst + (r_lo + 8) * 128 + col) = make_float2(tf32r(acc[k][n][2]), tf32r(acc[k][n][3]));
-          }
+          *reinterpret_cast<float2*>(dst + ((col >> 2) * 128 + r_lo) * 4 + (col & 3)) = make_float2(tf32r(acc[k][n][0]), tf32r(acc[k][n][1]));
+          *reinterpret_cast<float2*>(dst + ((col >> 2) * 128 + r_lo + 8) * 4 + (col & 3)) = make_float2(tf32r(acc[k][n][2]), tf32r(acc[k][n][3]));
         }
     }
     __syncthreads();                    // X = beta e^G K consumed
@@ -394,42 +384,30 @@ __global__ void __launch_bounds__(256, 2) gdn_chunk_local_kernel(GdnPrefillParam
 #pragma unroll
       for (int k = 0; k < 2; ++k) {
         const int mt2 = k ? m_lo : m_hi;
-        if constexpr (UM) {   // [token / 16][(token % 16) / 4][column][token % 4]: a scan thread owns a column and reads
-                              // four tokens per 128-bit load, a warp 512 contiguous bytes
-          float* dst = ws.Ut + unit * 8192 + (size_t)mt2 * 2048;
+        // [token / 16][(token % 16) / 4][column][token % 4]: a scan thread owns a column and reads four tokens per
+        // 128-bit load, a warp 512 contiguous bytes
+        float* dst = ws.Ut + unit * 8192 + (size_t)mt2 * 2048;
 #pragma unroll
-          for (int n = 0; n < 4; ++n) {
-            const int col = qn * 32 + n * 8 + 2 * tq;
-            float* d = dst + (g >> 2) * 512 + col * 4 + (g & 3);
-            d[0] = acc[k][n][0]; d[4] = acc[k][n][1]; d[1024] = acc[k][n][2]; d[1028] = acc[k][n][3];
-          }
-        } else {
-          float* dst = ws.Ut + (unit * 64 + mt2 * 16) * 128 + qn * 32;
-#pragma unroll
-          for (int n = 0; n < 4; ++n) {
-            *reinterpret_cast<float2*>(dst + g * 128 + n * 8 + 2 * tq) = make_float2(acc[k][n][0], acc[k][n][1]);
-            *reinterpret_cast<float2*>(dst + (g + 8) * 128 + n * 8 + 2 * tq) = make_float2(acc[k][n][2], acc[k][n][3]);
-          }
+        for (int n = 0; n < 4; ++n) {
+          const int col = qn * 32 + n * 8 + 2 * tq;
+          float* d = dst + (g >> 2) * 512 + col * 4 + (g & 3);
+          d[0] = acc[k][n][0]; d[4] = acc[k][n][1]; d[1024] = acc[k][n][2]; d[1028] = acc[k][n][3];
         }
       }
     }
   }
 }
 
-cr_status gdn_chunk_local_launch(const cr_geometry* g, const GdnPrefillParams& P, const ChunkWs& ws, bool bf16_in, bool umma_layout,
-                                 cudaStream_t stream) {
+cr_status gdn_chunk_local_launch(const cr_geometry* g, const GdnPrefillParams& P, const ChunkWs& ws, bool bf16_in, cudaStream_t stream) {
   static PerDeviceOnce configured;
-  if (first_use_on_device(configured)) {
-    CR_CUDA(cudaFuncSetAttribute(gdn_chunk_local_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kLocalSmem));
-    CR_CUDA(cudaFuncSetAttribute(gdn_chunk_local_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kLocalSmem));
-    CR_CUDA(cudaFuncSetAttribute(gdn_chunk_local_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kLocalSmem));
-    CR_CUDA(cudaFuncSetAttribute(gdn_chunk_local_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kLocalSmem));
-  }
+  if (cr_status st = once_per_device(configured, [] {
+        CR_CUDA(cudaFuncSetAttribute(gdn_chunk_local_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kLocalSmem));
+        CR_CUDA(cudaFuncSetAttribute(gdn_chunk_local_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kLocalSmem));
+        return CR_OK;
+      })) return st;
   const dim3 grid(ws.chunks, g->gdn_kheads);
-  if (bf16_in && umma_layout) gdn_chunk_local_kernel<true, true><<<grid, 256, kLocalSmem, stream>>>(P, ws);
-  else if (bf16_in) gdn_chunk_local_kernel<true, false><<<grid, 256, kLocalSmem, stream>>>(P, ws);
-  else if (umma_layout) gdn_chunk_local_kernel<false, true><<<grid, 256, kLocalSmem, stream>>>(P, ws);
-  else gdn_chunk_local_kernel<false, false><<<grid, 256, kLocalSmem, stream>>>(P, ws);
+  if (bf16_in) gdn_chunk_local_kernel<true><<<grid, 256, kLocalSmem, stream>>>(P, ws);
+  else gdn_chunk_local_kernel<false><<<grid, 256, kLocalSmem, stream>>>(P, ws);
   CR_LAUNCH_CHECK("gdn_chunk_local_kernel");
   return CR_OK;
 }

@@ -25,7 +25,7 @@
 
 namespace cr {
 
-__device__ int g_gdn_scan_status = 0;
+CR_DEFINE_STATUS_WORD(gdn_scan)
 
 constexpr int kWG = 4;                                    // compute warpgroups
 constexpr int kScanThreads = 128 * kWG + 64;              // + issuer warp + loader warp
@@ -123,6 +123,7 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_chunk_scan_tc_kernel(GdnP
       // loader that falls behind never sees a phase it was not waiting for.
       for (int c = 0; c + 2 < nch; ++c) {
         wait(&empty[c & 1], (c >> 1) & 1);
+        if (gave_up || dead) break;                        // no more copies once any wait has run out
         load(c + 2);
         prefetch(c + 2 + kLead);
       }
@@ -140,11 +141,13 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_chunk_scan_tc_kernel(GdnP
         const uint32_t cD1 = kColD1 + 128 * b;
         if (c == 0) wait(&full[s], ph);                    // later chunks: waited for at the end of the previous one
         wait(sReady, b);
+        if (gave_up || dead) break;                        // no more tensor-core work once any wait has run out
         umma::fence_after_sync();
 #pragma unroll
         for (int s8 = 0; s8 < 16; ++s8) umma::mma_tf32_ts(tm + cD1, tm + kColS + 8 * s8, dA + (uint64_t)(s8 * 256), idesc128, s8 > 0);
         umma::commit(d1);
         wait(uReady, b);
+        if (gave_up || dead) break;
         umma::fence_after_sync();
 #pragma unroll
         for (int s8 = 0; s8 < 8; ++s8) umma::mma_tf32_ts(tm + kColD2, tm + cD1 + 8 * s8, dK + (uint64_t)(s8 * 256), idesc128, s8 > 0);
@@ -238,18 +241,13 @@ __global__ void __launch_bounds__(kScanThreads, 1) gdn_chunk_scan_tc_kernel(GdnP
 
 cr_status gdn_chunk_scan_tc_launch(const cr_geometry* g, const GdnPrefillParams& P, const ChunkWs& ws, cudaStream_t stream) {
   static PerDeviceOnce configured;
-  if (first_use_on_device(configured)) {
-    CR_CUDA(cudaFuncSetAttribute(gdn_chunk_scan_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kScanSmem));
-  }
+  if (cr_status st = once_per_device(configured, [] {
+        CR_CUDA(cudaFuncSetAttribute(gdn_chunk_scan_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kScanSmem));
+        return CR_OK;
+      })) return st;
   gdn_chunk_scan_tc_kernel<<<g->gdn_vheads, kScanThreads, kScanSmem, stream>>>(P, ws);
   CR_LAUNCH_CHECK("gdn_chunk_scan_tc_kernel");
   return CR_OK;
-}
-
-int gdn_scan_status_read() {
-  int v = 0;
-  cudaMemcpyFromSymbol(&v, g_gdn_scan_status, sizeof(int));
-  return v;
 }
 
 }  // namespace cr

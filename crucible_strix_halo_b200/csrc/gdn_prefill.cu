@@ -256,14 +256,7 @@ size_t gdn_workspace_layout(const cr_geometry* g, int rows, GdnPrefillParams* P,
   return off;
 }
 
-int gdn_part_rows() {
-  static const int rows = [] {
-    const char* e = getenv("CR_GDN_PART_CHUNKS");
-    const int c = e ? atoi(e) : 0;
-    return c >= 1 && c <= 4096 ? c * 64 : kGdnPartRowsDefault;
-  }();
-  return rows;
-}
+int gdn_part_rows() { return options().gdn_part_chunks * 64; }
 
 // Row ranges of the parts of a pipelined call.  The first local kernel and the last scan run with nothing beside
 // them, so the first part is short and the parts at the end halve (each scan then ends soon after the local
@@ -273,7 +266,7 @@ static std::vector<std::pair<int, int>> part_schedule(int R, int part_rows) {
   const int chunks = (R + 63) / 64, P = part_rows / 64;
   std::vector<int> tail;
   int left = chunks;
-  const int first = chunks > 2 * P ? 32 : 0;
+  const int first = chunks > 2 * P ? std::min(32, P) : 0;   // never longer than the part a workspace is sized for
   left -= first;
   for (int t = P / 2; t >= 16 && left - t >= P; t /= 2) { tail.push_back(t); left -= t; }
   const int mid = (left + P - 1) / P;
@@ -344,7 +337,7 @@ extern "C" int cr_gdn_prefill_parts(int rows, int* first_row, int* n_rows, int m
 }
 
 extern "C" int cr_gdn_algo_available(cr_gdn_algo algo) {
-  return algo == CR_GDN_SERIAL_F32 || ((algo == CR_GDN_CHUNK_TC || algo == CR_GDN_CHUNK_MMA) && cr::gdn_chunk_available());
+  return algo == CR_GDN_SERIAL_F32 || (algo == CR_GDN_CHUNK_TC && cr::gdn_chunk_available());
 }
 
 extern "C" cr_status cr_gdn_prefill(const cr_geometry* g, const cr_gdn_prefill_args* args, cr_gdn_algo algo,
@@ -363,7 +356,12 @@ extern "C" cr_status cr_gdn_prefill(const cr_geometry* g, const cr_gdn_prefill_a
   CR_REQUIRE(fmt == CR_OUT_RAW_F32 || fmt == CR_OUT_RAW_BF16 || fmt == CR_OUT_EXL3_WHT, "cr_gdn_prefill: bad output format");
   CR_REQUIRE(fmt != CR_OUT_EXL3_WHT || a.suh_out, "cr_gdn_prefill: suh_out needed for the EXL3 output");
   CR_REQUIRE(fmt == CR_OUT_EXL3_WHT || a.pack_rows == 0, "cr_gdn_prefill: packed layout only with the EXL3 output");
-  CR_REQUIRE(algo == CR_GDN_SERIAL_F32 || algo == CR_GDN_CHUNK_TC || algo == CR_GDN_CHUNK_MMA, "cr_gdn_prefill: unknown algorithm");
+  CR_REQUIRE(algo == CR_GDN_SERIAL_F32 || algo == CR_GDN_CHUNK_TC, "cr_gdn_prefill: unknown algorithm");
+  if (algo == CR_GDN_CHUNK_TC && g->gdn_vheads / g->gdn_kheads > 3) {   // the chunk-local kernel keeps gate tables for 3 value heads per key head
+    set_error("cr_gdn_prefill: the chunked scan serves up to 3 value heads per key head (%d / %d given); use CR_GDN_SERIAL_F32",
+              g->gdn_vheads, g->gdn_kheads);
+    return CR_ERR_UNSUPPORTED;
+  }
   const int part_rows = a.R < gdn_part_rows() ? a.R : gdn_part_rows();
   const size_t part_bytes = gdn_workspace_layout(g, part_rows, nullptr, nullptr);
   const size_t need = a.R > gdn_part_rows() ? 2 * part_bytes : part_bytes;
@@ -405,39 +403,51 @@ extern "C" cr_status cr_gdn_prefill(const cr_geometry* g, const cr_gdn_prefill_a
     // that its CTAs (one whole SM each) are placed while the SMs are empty; the local kernel then fills the rest.
     PipeStreams* ps = pipe_streams();
     CR_REQUIRE(ps, "cr_gdn_prefill: cannot create the internal streams");
+    const std::vector<std::pair<int, int>> parts = part_schedule(a.R, gdn_part_rows());
+    const int np = (int)parts.size();
+    for (const auto& pr : parts) CR_REQUIRE(pr.second <= part_rows, "cr_gdn_prefill: internal part of %d rows exceeds the workspace part of %d", pr.second, part_rows);
     std::lock_guard<std::mutex> lock(ps->mu);
     CR_CUDA(cudaEventRecord(ps->fork, stream));
     CR_CUDA(cudaStreamWaitEvent(ps->hi, ps->fork, 0));
     CR_CUDA(cudaStreamWaitEvent(ps->lo, ps->fork, 0));
     CR_CUDA(cudaStreamWaitEvent(ps->mid, ps->fork, 0));
-    const std::vector<std::pair<int, int>> parts = part_schedule(a.R, gdn_part_rows());
-    const int np = (int)parts.size();
-    part_params(parts[0].first, 0, parts[0].second);
-    if (cr_status s = gdn_chunk_local_only(g, P, bf, ps->lo)) return s;
-    CR_CUDA(cudaEventRecord(ps->local_done[0], ps->lo));
-    int pi = 0;
-    for (; pi < np; ++pi) {
-      const int buf = pi & 1;
-      part_params(parts[pi].first, buf, parts[pi].second);
-      CR_CUDA(cudaStreamWaitEvent(ps->hi, ps->local_done[buf], 0));
-      if (cr_status s = gdn_chunk_scan_only(g, P, ps->hi)) return s;
-      // the gated readout runs on a third stream, so the next scan does not queue behind it
-      CR_CUDA(cudaEventRecord(ps->scan_done[buf], ps->hi));
-      CR_CUDA(cudaStreamWaitEvent(ps->mid, ps->scan_done[buf], 0));
-      if (cr_status s = gate(ps->mid)) return s;
-      CR_CUDA(cudaEventRecord(ps->part_done[buf], ps->mid));
-      if (pi + 1 < np) {   // local kernel of the next part, into the other workspace
-        // Its workspace was last read by the scan and the gate of part pi - 1.  Waiting for the gate (which runs
-        // late, behind the local kernel of part pi) also delays this launch just long enough for the scan of part
-        // pi to take its SMs while they are empty; waiting for the scan alone measured 7 % slower.
-        if (pi >= 1) CR_CUDA(cudaStreamWaitEvent(ps->lo, ps->part_done[buf ^ 1], 0));
-        part_params(parts[pi + 1].first, buf ^ 1, parts[pi + 1].second);
-        if (cr_status s = gdn_chunk_local_only(g, P, bf, ps->lo)) return s;
-        CR_CUDA(cudaEventRecord(ps->local_done[buf ^ 1], ps->lo));
+    auto enqueue = [&]() -> cr_status {
+      part_params(parts[0].first, 0, parts[0].second);
+      if (cr_status s = gdn_chunk_local_only(g, P, bf, ps->lo)) return s;
+      CR_CUDA(cudaEventRecord(ps->local_done[0], ps->lo));
+      for (int pi = 0; pi < np; ++pi) {
+        const int buf = pi & 1;
+        part_params(parts[pi].first, buf, parts[pi].second);
+        CR_CUDA(cudaStreamWaitEvent(ps->hi, ps->local_done[buf], 0));
+        if (cr_status s = gdn_chunk_scan_only(g, P, ps->hi)) return s;
+        // the gated readout runs on a third stream, so the next scan does not queue behind it
+        CR_CUDA(cudaEventRecord(ps->scan_done[buf], ps->hi));
+        CR_CUDA(cudaStreamWaitEvent(ps->mid, ps->scan_done[buf], 0));
+        if (cr_status s = gate(ps->mid)) return s;
+        CR_CUDA(cudaEventRecord(ps->part_done[buf], ps->mid));
+        if (pi + 1 < np) {   // local kernel of the next part, into the other workspace
+          // Its workspace was last read by the scan and the gate of part pi - 1.  Waiting for the gate (which runs
+          // late, behind the local kernel of part pi) also delays this launch just long enough for the scan of part
+          // pi to take its SMs while they are empty; waiting for the scan alone measured 7 % slower.
+          if (pi >= 1) CR_CUDA(cudaStreamWaitEvent(ps->lo, ps->part_done[buf ^ 1], 0));
+          part_params(parts[pi + 1].first, buf ^ 1, parts[pi + 1].second);
+          if (cr_status s = gdn_chunk_local_only(g, P, bf, ps->lo)) return s;
+          CR_CUDA(cudaEventRecord(ps->local_done[buf ^ 1], ps->lo));
+        }
       }
+      return CR_OK;
+    };
+    const cr_status enq = enqueue();
+    // Join: whatever was enqueued on the three internal streams (all of it, or the part before an error) is waited
+    // for by the caller's stream, so the streams never stay forked (a capture would otherwise be left unjoined).
+    cudaEvent_t join[3] = {ps->local_done[0], ps->scan_done[0], ps->part_done[0]};
+    cudaStream_t internal[3] = {ps->lo, ps->hi, ps->mid};
+    for (int i = 0; i < 3; ++i) {
+      const cudaError_t e1 = cudaEventRecord(join[i], internal[i]);
+      const cudaError_t e2 = e1 == cudaSuccess ? cudaStreamWaitEvent(stream, join[i], 0) : e1;
+      if (e2 != cudaSuccess && enq == CR_OK) return cuda_fail(e2, "cr_gdn_prefill: joining the internal streams");
     }
-    CR_CUDA(cudaStreamWaitEvent(stream, ps->part_done[(pi - 1) & 1], 0));   // the last gate: everything before it on
-    CR_CUDA(cudaStreamWaitEvent(stream, ps->scan_done[(pi - 1) & 1], 0));   // its stream, and the last scan, are done
+    if (enq) return enq;
   } else {
     int pi = 0;
     for (int p0 = 0; p0 < a.R; p0 += gdn_part_rows(), ++pi) {
@@ -449,7 +459,7 @@ extern "C" cr_status cr_gdn_prefill(const cr_geometry* g, const cr_gdn_prefill_a
         gdn_scan_serial_kernel<<<g->gdn_vheads * 4, 256, 0, stream>>>(P);
         CR_LAUNCH_CHECK("gdn_scan_serial_kernel");
       } else {   // the chunked scan prepares its rows itself
-        if (cr_status s = gdn_chunk_scan(g, P, bf, algo == CR_GDN_CHUNK_TC, stream)) return s;
+        if (cr_status s = gdn_chunk_scan(g, P, bf, stream)) return s;
       }
       if (cr_status s = gate(stream)) return s;
     }

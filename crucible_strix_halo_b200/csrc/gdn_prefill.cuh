@@ -9,8 +9,7 @@ namespace cr {
 // two workspaces used in turn.  The scan pays a fixed cost per launch (state load and store, pipeline fill, 15 to
 // 40 us measured), which argues for long parts; the first local kernel and the last scan have nothing to run
 // beside, which argues for short ones.  A part's intermediates take about 72 KB per row.
-constexpr int kGdnPartRowsDefault = 111 * 64;
-int gdn_part_rows();   // kGdnPartRowsDefault, or 64 x CR_GDN_PART_CHUNKS from the environment (read once; for tuning)
+int gdn_part_rows();   // 64 x cr_options.gdn_part_chunks (kGdnPartRowsDefault unless a host changed it)
 
 struct GdnPrefillParams {
   cr_gdn_args a;
@@ -27,7 +26,7 @@ struct GdnPrefillParams {
 
 bool gdn_chunk_available();
 size_t gdn_chunk_workspace_bytes(const cr_geometry* g, int rows);
-cr_status gdn_chunk_scan(const cr_geometry* g, const GdnPrefillParams& P, bool bf16_in, bool tcgen05, cudaStream_t stream);
+cr_status gdn_chunk_scan(const cr_geometry* g, const GdnPrefillParams& P, bool bf16_in, cudaStream_t stream);
 // The two halves of gdn_chunk_scan with the tcgen05 layouts, for callers that run them on different streams.
 cr_status gdn_chunk_local_only(const cr_geometry* g, const GdnPrefillParams& P, bool bf16_in, cudaStream_t stream);
 cr_status gdn_chunk_scan_only(const cr_geometry* g, const GdnPrefillParams& P, cudaStream_t stream);

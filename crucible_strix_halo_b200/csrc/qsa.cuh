@@ -19,7 +19,6 @@ cr_status qsa_prep_launch(const cr_geometry* g, const cr_qsa_args* spans, int n_
 cr_status qsa_score_launch(const cr_geometry* g, const cr_qsa_args* spans, int n_spans, cudaStream_t stream);
 // Prefill parts (many rows): the scores as four GEMMs on tcgen05 tensor cores.
 cr_status qsa_score_tc_launch(const QsaParams& P, int Rmax, int n, cudaStream_t stream);
-int qsa_score_status_read();
 cr_status qsa_topk_launch(const cr_geometry* g, const cr_qsa_args* spans, int n_spans, cudaStream_t stream);
 cr_status qsa_topk_cluster_launch(const QsaParams& P, int Rmax, int n, int nb_max, cudaStream_t stream);
 cr_status qsa_select_launch(const cr_geometry* g, const cr_qsa_args* spans, int n_spans, cudaStream_t stream);

@@ -287,7 +287,7 @@ __global__ void __launch_bounds__(256) qsa_merge_kernel(const __grid_constant__ 
 cr_status qsa_attn_launch(const cr_geometry* g, const cr_qsa_args* spans, int n_spans, float* partials, int splits,
                           int p0, int p1, cudaStream_t stream) {
   use_stream(stream);
-  CR_REQUIRE(splits >= 4 && splits <= 64, "qsa attention: %d KV splits unsupported", splits);
+  CR_REQUIRE(splits >= 4 && splits <= 32, "qsa attention: %d KV splits unsupported (4..32)", splits);
   int row_base = 0;
   for (int s0 = 0; s0 < n_spans; s0 += kMaxSpans) {
     const int n = n_spans - s0 < kMaxSpans ? n_spans - s0 : kMaxSpans;
@@ -296,10 +296,11 @@ cr_status qsa_attn_launch(const cr_geometry* g, const cr_qsa_args* spans, int n_
     for (int s = 0; s < n; ++s) P.base[s] += row_base;
     const int Rmax = qsa_max_rows(spans + s0, n);
     static PerDeviceOnce configured;
-    if (first_use_on_device(configured)) {
-      CR_CUDA(cudaFuncSetAttribute(qsa_attn_split_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(SplitSmem<1>)));
-      CR_CUDA(cudaFuncSetAttribute(qsa_attn_split_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(SplitSmem<2>)));
-    }
+    if (cr_status st = once_per_device(configured, [] {
+          CR_CUDA(cudaFuncSetAttribute(qsa_attn_split_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(SplitSmem<1>)));
+          CR_CUDA(cudaFuncSetAttribute(qsa_attn_split_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(SplitSmem<2>)));
+          return CR_OK;
+        })) return st;
     const dim3 grid(splits, Rmax * g->kv_heads, n);
     if ((long long)grid.x * grid.y * grid.z > 1024)
       CR_CUDA(launch_pdl(qsa_attn_split_kernel<1>, grid, dim3(128), sizeof(SplitSmem<1>), stream, P, partials, splits, p0, p1));
@@ -314,6 +315,7 @@ cr_status qsa_attn_launch(const cr_geometry* g, const cr_qsa_args* spans, int n_
 cr_status qsa_merge_launch(const cr_geometry* g, const cr_qsa_args* spans, int n_spans, const float* partials, int nparts,
                            bool part_major, float* partial_out, cr_out_format fmt, cudaStream_t stream) {
   use_stream(stream);
+  CR_REQUIRE(nparts >= 1 && nparts <= 32, "qsa merge: %d partial records per (row, head) unsupported (1..32)", nparts);
   int rows_total = 0, row_base = 0;
   for (int s = 0; s < n_spans; ++s) rows_total += spans[s].R;
   for (int s0 = 0; s0 < n_spans; s0 += kMaxSpans) {

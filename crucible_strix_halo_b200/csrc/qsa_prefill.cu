@@ -8,6 +8,7 @@
 
 namespace cr {
 constexpr int kPrefillSplits = 4;
+CR_DEFINE_STATUS_WORD(qsa_flash)
 }
 
 extern "C" size_t cr_qsa_prefill_scratch_bytes(const cr_geometry* g, int rows) {

@@ -19,7 +19,7 @@
 
 namespace cr {
 
-__device__ int g_qsa_score_status = 0;
+CR_DEFINE_STATUS_WORD(qsa_score)
 
 constexpr int kScRows = 64;                 // query rows per CTA (N)
 constexpr int kScBlocks = 128;              // pool blocks per tile (M)
@@ -122,6 +122,7 @@ __global__ void __launch_bounds__(kScThreads, 1) qsa_score_tc_kernel(const __gri
         const int buf = i & 1;
         wait(popFull, i & 1);
         if (i >= 2) wait(&accFree[buf], ((i >> 1) - 1) & 1);
+        if (gave_up || dead) break;                        // no more tensor-core work once any wait has run out
         umma::fence_after_sync();
 #pragma unroll
         for (int h = 0; h < 4; ++h) {
@@ -204,9 +205,10 @@ __global__ void __launch_bounds__(kScThreads, 1) qsa_score_tc_kernel(const __gri
 
 cr_status qsa_score_tc_launch(const QsaParams& P, int Rmax, int n, cudaStream_t stream) {
   static PerDeviceOnce configured;
-  if (first_use_on_device(configured)) {
-    CR_CUDA(cudaFuncSetAttribute(qsa_score_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kScoreSmem));
-  }
+  if (cr_status st = once_per_device(configured, [] {
+        CR_CUDA(cudaFuncSetAttribute(qsa_score_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kScoreSmem));
+        return CR_OK;
+      })) return st;
   const int row_tiles = (Rmax + kScRows - 1) / kScRows;
   int sm_count = 148;
   int dev = 0;
@@ -225,12 +227,6 @@ cr_status qsa_score_tc_launch(const QsaParams& P, int Rmax, int n, cudaStream_t 
   qsa_score_tc_kernel<<<dim3(row_tiles, splits, n), kScThreads, kScoreSmem, stream>>>(P);
   CR_LAUNCH_CHECK("qsa_score_tc_kernel");
   return CR_OK;
-}
-
-int qsa_score_status_read() {
-  int v = 0;
-  cudaMemcpyFromSymbol(&v, g_qsa_score_status, sizeof(int));
-  return v;
 }
 
 }  // namespace cr

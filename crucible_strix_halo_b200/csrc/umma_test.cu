@@ -52,7 +52,30 @@ __global__ void __launch_bounds__(128) umma_test_kernel(const float* A, const fl
   if (w == 0) umma::tmem_dealloc(tmem, 128);
 }
 
+CR_DEFINE_STATUS_WORD(debug_wait)
+
+// One CTA of 32 threads: lane 0 waits on an mbarrier that nothing completes.  No copy and no tensor-core work is
+// pending, so when the wait runs out the kernel simply reports and ends.
+__global__ void __launch_bounds__(32) debug_wait_kernel(int* status, unsigned long long max_ns) {
+  __shared__ __align__(8) uint64_t bar;
+  if (threadIdx.x == 0) { umma::mbar_init(&bar, 1); umma::mbar_fence_init(); }
+  __syncwarp();
+  if (threadIdx.x == 0 && !umma::mbar_wait_timed(&bar, 0, nullptr, max_ns)) {
+    *status = 1;
+    g_debug_wait_status = 1;
+  }
+}
+
 }  // namespace cr
+
+extern "C" cr_status cr_debug_wait_timeout(int* status, unsigned max_us, void* stream) {
+  using namespace cr;
+  CR_REQUIRE(status && max_us >= 1 && max_us <= 100000, "cr_debug_wait_timeout: need a status word and 1..100000 us");
+  use_stream((cudaStream_t)stream);
+  debug_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(status, (unsigned long long)max_us * 1000ull);
+  CR_LAUNCH_CHECK("debug_wait_kernel");
+  return CR_OK;
+}
 
 extern "C" cr_status cr_debug_umma_gemm(const float* A, const float* B, float* D, int K, int N, int* status, void* stream) {
   using namespace cr;

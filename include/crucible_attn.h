@@ -100,10 +100,10 @@ cr_status cr_gdn_step(const cr_geometry* g, const cr_gdn_args* spans, int n_span
 typedef enum {
   CR_GDN_SERIAL_F32 = 0,  /* exact fp32 token-serial scan (the role of GdnPersistentColumnKernel,
                              engine/layers/kernels/prefill_gdn.h:285-315) */
-  CR_GDN_CHUNK_TC = 1,    /* chunk-64 WY form, scan on tcgen05 tensor cores with the recurrent operands and the
+  CR_GDN_CHUNK_TC = 1     /* chunk-64 WY form, scan on tcgen05 tensor cores with the recurrent operands and the
                              accumulators in tensor memory
-                             (LaunchGdnPrefill / LaunchGdnMicro, engine/layers/kernels/prefill_gdn.h:1229-1279) */
-  CR_GDN_CHUNK_MMA = 2    /* the same algebra with warp-level mma.sync in the scan (kept as the comparison point) */
+                             (LaunchGdnPrefill / LaunchGdnMicro, engine/layers/kernels/prefill_gdn.h:1229-1279).
+                             Up to 3 value heads per key head (both model geometries); more: CR_ERR_UNSUPPORTED */
 } cr_gdn_algo;
 
 /* Replaces struct GdnPrefill (engine/layers/kernels/prefill_gdn.h:12-29).  input.replay = 0,
@@ -182,8 +182,10 @@ typedef struct {
 
 /* Scratch sizing (engine/layers/qsa_long.h:226, :396; engine/layers/ops.h:420;
  * engine/layers/cache_storage.h:40-46). */
-size_t cr_qsa_scratch_bytes(const cr_geometry* g, int rows);         /* split-KV partials + merge counters */
-size_t cr_qsa_select_scratch_bytes(const cr_geometry* g, int rows);  /* selection scratch (may be 0) */
+size_t cr_qsa_scratch_bytes(const cr_geometry* g, int rows);         /* split-KV partials: rows x Hq x 32 x 258 floats */
+size_t cr_qsa_select_scratch_bytes(const cr_geometry* g, int rows);  /* 0: the select kernels keep their histograms
+                                                                        on chip; kept so that QsaSelectScratchFloats
+                                                                        call sites compile */
 size_t cr_qsa_pool_floats(int ctx);
 cr_status cr_qsa_cache_bytes(const cr_geometry* g, int ctx, int bounded, size_t out_bytes[4]);
 
@@ -203,8 +205,9 @@ cr_status cr_qsa_select(const cr_geometry* g, const cr_qsa_args* spans, int n_sp
 
 /* Replaces LaunchQsaAttn / QsaAttnTailKernel (engine/layers/qsa_long.h:399-534): split-KV attention over the
  * attended positions, log-sum-exp merge, sigmoid gate, output transform.  `scratch` holds
- * cr_qsa_scratch_bytes(g, total rows) bytes; its counter area must be zero on first use (the kernel re-zeroes
- * what it used).  No kernel waits on another block: the last split to finish merges. */
+ * cr_qsa_scratch_bytes(g, total rows) bytes of split-KV partials; it needs no initialisation (every record the
+ * merge reads is written by the same call first).  Two launches: the split kernel, then a merge kernel; no
+ * block waits on another block and there are no counters (the reference's `sync` words have no counterpart). */
 cr_status cr_qsa_attn(const cr_geometry* g, const cr_qsa_args* spans, int n_spans, void* scratch,
                       size_t scratch_bytes, cr_out_format fmt, void* stream);
 
@@ -269,10 +272,32 @@ cr_status cr_qsa_merge_partials(const cr_geometry* g, const cr_qsa_args* a, int 
  * ------------------------------------------------------------------------------------------------- */
 const char* cr_last_error(void);   /* text of the last error on this thread */
 int cr_version(void);
-/* 0, or non-zero if a bounded device-side wait gave up since the library was loaded (synchronises the device):
- * bit 0 = in the tcgen05 GDN scan, bit 1 = in the tcgen05 QSA scoring kernel.  No counterpart in the reference,
- * whose kernels have no waits that can give up. */
+/* Every wait inside a kernel of this library (on an mbarrier that a bulk copy or a tensor-core commit completes) is
+ * bounded in time.  A wait that runs out sets a bit of a device status word, after which the kernel issues no more
+ * copies or tensor-core work, runs to its end, frees its tensor memory and returns: the context stays usable, the
+ * outputs of that launch are undefined.  cr_device_status() synchronises the current device and returns the word
+ * (0 = no wait has given up since the library was loaded or the word was cleared): bit 0 = tcgen05 GDN scan,
+ * bit 1 = tcgen05 QSA scoring, bit 2 = tcgen05 QSA prefill attention, bit 3 = cr_debug_wait_timeout.
+ * cr_device_check() is the same read as a status code: CR_OK or CR_ERR_TIMEOUT (cr_last_error() names the kernel).
+ * cr_device_status_clear() zeroes the word.  All three synchronise: call them outside stream capture, e.g. once per
+ * forward pass.  No counterpart in the reference, whose waits spin without bound
+ * (engine/layers/qsa_long.h:516-518, engine/layers/kernels/prefill_gdn.h:964-979). */
 int cr_device_status(void);
+cr_status cr_device_check(void);
+cr_status cr_device_status_clear(void);
+
+/* Tuning options of the process, in place of environment switches (the reference reads CRUCIBLE_* switches through
+ * one registry, engine/switches.h:44-110; build macros CRUCIBLE_QSA_SPLITS etc.).  cr_get_options() returns the
+ * current values, cr_set_options() validates and installs new ones; set them before the first launch that they
+ * affect and not concurrently with launches. */
+typedef struct {
+  int gdn_part_chunks;   /* 64-row chunks per internal part of a long cr_gdn_prefill call: 32..4096 (default 111) */
+  int pdl;               /* 1 = programmatic dependent launch along the decode chain (default), 0 = plain launches */
+  int qsa_score_simt;    /* 1 = prefill scores with fp32 FMAs instead of tcgen05 (default 0; an A/B and debugging aid) */
+  int qsa_union_rows;    /* rows per union tile of the prefill attention: 0 = automatic, 8, 16; -1 = row-wise kernel */
+} cr_options;
+cr_status cr_get_options(cr_options* out);
+cr_status cr_set_options(const cr_options* in);
 /* Number of kernels this library has launched in this process (for launch accounting in benches). */
 unsigned long long cr_kernel_launches(void);
 
@@ -284,10 +309,15 @@ cr_status cr_profile_enable(int on);
 cr_status cr_profile_begin(void* stream);
 int cr_profile_collect(char* names, float* ms, int* calls, int max_stages);
 
-/* Self-check of the tensor-core (tcgen05) building blocks: D[128][N] = A B^T in tf32 on one CTA, A [128][K] and
- * B [N][K] both K-major.  *status (device int) becomes 1 if the bounded wait on the MMA gave up.
- * No counterpart in the reference. */
+/* Self-check of the tensor-core (tcgen05) building blocks, exported as a test hook: D[128][N] = A B^T in tf32 on
+ * one CTA, A [128][K] and B [N][K] both K-major.  *status (device int) becomes 1 if the bounded wait on the MMA
+ * gave up.  No counterpart in the reference. */
 cr_status cr_debug_umma_gemm(const float* A, const float* B, float* D, int K, int N, int* status, void* stream);
+/* Test hook for the bounded waits: one CTA waits up to max_us microseconds on an mbarrier that nothing will ever
+ * complete (no copy, no tensor-core work pending), then sets *status (device int) to 1, raises bit 3 of the device
+ * status word and returns normally.  Shows that a wait that runs out ends the kernel and leaves the context
+ * usable.  max_us in 1..100000.  No counterpart in the reference. */
+cr_status cr_debug_wait_timeout(int* status, unsigned max_us, void* stream);
 
 #ifdef __cplusplus
 }

@@ -88,3 +88,27 @@ def test_gdn_prefill_part_schedule_covers_every_row():
         if rows >= 32768:
             assert n[0] == 32 * 64 and n[k - 1] <= n[k - 2] <= n[k - 3]
     assert capi.lib.cr_gdn_prefill_parts(0, None, None, 0) == 0
+
+
+def test_options_are_validated_and_bound_the_part_schedule():
+    """cr_get_options / cr_set_options are host-only: bad values are refused and leave the options unchanged; with a
+    part option below the default every part of a long call, the short first one included, stays within the part the
+    workspace is sized for."""
+    import ctypes as C
+    from crucible_strix_halo_b200 import capi
+    old = capi.get_options()
+    assert (old.gdn_part_chunks, old.pdl, old.qsa_score_simt) == (111, 1, 0)
+    for bad in (dict(gdn_part_chunks=8), dict(gdn_part_chunks=5000), dict(pdl=2), dict(qsa_score_simt=-1), dict(qsa_union_rows=5)):
+        with pytest.raises(capi.CrError):
+            capi.set_options(**bad)
+        assert capi.get_options().gdn_part_chunks == 111
+    try:
+        for chunks in (32, 33, 50, 111, 400):
+            capi.set_options(gdn_part_chunks=chunks)
+            for rows in (chunks * 64, chunks * 64 + 1, 3 * chunks * 64 + 5, 32768, 262144):
+                first, n = (C.c_int * 256)(), (C.c_int * 256)()
+                k = capi.lib.cr_gdn_prefill_parts(rows, first, n, 256)
+                assert 1 <= k <= 256 and sum(n[:k]) == rows
+                assert max(n[:k]) <= chunks * 64, (chunks, rows, list(n[:k]))
+    finally:
+        capi.check(capi.lib.cr_set_options(C.byref(old)))

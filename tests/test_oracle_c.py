@@ -9,7 +9,7 @@ from oracle import attn_oracle as ao
 
 @pytest.fixture(scope="module")
 def clib():
-    from crucible_strix_halo_b200 import build
+    from oracle import build
     lib = C.CDLL(build.build_oracle())
     lib.oracle_threads.restype = C.c_int
     return lib

@@ -20,3 +20,24 @@ def test_umma_gemm(K, N):
     ref = A.double() @ B.double().t()
     err = (D.double() - ref).abs().max().item()
     assert err < 3e-2 * (K ** 0.5) / 8 + 1e-3, "max error %g" % err     # tf32 operands: about 1e-3 relative per term
+
+
+def test_bounded_wait_runs_out_and_the_context_stays_usable():
+    """A wait on an mbarrier that nothing completes gives up after its time limit: the kernel returns, the status word
+    and cr_device_check() report it (CR_ERR_TIMEOUT), clearing works, and the next ordinary launch is correct."""
+    from crucible_strix_halo_b200 import capi
+    import time
+    capi.check(capi.lib.cr_device_status_clear())
+    assert capi.lib.cr_device_status() == 0 and capi.lib.cr_device_check() == capi.OK
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    t0 = time.perf_counter()
+    capi.check(capi.lib.cr_debug_wait_timeout(status.data_ptr(), 200, None))      # 200 microseconds
+    torch.cuda.synchronize()
+    assert time.perf_counter() - t0 < 5.0                       # it returned on its own
+    assert int(status.item()) == 1
+    assert capi.lib.cr_device_status() == 8
+    assert capi.lib.cr_device_check() == capi.ERR_TIMEOUT
+    assert b"debug_wait_kernel" in capi.lib.cr_last_error()
+    capi.check(capi.lib.cr_device_status_clear())
+    assert capi.lib.cr_device_status() == 0 and capi.lib.cr_device_check() == capi.OK
+    test_umma_gemm(64, 64)                                      # the context is intact
