@@ -193,7 +193,7 @@ class GdnPrefill32k:
 
     def config(self):
         return {"workload": self.name, "seq_len": self.T, "gdn_heads": "16qk/32v x128", "chunk": 64, "sessions_per_gpu": 1,
-                "algo": {0: "serial_f32", 1: "chunk64_tcgen05", 2: "chunk64_mma_sync"}[self.algo],
+                "algo": {0: "serial_f32", 1: "chunk64_tcgen05"}[self.algo],
                 "l2": "inputs (0.8 GB per step) exceed the 126 MB L2"}
 
 
@@ -474,7 +474,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--workload", default="gdn_prefill_32k", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--algo", default="auto", choices=["auto", "serial", "chunk", "mma"])
+    ap.add_argument("--algo", default="auto", choices=["auto", "serial", "chunk"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--seq", type=int, default=0, help="gdn_prefill_32k only: a shorter sequence, for profiler captures")
     args = ap.parse_args()
@@ -493,7 +493,7 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
         dist.barrier()
     from crucible_strix_halo_b200 import capi
-    algo = {"serial": capi.GDN_SERIAL_F32, "chunk": capi.GDN_CHUNK_TC, "mma": capi.GDN_CHUNK_MMA}.get(args.algo)
+    algo = {"serial": capi.GDN_SERIAL_F32, "chunk": capi.GDN_CHUNK_TC}.get(args.algo)
     if algo is None:
         algo = capi.GDN_CHUNK_TC if capi.lib.cr_gdn_algo_available(capi.GDN_CHUNK_TC) else capi.GDN_SERIAL_F32
     if args.seq and args.workload == "gdn_prefill_32k":

@@ -12,6 +12,76 @@ import sys
 import numpy as np
 
 
+class _Prescribed:
+    """Stands in for a decoded weight matrix: `lhs @ self` returns had(want), so that the reference's
+    linear() = had(had(x * suh) @ what) * svh yields `want` (its Hadamard transform is an involution)."""
+    __array_ufunc__ = None
+
+    def __init__(self, had_want):
+        self.had_want = had_want
+
+    def __rmatmul__(self, lhs):
+        assert lhs.shape[0] == self.had_want.shape[0]
+        return self.had_want
+
+
+class _StubCkpt:
+    """The two methods ref/oracle.py::gdn and ::qsa use (ref/oracle.py:47-55)."""
+
+    def __init__(self, arrays, lins):
+        self.arrays, self.lins = arrays, lins
+
+    def f64(self, name):
+        return np.asarray(self.arrays[name], np.float64)
+
+    def lin(self, prefix):
+        return self.lins[prefix]
+
+
+def layer_vectors(ro):
+    out = {}
+    f16 = lambda a: np.asarray(a, np.float16).astype(np.float64)          # exactly representable inputs
+    ident = lambda want: (_Prescribed(ro.had(want)), np.ones(1), np.ones(1))
+
+    class _Identity:
+        __array_ufunc__ = None
+
+        def __rmatmul__(self, lhs):
+            return lhs
+
+    # ---- GDN: 20 rows, 48 value / 16 key heads
+    rng = np.random.default_rng(21)
+    n, hid = 20, 128
+    x = f16(rng.normal(size=(n, hid)))
+    qkv, z = f16(rng.normal(size=(n, 10240))), f16(rng.normal(size=(n, 6144)))
+    wa, wb = f16(rng.normal(size=(48, hid)) * 0.1), f16(rng.normal(size=(48, hid)) * 0.1)
+    conv = f16(rng.normal(size=(10240, 4)) * 0.5)
+    A_log, dtb = f16(np.clip(rng.normal(-1, 1.5, 48), -5, 1.5)), f16(rng.normal(size=48) * 0.5)
+    gamma = f16(1 + 0.1 * rng.normal(size=128))
+    p = "g."
+    ck = _StubCkpt({p + "in_proj_a.weight": wa, p + "in_proj_b.weight": wb, p + "conv1d.weight": conv[:, None, :],
+                    p + "A_log": A_log, p + "dt_bias": dtb, p + "norm.weight": gamma},
+                   {p + "in_proj_qkv": ident(qkv), p + "in_proj_z": ident(z), p + "out_proj": (_Identity(), np.ones(1), np.ones(1))})
+    o = ro.gdn(ck, p, x)                                   # = had(had(core output)) = core output
+    for name, val in dict(x=x, qkv=qkv, z=z, wa=wa, wb=wb, conv=conv, A_log=A_log, dt_bias=dtb, gamma=gamma).items():
+        out["layer_gdn_" + name] = val.astype(np.float16)
+    out["layer_gdn_out"] = o
+    # ---- QSA: 24 rows, dense causal, 24 query / 2 KV heads
+    rng = np.random.default_rng(22)
+    n = 24
+    x = np.zeros((n, hid))
+    q, k, v = f16(rng.normal(size=(n, 24 * 512))), f16(rng.normal(size=(n, 512))), f16(rng.normal(size=(n, 512)))
+    qn, kn = f16(0.1 * rng.normal(size=256)), f16(0.1 * rng.normal(size=256))
+    p = "a."
+    ck = _StubCkpt({p + "q_norm.weight": qn, p + "k_norm.weight": kn},
+                   {p + "q_proj": ident(q), p + "k_proj": ident(k), p + "v_proj": ident(v), p + "o_proj": (_Identity(), np.ones(1), np.ones(1))})
+    o = ro.qsa(ck, p, x)
+    for name, val in dict(q=q, k=k, v=v, q_norm=qn, k_norm=kn).items():
+        out["layer_qsa_" + name] = val.astype(np.float16)
+    out["layer_qsa_out"] = o
+    return out
+
+
 def main(ref_root):
     sys.path.insert(0, os.path.join(ref_root, "ref"))
     import prefill_ref as pr          # ref/prefill_ref.py
@@ -78,6 +148,18 @@ def main(ref_root):
     except Exception as e:  # torch/safetensors missing: helpers stay unpinned, recurrences are pinned
         print("ref/oracle.py helpers not recorded:", e)
         out["helpers"] = np.array(0)
+
+    # (6) the reference's own layer functions ref/oracle.py::gdn (:101-130) and ::qsa (:147-165), run at the
+    # reference geometry (48/16 GDN heads, 24/2 QSA heads) on a duck-typed checkpoint: they only call ck.f64(name)
+    # and ck.lin(prefix).  Projection outputs are prescribed (fp16-exact values, so the stored inputs are exact),
+    # the output projection is the identity, so what comes back is the layer core's gated output.
+    try:
+        import oracle as ro
+        out.update(layer_vectors(ro))
+        out["layers"] = np.array(1)
+    except Exception as e:
+        print("ref/oracle.py layer functions not recorded:", e)
+        out["layers"] = np.array(0)
 
     dst = os.path.join(os.path.dirname(os.path.abspath(__file__)), "ref_vectors.npz")
     np.savez_compressed(dst, **out)

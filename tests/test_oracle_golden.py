@@ -141,3 +141,49 @@ def test_gdn_layer_chunk_equals_serial():
     o2, s2, _ = ao.gdn_layer(*args, chunk=64)
     np.testing.assert_allclose(o2, o1, rtol=1e-9, atol=1e-11)
     np.testing.assert_allclose(s2, s1, rtol=1e-9, atol=1e-11)
+
+
+def test_gdn_layer_matches_the_references_own_layer_function():
+    """ref/oracle.py::gdn (:101-130) run on a duck-typed checkpoint at the reference geometry (48 value / 16 key
+    heads): conv + SiLU, L2 norms, head repetition, gates, serial recurrence from a zero state, gated RMSNorm."""
+    assert int(G["layers"]) == 1, "golden file was generated without ref/oracle.py's layer functions"
+    f = lambda name: G["layer_gdn_" + name].astype(np.float64)
+    g = ao.Geometry(hidden=128, q_heads=24, kv_heads=2, gdn_vheads=48, gdn_kheads=16)
+    x = f("x")
+    a, b = x @ f("wa").T, x @ f("wb").T                 # ref/oracle.py:105-106
+    out, state, _ = ao.gdn_layer(f("qkv"), f("z"), a, b, f("conv"), f("A_log"), f("dt_bias"), f("gamma"), np.zeros((48, 128, 128)), g)
+    np.testing.assert_allclose(out, G["layer_gdn_out"], rtol=1e-9, atol=1e-11)
+    # the chunked form of the same layer agrees as well
+    out_c, _, _ = ao.gdn_layer(f("qkv"), f("z"), a, b, f("conv"), f("A_log"), f("dt_bias"), f("gamma"), np.zeros((48, 128, 128)), g, chunk=64)
+    np.testing.assert_allclose(out_c, G["layer_gdn_out"], rtol=1e-8, atol=1e-10)
+
+
+def test_qsa_dense_rows_match_the_references_own_layer_function():
+    """ref/oracle.py::qsa (:147-165) on a duck-typed checkpoint at the reference geometry (24 query / 2 KV heads):
+    CN-RMSNorm with (1 + w), partial RoPE, scale 1/16, causal softmax, KV head h // 12, sigmoid gate.  The oracle's
+    cache holds K and V in fp16 (as the engine does), the reference function keeps them in fp64: the tolerance is the
+    fp16 rounding of K (2^-11 relative on a logit of a few units) and V."""
+    assert int(G["layers"]) == 1
+    f = lambda name: G["layer_qsa_" + name].astype(np.float64)
+    g = ao.Geometry(hidden=128, q_heads=24, kv_heads=2, gdn_vheads=48, gdn_kheads=16)
+    n = len(f("q"))
+    cache = ao.QsaCache(g, 64)
+    norms = [1 + f("q_norm"), 1 + f("k_norm"), np.ones(128), np.ones(128)]
+    out, sels, _, qn, _ = ao.qsa_rows(f("q").reshape(n, 24, 512), f("k"), f("v"), np.zeros((n, 640)), norms, cache, 0, g, return_detail=True)
+    assert all(s is None for s in sels)                  # dense below 512 blocks
+    ref = G["layer_qsa_out"]
+    assert np.abs(out - ref).max() < 4e-3 and np.linalg.norm(out - ref) / np.linalg.norm(ref) < 1e-3
+    # with K and V kept in fp64 (no cache rounding) the two agree to rounding: the algebra is the same
+    D = 256
+    q64 = f("q").reshape(n, 24, 512)
+    pos = np.arange(n, dtype=np.float64)
+    kn = ao.rope64(ao.cn_rmsnorm(f("k").reshape(n, 2, D), norms[1]), pos, g)
+    v64 = f("v").reshape(n, 2, D)
+    exact = np.empty((n, 24, D))
+    for r in range(n):
+        for h in range(24):
+            lg = kn[:r + 1, h // 12] @ qn[r, h] / 16.0
+            pr = np.exp(lg - lg.max())
+            exact[r, h] = (pr / pr.sum()) @ v64[:r + 1, h // 12]
+    exact = (exact * ao.sigmoid(q64[..., D:])).reshape(n, -1)
+    np.testing.assert_allclose(exact, ref, rtol=1e-9, atol=1e-11)
