@@ -60,6 +60,10 @@ class QsaArgs(C.Structure):
                 ("pack_rows", C.c_int), ("pack_off", C.c_int), ("mrope", P), ("rope", P)]
 
 
+class QsaUnion(C.Structure):
+    _fields_ = [("list", P), ("count", P)]
+
+
 class QsaPrefillArgs(C.Structure):
     _fields_ = [("input", QsaArgs), ("q_hi", P), ("scratch", P), ("scratch_bytes", C.c_size_t)]
 
@@ -93,11 +97,17 @@ _protos = {
     "cr_qsa_prefill_scratch_bytes": (C.c_size_t, [G, C.c_int]),
     "cr_qsa_prefill_cache": (C.c_int, [G, C.POINTER(QsaArgs), P]),
     "cr_qsa_prefill": (C.c_int, [G, C.POINTER(QsaPrefillArgs), C.c_int, C.c_int, P]),
+    "cr_qsa_prefill_attend": (C.c_int, [G, C.POINTER(QsaPrefillArgs), C.c_int, C.c_int, P]),
+    "cr_qsa_union_list_ints": (C.c_size_t, [G, C.c_int]),
+    "cr_qsa_union_tile_rows": (C.c_int, [G]),
+    "cr_qsa_union_build": (C.c_int, [G, C.POINTER(QsaArgs), C.POINTER(QsaUnion), P]),
     "cr_qsa_shard_candidates": (C.c_int, [G, C.POINTER(QsaArgs), C.c_int, C.c_int, P, P, P]),
+    "cr_qsa_shard_select": (C.c_int, [G, C.POINTER(QsaArgs), C.c_int, C.c_int, P, P, P]),
     "cr_qsa_merge_candidates": (C.c_int, [G, C.POINTER(QsaArgs), C.c_int, P, P, P]),
     "cr_qsa_shard_attn": (C.c_int, [G, C.POINTER(QsaArgs), C.c_int, C.c_int, P, P, C.c_size_t, P]),
     "cr_qsa_merge_partials": (C.c_int, [G, C.POINTER(QsaArgs), C.c_int, P, C.c_int, P]),
     "cr_debug_umma_gemm": (C.c_int, [P, P, P, C.c_int, C.c_int, P, P]),
+    "cr_debug_umma_f16_gemm": (C.c_int, [P, P, P, C.c_int, C.c_int, C.c_int, P, P]),
     "cr_last_error": (C.c_char_p, []),
     "cr_version": (C.c_int, []),
     "cr_device_status": (C.c_int, []),

@@ -1,5 +1,6 @@
 // Shared declarations of the QSA kernels (qsa_prep.cu, qsa_select.cu, qsa_attn.cu, qsa_prefill.cu).
 #pragma once
+#include <climits>
 #include "common.cuh"
 
 namespace cr {
@@ -9,6 +10,7 @@ struct QsaParams {
   cr_qsa_args span[kMaxSpans];
   int base[kMaxSpans];
   int Hq, Hkv, n;
+  int b_lo, b_hi;          // scoring only: the blocks [b_lo, b_hi) are scored (a rank's own blocks; 0, INT_MAX = all)
 };
 
 cr_status qsa_validate(const cr_geometry* g, const cr_qsa_args* spans, int n_spans, int max_rows, const char* who);
@@ -16,11 +18,10 @@ int qsa_max_rows(const cr_qsa_args* spans, int n);
 void qsa_fill_params(QsaParams& P, const cr_geometry* g, const cr_qsa_args* spans, int n);
 cr_status qsa_prep_launch(const cr_geometry* g, const cr_qsa_args* spans, int n_spans, int u0, __half* q_hi, int q_skip,
                           cudaStream_t stream);
-cr_status qsa_score_launch(const cr_geometry* g, const cr_qsa_args* spans, int n_spans, cudaStream_t stream);
+cr_status qsa_score_launch(const cr_geometry* g, const cr_qsa_args* spans, int n_spans, cudaStream_t stream, int b_lo = 0, int b_hi = INT_MAX);
 // Prefill parts (many rows): the scores as four GEMMs on tcgen05 tensor cores.
 cr_status qsa_score_tc_launch(const QsaParams& P, int Rmax, int n, cudaStream_t stream);
 cr_status qsa_topk_launch(const cr_geometry* g, const cr_qsa_args* spans, int n_spans, cudaStream_t stream);
-cr_status qsa_topk_cluster_launch(const QsaParams& P, int Rmax, int n, int nb_max, cudaStream_t stream);
 cr_status qsa_select_launch(const cr_geometry* g, const cr_qsa_args* spans, int n_spans, cudaStream_t stream);
 // splits: KV splits per (row, KV head). p0/p1: position window (shard mode) or 0 / INT_MAX.
 cr_status qsa_attn_launch(const cr_geometry* g, const cr_qsa_args* spans, int n_spans, float* partials, int splits,

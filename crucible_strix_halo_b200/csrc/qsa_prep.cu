@@ -156,6 +156,7 @@ void qsa_fill_params(QsaParams& P, const cr_geometry* g, const cr_qsa_args* span
   int base = 0;
   for (int s = 0; s < n; ++s) { P.base[s] = base; base += spans[s].R; }
   P.Hq = g->q_heads; P.Hkv = g->kv_heads; P.n = n;
+  P.b_lo = 0; P.b_hi = INT_MAX;
 }
 
 cr_status qsa_prep_launch(const cr_geometry* g, const cr_qsa_args* spans, int n_spans, int u0, __half* q_hi, int q_skip,

@@ -28,18 +28,8 @@ constexpr int kQopBytes = 4 * 2 * 16 * kScRows * 16;      // [head][hi/lo][dim /
 constexpr int kPopBytes = 2 * 16 * kScBlocks * 16;        // [hi/lo][dim / 8][block][8 fp16]
 constexpr size_t kScoreSmem = kQopBytes + kPopBytes + 128;
 
-// kind::f16 with fp16 operands (format 0), fp32 accumulation, both operands K-major.
-__host__ __device__ constexpr uint32_t idesc_f16(int M, int N) {
-  return (1u << 4) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
-}
-__device__ __forceinline__ void mma_f16_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(d_tmem),
-      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
+using umma::mma_f16_ss;
+__host__ __device__ constexpr uint32_t idesc_f16(int M, int N) { return umma::idesc_f16(M, N, false, false); }
 // eight fp32 values -> fp16 heads and fp16 remainders, each packed into 16 bytes
 __device__ __forceinline__ void split8(const float (&x)[8], uint4& hi, uint4& lo) {
   unsigned h[4], l[4];
@@ -68,10 +58,12 @@ __global__ void __launch_bounds__(kScThreads, 1) qsa_score_tc_kernel(const __gri
   const int r0 = blockIdx.x * kScRows;
   if (r0 >= a.R) return;
   const int rows = min(kScRows, a.R - r0);
-  const int nb_hi = (a.pos0 + r0 + rows) / 4;             // blocks visible to the last row of the tile
-  if (nb_hi <= CR_SEL_BLOCKS) return;
-  const int tiles = (nb_hi + kScBlocks - 1) / kScBlocks;
-  const int t0 = (int)((long long)tiles * blockIdx.y / gridDim.y), t1 = (int)((long long)tiles * (blockIdx.y + 1) / gridDim.y);
+  const int nb_all = (a.pos0 + r0 + rows) / 4;            // blocks visible to the last row of the tile
+  if (nb_all <= CR_SEL_BLOCKS) return;
+  const int nb_hi = min(nb_all, P.b_hi);                  // the scored range [b_lo, b_hi) of a rank
+  const int tile_lo = P.b_lo / kScBlocks, tiles = (nb_hi + kScBlocks - 1) / kScBlocks - tile_lo;
+  if (tiles <= 0) return;
+  const int t0 = tile_lo + (int)((long long)tiles * blockIdx.y / gridDim.y), t1 = tile_lo + (int)((long long)tiles * (blockIdx.y + 1) / gridDim.y);
   if (t0 >= t1) return;
   const int t = threadIdx.x, w = t >> 5, l = t & 31;
 
@@ -190,7 +182,7 @@ __global__ void __launch_bounds__(kScThreads, 1) qsa_score_tc_kernel(const __gri
       umma::fence_before_sync();
       __syncwarp();
       if (l == 0) umma::mbar_arrive_relaxed(&accFree[buf]);
-      if (b < nb_hi) {
+      if (b < nb_hi && b >= P.b_lo) {
         float* dst = a.scores + (size_t)r0 * a.sstride + b;
 #pragma unroll
         for (int c = 0; c < kScRows; ++c)

@@ -52,6 +52,59 @@ __global__ void __launch_bounds__(128) umma_test_kernel(const float* A, const fl
   if (w == 0) umma::tmem_dealloc(tmem, 128);
 }
 
+// D[128][N] = A[128][K] B[K][N] with fp16 operands (kind::f16): A K-major, B as it lies in memory when the N index
+// is contiguous (MN-major: the layout of a V tile, keys x channels).  Shared-memory images, no swizzle, 16-byte units:
+//   A: unit (k / 8, row)      at ((k / 8) * 128 + row) * 16
+//   B: unit (n / 8, k)        at ((n / 8) * K + k) * 16      core matrix = 8 k x 8 n, n contiguous
+// variant 0: B descriptor with LBO = step between core matrices along N, SBO = step along K; variant 1: swapped.
+__global__ void __launch_bounds__(128) umma_f16_test_kernel(const __half* A, const __half* B, float* D, int K, int N, int variant, int* status) {
+  extern __shared__ __align__(128) unsigned char smb[];
+  unsigned char* As = smb;
+  unsigned char* Bs = smb + (size_t)128 * K * 2;
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ uint32_t tmem_slot;
+  const int t = threadIdx.x, w = t >> 5;
+  for (int u = t; u < 128 * K / 8; u += 128) {
+    const int row = u % 128, kc = u / 128;
+    *reinterpret_cast<uint4*>(As + ((size_t)kc * 128 + row) * 16) = *reinterpret_cast<const uint4*>(A + (size_t)row * K + kc * 8);
+  }
+  for (int u = t; u < K * N / 8; u += 128) {
+    const int nc = u % (N / 8), k = u / (N / 8);
+    *reinterpret_cast<uint4*>(Bs + ((size_t)nc * K + k) * 16) = *reinterpret_cast<const uint4*>(B + (size_t)k * N + nc * 8);
+  }
+  if (t == 0) { umma::mbar_init(&bar, 1); umma::mbar_fence_init(); }
+  if (w == 0) umma::tmem_alloc(&tmem_slot, 256);
+  umma::fence_async_smem();
+  umma::fence_before_sync();
+  __syncthreads();
+  umma::fence_after_sync();
+  const uint32_t tmem = tmem_slot;
+  if (t == 0) {
+    const uint32_t idesc = umma::idesc_f16(128, N, false, true);
+    const uint32_t step_n = (uint32_t)K * 16u, step_k = 128u;
+    for (int k0 = 0; k0 < K; k0 += 16) {
+      const uint64_t da = umma::smem_desc(As + (size_t)(k0 / 8) * 128 * 16, 128 * 16, 128);
+      const uint64_t db = variant == 0 ? umma::smem_desc(Bs + (size_t)k0 * 16, step_n, step_k) : umma::smem_desc(Bs + (size_t)k0 * 16, step_k, step_n);
+      umma::mma_f16_ss(tmem, da, db, idesc, k0 > 0);
+    }
+    umma::commit(&bar);
+  }
+  const bool ok = umma::mbar_wait(&bar, 0);
+  umma::fence_after_sync();
+  for (int c0 = 0; c0 < N; c0 += 32) {
+    float v[32];
+    umma::tmem_ld32(umma::tmem_addr(tmem, w, c0), v);
+    if (ok) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) D[(size_t)t * N + c0 + i] = v[i];
+    }
+  }
+  if (!ok && t == 0) *status = 1;
+  umma::fence_before_sync();
+  __syncthreads();
+  if (w == 0) umma::tmem_dealloc(tmem, 256);
+}
+
 CR_DEFINE_STATUS_WORD(debug_wait)
 
 // One CTA of 32 threads: lane 0 waits on an mbarrier that nothing completes.  No copy and no tensor-core work is
@@ -74,6 +127,19 @@ extern "C" cr_status cr_debug_wait_timeout(int* status, unsigned max_us, void* s
   use_stream((cudaStream_t)stream);
   debug_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(status, (unsigned long long)max_us * 1000ull);
   CR_LAUNCH_CHECK("debug_wait_kernel");
+  return CR_OK;
+}
+
+extern "C" cr_status cr_debug_umma_f16_gemm(const uint16_t* A, const uint16_t* B, float* D, int K, int N, int variant, int* status, void* stream) {
+  using namespace cr;
+  CR_REQUIRE(A && B && D && status, "cr_debug_umma_f16_gemm: null buffer");
+  CR_REQUIRE(K >= 16 && K % 16 == 0 && K <= 128 && N >= 32 && N % 32 == 0 && N <= 256, "cr_debug_umma_f16_gemm: K in 16..128 step 16, N in 32..256 step 32");
+  CR_REQUIRE(variant == 0 || variant == 1, "cr_debug_umma_f16_gemm: variant 0 or 1");
+  const size_t smem = (size_t)(128 + N) * K * 2;
+  CR_CUDA(cudaFuncSetAttribute(umma_f16_test_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  use_stream((cudaStream_t)stream);
+  umma_f16_test_kernel<<<1, 128, smem, (cudaStream_t)stream>>>(reinterpret_cast<const __half*>(A), reinterpret_cast<const __half*>(B), D, K, N, variant, status);
+  CR_LAUNCH_CHECK("umma_f16_test_kernel");
   return CR_OK;
 }
 

@@ -4,7 +4,7 @@ Natural shards need no exchange: sessions (decode / verify) and sequences (prefi
 heads are independent recurrences (GdnHeadShard).  One long sequence of the QSA layer is split over the KV positions:
 
     rank g owns positions [lo_g, hi_g)  (whole 4-token blocks; the newest rows belong to the last rank)
-    1. local scores + top-512 candidates over the owned blocks          cr_qsa_shard_candidates
+    1. local scores + top-512 candidates over the owned blocks          cr_qsa_shard_select
     2. all-gather candidates [ranks][rows][512] (score, id)             -> every rank: cr_qsa_merge_candidates
     3. attention over the owned part of the attended positions          cr_qsa_shard_attn -> (m, l, acc[256])
     4. all-gather partials [ranks][rows][heads][258]                    -> cr_qsa_merge_partials (LSE merge + gate)
@@ -98,6 +98,17 @@ class SplitKvQsa:
         return self.backend.merge_partials(self._all_gather(parts))
 
 
+def run_emulated_ranks(backend, world, total_positions):
+    """The exchange of SplitKvQsa.run with the ranks played one after the other by ONE process on one device (tests and
+    single-GPU checks): every rank's candidates, one merge, every rank's partials, one merge."""
+    import torch
+    ranges = [kv_block_range(total_positions, world, r) for r in range(world)]
+    cands = [backend.shard_candidates(b0, b1) for (b0, b1), _ in ranges]
+    backend.merge_candidates(torch.stack([c[0] for c in cands]), torch.stack([c[1] for c in cands]))
+    parts = [backend.shard_attn(p0, p1).clone() for _, (p0, p1) in ranges]
+    return backend.merge_partials(torch.stack(parts))
+
+
 class CudaQsaBackend:
     """The C-ABI calls behind SplitKvQsa for one prepared part: `args` is the cr_qsa_args of the part (scores
     already computed for the owned blocks by cr_qsa_select or cr_qsa_prefill's score stage)."""
@@ -113,9 +124,10 @@ class CudaQsaBackend:
         return C.c_void_p(self.torch.cuda.current_stream().cuda_stream)
 
     def shard_candidates(self, b0, b1):
+        """Scores of the rank's own blocks [b0, b1), then its best 512 per row."""
         t = self.torch
         cs = t.empty(self.rows, 512, device="cuda"); ci = t.empty(self.rows, 512, device="cuda", dtype=t.int32)
-        self.capi.check(self.capi.lib.cr_qsa_shard_candidates(C.byref(self.g), self.arr, b0, b1, cs.data_ptr(), ci.data_ptr(), self._stream()))
+        self.capi.check(self.capi.lib.cr_qsa_shard_select(C.byref(self.g), self.arr, b0, b1, cs.data_ptr(), ci.data_ptr(), self._stream()))
         return cs, ci
 
     def merge_candidates(self, all_scores, all_ids):

@@ -237,6 +237,20 @@ typedef struct {
 
 size_t cr_qsa_prefill_scratch_bytes(const cr_geometry* g, int rows);
 
+/* Replaces struct QsaUnion (engine/layers/kernels/prefill_qsa_union.h:18-21).  A tile is cr_qsa_union_tile_rows(g)
+ * consecutive rows (128 / query heads per KV head: 16 or 10; the reference uses 4).  list: per tile
+ * cr_qsa_union_list_ints(g, rows) / tiles ints = pairs (block id, row mask), ascending block ids; bit r of the mask:
+ * row r of the tile attends the block (the reference packs block | mask << 24 into one int, which caps the mask at
+ * 4 rows).  count: entries per tile.  cr_qsa_prefill builds the lists in its own scratch; cr_qsa_union_build is the
+ * stage alone (QsaUnionBuildKernel, prefill_qsa_union.h:25-68), from a->sel / a->nsel / a->pos0 / a->R. */
+typedef struct {
+  int* list;
+  int* count;
+} cr_qsa_union;
+size_t cr_qsa_union_list_ints(const cr_geometry* g, int rows);   /* QsaUnionListInts, prefill_qsa_union.h:745 */
+int cr_qsa_union_tile_rows(const cr_geometry* g);
+cr_status cr_qsa_union_build(const cr_geometry* g, const cr_qsa_args* a, const cr_qsa_union* u, void* stream);
+
 /* Replaces LaunchQsaPrefillCache (engine/layers/kernels/prefill_qsa.h:248-260): cache half of a prefill part. */
 cr_status cr_qsa_prefill_cache(const cr_geometry* g, const cr_qsa_args* a, void* stream);
 
@@ -245,6 +259,11 @@ cr_status cr_qsa_prefill_cache(const cr_geometry* g, const cr_qsa_args* a, void*
  * selection, attention with the fused gate.  skip: leading rows that only get cache work (multiple of 16). */
 cr_status cr_qsa_prefill(const cr_geometry* g, const cr_qsa_prefill_args* a, int skip, cr_out_format fmt,
                          void* stream);
+/* The attention stage of a part alone (LaunchQsaUnionFlashGate, prefill_qsa_union.h:762-778): union lists + tiled
+ * attention + gate for rows [skip, R), from selections already in a->input.sel / nsel, prepared queries in a->q_hi
+ * and a cache that holds the part.  The stage a bench drives with injected selections. */
+cr_status cr_qsa_prefill_attend(const cr_geometry* g, const cr_qsa_prefill_args* a, int skip, cr_out_format fmt,
+                                void* stream);
 
 /* ---------------------------------------------------------------------------------------------------
  * Split-KV across devices (no counterpart in the single-device reference; the partial record is the
@@ -256,6 +275,11 @@ cr_status cr_qsa_prefill(const cr_geometry* g, const cr_qsa_prefill_args* a, int
  * cand_scores/cand_ids: [rows][512]; unused slots hold score -1 and id -1. */
 cr_status cr_qsa_shard_candidates(const cr_geometry* g, const cr_qsa_args* a, int b0, int b1,
                                   float* cand_scores, int* cand_ids, void* stream);
+/* The same with the scoring in front: scores of blocks [b0, b1) only (the rank reads nothing but its own part of the
+ * pool; the cache pointers of a->c may be bases biased so that absolute positions index the rank's own storage), then
+ * the candidates.  Scores outside [b0, b1) are left untouched. */
+cr_status cr_qsa_shard_select(const cr_geometry* g, const cr_qsa_args* a, int b0, int b1,
+                              float* cand_scores, int* cand_ids, void* stream);
 /* Global selection from the gathered candidates of all ranks [ranks][rows][512]; writes a->sel / a->nsel. */
 cr_status cr_qsa_merge_candidates(const cr_geometry* g, const cr_qsa_args* a, int ranks,
                                   const float* cand_scores, const int* cand_ids, void* stream);
@@ -313,6 +337,11 @@ int cr_profile_collect(char* names, float* ms, int* calls, int max_stages);
  * one CTA, A [128][K] and B [N][K] both K-major.  *status (device int) becomes 1 if the bounded wait on the MMA
  * gave up.  No counterpart in the reference. */
 cr_status cr_debug_umma_gemm(const float* A, const float* B, float* D, int K, int N, int* status, void* stream);
+/* The same self-check for fp16 operands (kind::f16) with the B operand MN-major, i.e. B [K][N] as a V tile lies in the
+ * cache (keys x channels, channels contiguous): D[128][N] = A[128][K] B.  variant selects which of the two descriptor
+ * strides is the step along N (0) or along K (1); the production kernel uses the one this check confirms. */
+cr_status cr_debug_umma_f16_gemm(const uint16_t* A, const uint16_t* B, float* D, int K, int N, int variant, int* status,
+                                 void* stream);
 /* Test hook for the bounded waits: one CTA waits up to max_us microseconds on an mbarrier that nothing will ever
  * complete (no copy, no tensor-core work pending), then sets *status (device int) to 1, raises bit 3 of the device
  * status word and returns normally.  Shows that a wait that runs out ends the kernel and leaves the context

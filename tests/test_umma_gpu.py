@@ -22,6 +22,28 @@ def test_umma_gemm(K, N):
     assert err < 3e-2 * (K ** 0.5) / 8 + 1e-3, "max error %g" % err     # tf32 operands: about 1e-3 relative per term
 
 
+@pytest.mark.parametrize("K,N", [(16, 32), (64, 256), (32, 64), (128, 128)])
+def test_umma_f16_gemm_with_mn_major_b(K, N):
+    """kind::f16 with the B operand as a V tile lies in memory (keys x channels, channels contiguous): the descriptor
+    whose leading offset is the step along keys and whose stride offset is the step along channels gives A B; the
+    other assignment does not.  Pins the convention the tiled prefill attention relies on."""
+    from crucible_strix_halo_b200 import capi
+    g = torch.Generator(device="cuda").manual_seed(K * 7 + N)
+    A = torch.randn(128, K, device="cuda", generator=g).half()
+    B = torch.randn(K, N, device="cuda", generator=g).half()
+    ref = A.double() @ B.double()
+    errs = []
+    for variant in (1, 0):
+        D = torch.zeros(128, N, device="cuda")
+        status = torch.zeros(1, dtype=torch.int32, device="cuda")
+        capi.check(capi.lib.cr_debug_umma_f16_gemm(A.data_ptr(), B.data_ptr(), D.data_ptr(), K, N, variant, status.data_ptr(), None))
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+        errs.append((D.double() - ref).abs().max().item())
+    assert errs[0] < 1e-4, errs
+    assert errs[1] > 1.0, errs
+
+
 def test_bounded_wait_runs_out_and_the_context_stays_usable():
     """A wait on an mbarrier that nothing completes gives up after its time limit: the kernel returns, the status word
     and cr_device_check() report it (CR_ERR_TIMEOUT), clearing works, and the next ordinary launch is correct."""
