@@ -4,12 +4,20 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
 
 A step is one pass of the hot path over one batch of synthetic input.  Workloads:
-  gdn_prefill_32k  one Gated DeltaNet layer, chunked prefill, batch 1, seq 32768, 16 QK x 128 / 32 V x 128 heads,
-                   bf16 inputs, fp32 state (the default: the config the headline metric is quoted on)
-  decode_262k      QSA sparse attention decode + GDN recurrent update, 4 sessions x 262,144-token fp16 KV cache
-  qsa_prefill_262k one QSA layer, the last 2,048-row part of a 262,144-token prefill (scores, top-512, attention)
-Under torchrun (N > 1) every rank runs the same workload on its own sequences / sessions (weak scaling, no
-data-path collective); time is the max over ranks, value the whole-job throughput.
+  gdn_prefill_32k     one Gated DeltaNet layer, chunked prefill, batch 1, seq 32768, 16 QK x 128 / 32 V x 128 heads,
+                      bf16 inputs, fp32 state (the headline: the config the metric is quoted on)
+  decode_262k         QSA sparse attention decode + GDN recurrent update, 4 sessions x 262,144-token fp16 KV cache
+  qsa_prefill_262k    one QSA layer, the last 2,048-row part of a 262,144-token prefill (scores, top-512, attention),
+                      selections from the random indexer (nearly independent per row)
+  qsa_attend_262k_drift  the attention stage of the same part with injected selections that drift from row to row
+                      (a 512-block set, every member replaced with probability 0.25 per row), as real selections overlap
+  verify_131k         speculative verify: 8 sessions x 131,072 context, 9-row spans (1 certain row + 8 drafts), QSA +
+                      GDN with lazy commit, replay counts uniform 0..8
+  prefill_262k_stack  long cold prefill of 262,144 tokens through a 3:1 stack of GDN:QSA layers in 2,048-row parts
+With no --workload the line's headline is gdn_prefill_32k and a `workloads` object carries the figures of all of them
+(shorter runs).  Under torchrun (N > 1) every rank runs the headline on its own sequence (weak scaling, no data-path
+collective) and the `workloads` object carries qsa_prefill_262k_split_kv: ONE sequence whose KV positions are split
+over the ranks, with all-gathers of candidates and partials over NCCL (strong scaling).  Time is the max over ranks.
 Prints ONE JSON line (rank 0).  --impl reference times the CPU restatement of the reference's algorithm
 (oracle/_build/liboracle.so) on the host cores, on a bounded sample of the same workload.
 """
@@ -343,119 +351,467 @@ class QsaPrefill262k:
         self.ses.k.copy_(rn(ctx, 2, 256).half()); self.ses.v.copy_(rn(ctx, 2, 256).half())
         self.ses.ik_pool.copy_(rn(self.ses.ik_pool.numel())); self.ses.ik_raw.copy_(rn(ctx, 128))
         self.plan = layers.QsaPrefillPlan(self.w, R, fmt=capi.OUT_RAW_BF16)
-        self.inp = rn(R, 8192 + 512 + 512 + 640)
-        self.work = torch.empty_like(self.inp)               # q and idx are normalised in place: a fresh copy per step
-        self.h_in = self.inp.cpu().pin_memory()
+        self.inp = {"q": rn(R, 16, 512), "k": rn(R, 512), "v": rn(R, 512), "idx": rn(R, 640)}     # the part's projection rows
+        self.work = {n: torch.empty_like(t) for n, t in self.inp.items() if n in ("q", "idx")}    # normalised in place: a fresh copy per step
+        self.h_in = {n: t.cpu().pin_memory() for n, t in self.inp.items()}
         self.h_out = torch.empty(R, 4096, dtype=torch.bfloat16).pin_memory()
-        self.h2d, self.d2h = self.h_in.numel() * 4, self.h_out.numel() * 2
+        self.h2d, self.d2h = sum(t.numel() * 4 for t in self.h_in.values()), self.h_out.numel() * 2
         self.units_per_step = R
         # gathered K/V rows of every query row + one pass over the pooled keys + the rows in and out
         self.alg_bytes = R * 2051 * 2048 + 65536 * 512 + self.h2d + self.d2h
-        self.kernel_bytes = {"qsa_attn_split_kernel": R * 2051 * 2048}
+        self.kernel_bytes = {"qsa_attn_split_kernel": R * 2051 * 2048, "qsa_flash_tc_kernel": R * 2051 * 2048}
+        # useful flops: attention 4 * Hq * D * n per row + scoring 2 * 4 * 128 * nb per row
+        self.alg_flops = R * (4 * 16 * 256 * 2051) + sum(1024 * ((self.POS0 + r + 1) // 4) for r in range(R))
 
-    def _run(self, src):
-        R = self.R
-        q, k = src[:, :8192].view(R, 16, 512), src[:, 8192:8704]
-        v, idx = src[:, 8704:9216], src[:, 9216:]
-        return self.plan.run(self.ses, q, k, v, idx, self.POS0)
+    def _run(self):
+        return self.plan.run(self.ses, self.work["q"], self.inp["k"], self.inp["v"], self.work["idx"], self.POS0)
 
     def step(self):
-        self.work.copy_(self.inp)
-        return self._run(self.work)
+        for n, t in self.work.items():
+            t.copy_(self.inp[n])
+        return self._run()
 
     step_eager = step
 
     def step_e2e(self):
-        self.work.copy_(self.h_in, non_blocking=True)
-        self.h_out.copy_(self._run(self.work), non_blocking=True)
+        for n, t in self.inp.items():
+            (self.work[n] if n in self.work else t).copy_(self.h_in[n], non_blocking=True)
+        self.h_out.copy_(self._run(), non_blocking=True)
 
     def config(self):
         return {"workload": self.name, "context": self.POS0 + self.R, "part_rows": self.R, "qsa_heads": "16q/2kv x256", "block": 4,
                 "top_k_blocks": 512, "selections": "i.i.d. (random indexer)", "l2": "the K/V cache (0.5 GB) exceeds the 126 MB L2"}
 
 
-WORKLOADS = {"gdn_prefill_32k": GdnPrefill32k, "decode_262k": Decode262k, "qsa_prefill_262k": QsaPrefill262k}
+
+
+def drift_selections(torch, R, nb0, gen, drift=0.25):
+    """Selections that drift from row to row: a 512-block set of which every member is replaced with probability
+    `drift` per row by a block drawn uniformly from the nb0 complete blocks; ascending ids per row [R, 512] int32."""
+    cur = torch.randperm(nb0, device="cuda", generator=gen)[:512]
+    rows = []
+    for _ in range(R):
+        keep = torch.rand(512, device="cuda", generator=gen) >= drift
+        cur = torch.where(keep, cur, torch.randint(0, nb0, (512,), device="cuda", generator=gen))
+        u = torch.unique(cur)
+        while u.numel() < 512:                               # a replacement hit a member: draw again
+            u = torch.unique(torch.cat([u, torch.randint(0, nb0, (512 - u.numel(),), device="cuda", generator=gen)]))
+        cur = u[:512]
+        rows.append(cur)
+    return torch.stack(rows).int()
+
+
+class QsaAttendDrift(QsaPrefill262k):
+    """The attention stage of the same 2,048-row part (union lists + tiled attention + gate) with injected selections
+    that overlap from row to row the way real selections do: the drift model of the reference's attention probe
+    (512-block set, each member replaced with probability 0.25 per row; bench/qsa_attn.hip:46-90), generated here."""
+    name = "qsa_attend_262k_drift"
+    metric = "qsa_prefill_attention_stage_tokens_per_s_at_262k"
+
+    def __init__(self, rank, algo):
+        super().__init__(rank, algo)
+        torch, capi, layers = self.torch, self.capi, self.layers
+        gen = torch.Generator(device="cuda").manual_seed(3500 + rank)
+        R = self.R
+        self.ses.sel.copy_(drift_selections(torch, R, (self.POS0 + 1) // 4, gen))
+        self.ses.nsel.fill_(512)
+        self.plan.q_hi.copy_(self.inp["q"][:, :, :256].half())
+        self.args = capi.QsaPrefillArgs(layers.qsa_args(self.w, self.ses, self.inp["q"], self.inp["k"], self.inp["v"], self.inp["idx"], self.plan.out, self.POS0),
+                                        capi.dptr(self.plan.q_hi), capi.dptr(self.plan.scratch), self.plan.scratch.numel())
+        union = torch.unique(self.ses.sel[:16]).numel()
+        self.union_16 = int(union)
+        self.h_q = self.plan.q_hi.cpu().pin_memory()
+        self.h2d, self.d2h = self.h_q.numel() * 2, self.h_out.numel() * 2
+        # bytes: every block of a 16-row tile's union once per KV head pair (4 KB of K + V per block), rows in and out
+        self.alg_bytes = (R // 16) * union * 2 * 4096 + self.h2d + self.d2h
+        self.kernel_bytes = {"qsa_flash_tc_kernel": (R // 16) * union * 2 * 4096}
+        self.alg_flops = R * (4 * 16 * 256 * 2051)
+
+    def step(self):
+        g = self.capi.GEOM_BENCH
+        self.capi.check(self.capi.lib.cr_qsa_prefill_attend(C.byref(g), C.byref(self.args), 0, self.capi.OUT_RAW_BF16,
+                                                            C.c_void_p(self.torch.cuda.current_stream().cuda_stream)))
+        return self.plan.out
+
+    step_eager = step
+
+    def step_e2e(self):
+        self.plan.q_hi.copy_(self.h_q, non_blocking=True)
+        self.h_out.copy_(self.step(), non_blocking=True)
+
+    def config(self):
+        c = super().config()
+        c.update(workload=self.name, selections="drift 0.25 per row (injected); a 16-row tile attends %d distinct blocks" % self.union_16)
+        return c
+
+
+class Verify131k:
+    """configs[4]: 8 sessions at 131,072 context, each verifying 8 draft tokens: a span is 1 certain row + 8 drafts
+    (commit = 1, 9 rows, pending-row stride 16), the pass before it accepted a ~ U{0..8} drafts, which this pass replays
+    into the GDN state first.  QSA: one packed launch chain over the 8 spans (72 rows); GDN: one launch over 8 spans."""
+    name = "verify_131k"
+    CTX, SESSIONS, ROWS = 131072, 8, 9
+    unit, metric, dtype = "rows/s", "qsa_gdn_verify_rows_per_s_at_131k", "fp16 kv / fp32"
+
+    def __init__(self, rank, algo):
+        import torch
+        from crucible_strix_halo_b200 import capi, layers
+        self.torch, self.capi, self.layers = torch, capi, layers
+        g = capi.GEOM_BENCH
+        gen = torch.Generator(device="cuda").manual_seed(5000 + rank)
+        rn = lambda *s, std=1.0, mean=0.0: torch.randn(*s, device="cuda", generator=gen) * std + mean
+        S, R = self.SESSIONS, self.ROWS
+        self.qw = layers.QsaWeights(g, 1 + rn(256, std=0.1), 1 + rn(256, std=0.1), 1 + rn(128, std=0.1), 1 + rn(128, std=0.1))
+        self.gw = layers.GdnWeights(g, rn(g.gdn_channels, 4, std=0.5), rn(32, std=1.5, mean=-1).clamp(-5, 1.5), rn(32, std=0.5),
+                                    1 + rn(128, std=0.1), ab=rn(64, 2048, std=0.05))
+        self.pos = self.CTX - R
+        sizes = dict(q=16 * 512, idx=640, k=512, v=512, qkv=g.gdn_channels, z=4096, x=2048)
+        self.inp = {n: rn(S, R, w_) for n, w_ in sizes.items()}                 # projection rows of the pass, one tensor per input
+        self.work = {n: torch.empty_like(self.inp[n]) for n in ("q", "idx")}     # normalised in place: a fresh copy per step
+        self.qs, self.gs = [], []
+        for s in range(S):
+            q = layers.QsaSession(g, self.CTX, max_rows=R)
+            q.k.copy_(rn(self.CTX, 2, 256).half()); q.v.copy_(rn(self.CTX, 2, 256).half())
+            q.ik_pool.copy_(rn(q.ik_pool.numel())); q.ik_raw.copy_(rn(self.CTX, 128))
+            gs = layers.GdnSession(g, pend_rows=16)
+            gs.state[:32 * 16384].copy_(rn(32 * 16384, std=0.05))
+            gs.pend.copy_(rn(*gs.pend.shape, std=0.1))
+            gs.pend[:, :, 256] = 0.5 + 0.5 * torch.rand(32, 16, device="cuda", generator=gen)      # decay
+            gs.pend[:, :, 257] = torch.rand(32, 16, device="cuda", generator=gen)                  # beta
+            self.qs.append(q); self.gs.append(gs)
+        # accepted drafts of the previous pass per (step, session), uniform 0..8, seeded
+        self.replays = torch.randint(0, 9, (64, S), generator=torch.Generator().manual_seed(5100 + rank)).tolist()
+        self.t = 0
+        self.plan = layers.QsaStepPlan(self.qw, S * R)
+        self.out_all = torch.empty(S, 2, R, 4096, device="cuda")
+        self.h_in = {n: t.cpu().pin_memory() for n, t in self.inp.items()}
+        self.h_out = torch.empty(S, 2, R, 4096).pin_memory()
+        self.h2d, self.d2h = sum(t.numel() * 4 for t in self.h_in.values()), self.h_out.numel() * 4
+        self.units_per_step = S * R
+        # per session-pass: one pool scan for all rows, the K/V rows of the union of the 9 rows' positions (upper bound:
+        # 9 x 2051 rows; the rows of one span select nearly the same blocks, so about one row's worth is fetched from
+        # DRAM), the GDN state in and out, pending rows in and out
+        self.alg_bytes = S * (32768 * 512 + 2051 * 2048 + 2 * 2097152 + 2 * 32 * 8 * 258 * 4)
+        self.kernel_bytes = {"qsa_score_kernel": 32768 * 512 * S, "gdn_step_kernel": 2 * 2097152 * S}
+        self.side = torch.cuda.Stream()
+
+    def _step(self, in_place=False):
+        torch = self.torch
+        S = self.SESSIONS
+        replay = self.replays[self.t % len(self.replays)]
+        self.t += 1
+        if not in_place:
+            for n, t in self.work.items():
+                t.copy_(self.inp[n])
+        cur = torch.cuda.current_stream()
+        self.side.wait_stream(cur)
+        with torch.cuda.stream(self.side):
+            self.layers.gdn_step(self.gw, [dict(session=self.gs[s], qkv=self.inp["qkv"][s], z=self.inp["z"][s], x=self.inp["x"][s], pos0=self.pos,
+                                                 replay=replay[s], commit=1) for s in range(S)], outs=[self.out_all[s, 1] for s in range(S)])
+        src = self.inp if in_place else self.work
+        spans = [dict(session=self.qs[s], q=src["q"][s].view(self.ROWS, 16, 512), k=self.inp["k"][s], v=self.inp["v"][s], idx=src["idx"][s], pos0=self.pos)
+                 for s in range(S)]
+        self.plan.run(spans, outs=[self.out_all[s, 0] for s in range(S)])
+        cur.wait_stream(self.side)
+        return self.out_all
+
+    def step(self):
+        return self._step()
+
+    step_eager = step
+
+    def step_profile(self):
+        return self._step()
+
+    def step_e2e(self):
+        for n, t in self.inp.items():
+            t.copy_(self.h_in[n], non_blocking=True)
+        self._step(in_place=True)
+        self.h_out.copy_(self.out_all, non_blocking=True)
+
+    def config(self):
+        return {"workload": self.name, "sessions_per_gpu": self.SESSIONS, "context": self.CTX, "span_rows": self.ROWS, "commit": 1,
+                "replay": "uniform 0..8 per session and pass (seeded)", "pend_rows": 16, "qsa_heads": "16q/2kv x256",
+                "gdn_state": "32x128x128 fp32", "l2": "per-pass traffic (202 MB) exceeds the 126 MB L2"}
+
+
+class PrefillStack262k:
+    """configs[3]: cold prefill of 262,144 tokens through a 3:1 stack of GDN:QSA layers (4 layers), processed in
+    2,048-row parts against the growing cache: per part three cr_gdn_prefill calls (each layer its own state, ring and
+    weights) and one cr_qsa_prefill call.  A step is the whole sequence (128 parts).  The rows of every part are the same
+    seeded 2,048-row block per layer (the positions, the caches and the states differ from part to part)."""
+    name = "prefill_262k_stack"
+    T, PART = 262144, 2048
+    unit, metric, dtype = "tokens/s", "gdn3_qsa1_stack_prefill_tokens_per_s_at_262k", "bf16 in (GDN) / fp32 in (QSA) / fp16 kv / fp32 state"
+
+    def __init__(self, rank, algo, parts=None):
+        import torch
+        from crucible_strix_halo_b200 import capi, layers
+        self.torch, self.capi, self.layers = torch, capi, layers
+        g = capi.GEOM_BENCH
+        gen = torch.Generator(device="cuda").manual_seed(6000 + rank)
+        rn = lambda *s, std=1.0, mean=0.0: torch.randn(*s, device="cuda", generator=gen) * std + mean
+        R = self.PART
+        self.parts = parts if parts is not None else list(range(self.T // R))
+        self.algo = algo
+        self.gw = [layers.GdnWeights(g, rn(g.gdn_channels, 4, std=0.5), rn(32, std=1.5, mean=-1).clamp(-5, 1.5), rn(32, std=0.5),
+                                     1 + rn(128, std=0.1)) for _ in range(3)]
+        self.gses = [layers.GdnSession(g) for _ in range(3)]
+        self.gplan = [layers.GdnPrefillPlan(w, R, in_dtype=capi.IN_BF16, fmt=capi.OUT_RAW_BF16) for w in self.gw]
+        self.g_in = [(rn(R, g.gdn_channels).bfloat16(), rn(R, 4096).bfloat16(), rn(R, 64).bfloat16()) for _ in range(3)]
+        self.qw = layers.QsaWeights(g, 1 + rn(256, std=0.1), 1 + rn(256, std=0.1), 1 + rn(128, std=0.1), 1 + rn(128, std=0.1))
+        self.qses = layers.QsaSession(g, self.T, max_rows=R)
+        self.qplan = layers.QsaPrefillPlan(self.qw, R, fmt=capi.OUT_RAW_BF16)
+        self.q_in = {"q": rn(R, 16, 512), "k": rn(R, 512), "v": rn(R, 512), "idx": rn(R, 640)}
+        self.q_work = {n: torch.empty_like(self.q_in[n]) for n in ("q", "idx")}
+        self.units_per_step = len(self.parts) * R
+        per_tok_gdn = GDN_BYTES_PER_TOKEN
+        att = sum(min(p * R + r + 1, 2051) for p in self.parts for r in range(0, R, 64)) * 64       # attended positions, sampled rows
+        self.alg_bytes = 3 * per_tok_gdn * self.units_per_step + att * 2048 + sum(((p + 1) * R // 4) * 512 for p in self.parts if (p + 1) * R // 4 > 512)
+        self.alg_flops = 3 * 5.4e6 * self.units_per_step + att * 4 * 16 * 256 + sum(1024 * ((p * R + r + 1) // 4) for p in self.parts for r in range(0, R, 64)) * 64
+        self.kernel_bytes = {}
+        self.h_g = [tuple(t.cpu().pin_memory() for t in tpl) for tpl in self.g_in]
+        self.h_q = {n: t.cpu().pin_memory() for n, t in self.q_in.items()}
+        self.h_out = torch.empty(4, R, 4096, dtype=torch.bfloat16).pin_memory()
+        self.h2d = (sum(t.numel() * 2 for tpl in self.h_g for t in tpl) + sum(t.numel() * 4 for t in self.h_q.values())) * len(self.parts)
+        self.d2h = self.h_out.numel() * 2 * len(self.parts)
+
+    def _reset(self):
+        for s in self.gses:
+            s.state.zero_(); s.hist.zero_()
+
+    def _part(self, p, e2e=False):
+        R, capi = self.PART, self.capi
+        outs = []
+        for i in range(3):
+            qkv, z, ab = self.g_in[i]
+            if e2e:
+                for d, h in zip(self.g_in[i], self.h_g[i]):
+                    d.copy_(h, non_blocking=True)
+            outs.append(self.gplan[i].run(self.gses[i], qkv, z, ab, p * R, self.algo))
+        for n, t in self.q_in.items():
+            dst = self.q_work[n] if n in self.q_work else t
+            if e2e:
+                dst.copy_(self.h_q[n], non_blocking=True)
+            elif n in self.q_work:
+                dst.copy_(t)
+        outs.append(self.qplan.run(self.qses, self.q_work["q"], self.q_in["k"], self.q_in["v"], self.q_work["idx"], p * R))
+        if e2e:
+            for i, o in enumerate(outs):
+                self.h_out[i].copy_(o, non_blocking=True)
+
+    def step(self):
+        self._reset()
+        for p in self.parts:
+            self._part(p)
+
+    step_eager = step
+
+    def step_e2e(self):
+        self._reset()
+        for p in self.parts:
+            self._part(p, e2e=True)
+
+    def config(self):
+        return {"workload": self.name, "seq_len": self.T, "part_rows": self.PART, "parts_run": len(self.parts), "layers": "GDN, GDN, GDN, QSA",
+                "gdn_heads": "16qk/32v x128", "qsa_heads": "16q/2kv x256", "block": 4, "top_k_blocks": 512,
+                "selections": "i.i.d. (random indexer)", "l2": "the K/V cache (0.5 GB) and the GDN inputs exceed the 126 MB L2"}
+
+
+class SplitKvPrefill262k:
+    """The QSA part of qsa_prefill_262k with the KV sequence split over the ranks (strong scaling: ONE sequence): rank g
+    owns the cache positions of blocks [b0_g, b1_g) (its cache pointers are biased, so it stores only its share), scores
+    its own blocks, all-gathers 512 candidates per row, merges them into the global selection, attends its own
+    positions, all-gathers the (m, l, acc) partials and merges them (NCCL over NVLink)."""
+    name = "qsa_prefill_262k_split_kv"
+    POS0, R = 262144 - 2048, 2048
+    unit, metric, dtype = "tokens/s", "qsa_layer_prefill_tokens_per_s_at_262k_split_kv", "fp16 kv / fp32 q"
+
+    def __init__(self, rank, world):
+        import torch
+        import torch.distributed as dist
+        from crucible_strix_halo_b200 import capi, layers, parallel
+        self.torch, self.capi, self.layers, self.dist = torch, capi, layers, dist
+        g = capi.GEOM_BENCH
+        R, ctx = self.R, self.POS0 + self.R
+        self.rank, self.world = rank, world
+        (b0, b1), (p0, p1) = parallel.kv_block_range(ctx, world, rank)
+        self.b0, self.b1, self.p0, self.p1 = b0, b1, p0, min(p1, ctx)
+        own = self.p1 - self.p0
+        gen = torch.Generator(device="cuda").manual_seed(7000)          # the same sequence on every rank
+        rn = lambda *s, std=1.0: torch.randn(*s, device="cuda", generator=gen) * std
+        self.w = layers.QsaWeights(g, 1 + rn(256, std=0.1), 1 + rn(256, std=0.1), 1 + rn(128, std=0.1), 1 + rn(128, std=0.1))
+        self.inp = {"q": rn(R, 16, 512), "k": rn(R, 512), "v": rn(R, 512), "idx": rn(R, 640)}
+        lgen = torch.Generator(device="cuda").manual_seed(7100 + rank)   # the rank's own share of the cache
+        lrn = lambda *s: torch.randn(*s, device="cuda", generator=lgen)
+        # own share only: K, V [own][2][256]; pool tiles covering the own blocks; bases biased to absolute positions
+        self.k = lrn(own + 8, 2, 256).half(); self.v = lrn(own + 8, 2, 256).half()
+        t0 = b0 // 32
+        self.pool = lrn(((b1 + 31) // 32 - t0 + 1) * 4096)
+        self.raw = torch.zeros(16, 128, device="cuda")
+        self.scores = torch.empty(R, b1 - b0 + 64, device="cuda")        # the rank's own columns; biased base
+        self.sel = torch.zeros(R, 512, device="cuda", dtype=torch.int32)
+        self.nsel = torch.zeros(R, device="cuda", dtype=torch.int32)
+        self.out = torch.empty(R, 4096, device="cuda", dtype=torch.bfloat16)
+        self.work = {n: torch.empty_like(self.inp[n]) for n in ("q", "idx")}
+        cache = capi.QsaCache(self.k.data_ptr() - self.p0 * 1024, self.v.data_ptr() - self.p0 * 1024, self.raw.data_ptr(),
+                              self.pool.data_ptr() - t0 * 4096 * 4, 16)
+        score_stride = self.scores.shape[1]
+        self.args = capi.QsaArgs(capi.dptr(self.work["q"]), capi.dptr(self.inp["k"]), capi.dptr(self.inp["v"]), capi.dptr(self.work["idx"]),
+                                 capi.dptr(self.w.q_norm1), capi.dptr(self.w.k_norm1), capi.dptr(self.w.iq_norm1), capi.dptr(self.w.ik_norm1),
+                                 cache, self.scores.data_ptr() - b0 * 4, score_stride, capi.dptr(self.sel), capi.dptr(self.nsel), None,
+                                 capi.dptr(self.out), self.POS0, R, None, 0, 0, None, capi.dptr(self.w.rope))
+        self.cs = torch.empty(R, 512, device="cuda"); self.ci = torch.empty(R, 512, device="cuda", dtype=torch.int32)
+        self.all_cs = torch.empty(world, R, 512, device="cuda"); self.all_ci = torch.empty(world, R, 512, device="cuda", dtype=torch.int32)
+        self.part = torch.empty(R, 16, 258, device="cuda"); self.all_part = torch.empty(world, R, 16, 258, device="cuda")
+        self.scratch = torch.empty(R * 16 * 4 * 258 * 4, dtype=torch.uint8, device="cuda")
+        self.units_per_step = R
+        self.wire_bytes = (world - 1) * (self.cs.numel() * 4 + self.ci.numel() * 4 + self.part.numel() * 4)   # received per rank per part
+        self.ev = [torch.cuda.Event(enable_timing=True) for _ in range(6)]
+        self.coll_ms = [0.0, 0.0]
+        self.h_in = {n: t.cpu().pin_memory() for n, t in self.inp.items()}
+        self.h_out = torch.empty(R, 4096, dtype=torch.bfloat16).pin_memory()
+        self.h2d, self.d2h = sum(t.numel() * 4 for t in self.h_in.values()), self.h_out.numel() * 2
+
+    def _prep(self):
+        """q and the indexer queries normalised + roped in place (every rank does this cheap step for all rows)."""
+        capi, g = self.capi, self.capi.GEOM_BENCH
+        capi.check(capi.lib.cr_qsa_prep_queries(C.byref(g), (capi.QsaArgs * 1)(self.args), 1, C.c_void_p(self.torch.cuda.current_stream().cuda_stream)))
+
+    def _run(self, timed=False):
+        capi, dist, g = self.capi, self.dist, self.capi.GEOM_BENCH
+        st = C.c_void_p(self.torch.cuda.current_stream().cuda_stream)
+        arr = (capi.QsaArgs * 1)(self.args)
+        # the cache rows of the part belong to the last rank's positions and are part of the synthetic cache here
+        self._prep()
+        capi.check(capi.lib.cr_qsa_shard_select(C.byref(g), arr, self.b0, self.b1, self.cs.data_ptr(), self.ci.data_ptr(), st))
+        if timed: self.ev[0].record()
+        if self.world > 1:
+            dist.all_gather_into_tensor(self.all_cs, self.cs); dist.all_gather_into_tensor(self.all_ci, self.ci)
+        else:
+            self.all_cs.copy_(self.cs.unsqueeze(0)); self.all_ci.copy_(self.ci.unsqueeze(0))
+        if timed: self.ev[1].record()
+        capi.check(capi.lib.cr_qsa_merge_candidates(C.byref(g), arr, self.world, self.all_cs.data_ptr(), self.all_ci.data_ptr(), st))
+        capi.check(capi.lib.cr_qsa_shard_attn(C.byref(g), arr, self.p0, self.p1 if self.rank < self.world - 1 else 2 ** 31 - 1,
+                                              self.part.data_ptr(), self.scratch.data_ptr(), self.scratch.numel(), st))
+        if timed: self.ev[2].record()
+        if self.world > 1:
+            dist.all_gather_into_tensor(self.all_part, self.part)
+        else:
+            self.all_part.copy_(self.part.unsqueeze(0))
+        if timed: self.ev[3].record()
+        capi.check(capi.lib.cr_qsa_merge_partials(C.byref(g), arr, self.world, self.all_part.data_ptr(), capi.OUT_RAW_BF16, st))
+        return self.out
+
+    def _fresh(self):
+        for n, t in self.work.items():
+            t.copy_(self.inp[n])
+
+    def step(self):
+        self._fresh()
+        return self._run()
+
+    def step_timed(self):
+        self._fresh()
+        out = self._run(timed=True)
+        self.torch.cuda.synchronize()
+        self.coll_ms[0] += self.ev[0].elapsed_time(self.ev[1]); self.coll_ms[1] += self.ev[2].elapsed_time(self.ev[3])
+        return out
+
+    def step_e2e(self):
+        for n, t in self.inp.items():
+            (self.work[n] if n in self.work else t).copy_(self.h_in[n], non_blocking=True)
+        self.h_out.copy_(self._run(), non_blocking=True)
+
+    def config(self):
+        return {"workload": self.name, "context": self.POS0 + self.R, "part_rows": self.R, "ranks": self.world,
+                "split": "KV positions by whole blocks, the newest rows on the last rank", "collectives": "all-gather of candidates, all-gather of partials (NCCL)",
+                "wire_bytes_received_per_rank_per_part": self.wire_bytes}
+
+
+WORKLOADS = {"gdn_prefill_32k": GdnPrefill32k, "decode_262k": Decode262k, "qsa_prefill_262k": QsaPrefill262k,
+             "qsa_attend_262k_drift": QsaAttendDrift, "verify_131k": Verify131k, "prefill_262k_stack": PrefillStack262k}
+SUB_WORKLOADS = ["decode_262k", "qsa_prefill_262k", "qsa_attend_262k_drift", "verify_131k", "prefill_262k_stack"]
+SUB_STEPS = {"decode_262k": (20, 5), "qsa_prefill_262k": (5, 3), "qsa_attend_262k_drift": (5, 3), "verify_131k": (20, 5), "prefill_262k_stack": (2, 1)}
+BF16_PEAK_FALLBACK = 1590.0
 
 
 # ------------------------------------------------------------------------------------------------------------
 # CPU baseline (the oracle's C port on the host cores)
 # ------------------------------------------------------------------------------------------------------------
 
-def cpu_baseline(workload, seconds_hint=10.0):
+def cpu_baseline(workload, seconds=6.0):
+    """Times the C port of the oracle on every host core this process may use, for at least `seconds` seconds, on a
+    bounded sample of the workload."""
     from oracle import build as oracle_build
-    lib_path = oracle_build.build_oracle()
-    lib = C.CDLL(lib_path)
+    lib = C.CDLL(oracle_build.build_oracle())
     lib.oracle_threads.restype = C.c_int
-    lib.oracle_set_threads(C.c_int(len(os.sched_getaffinity(0))))   # every core this process may run on
+    lib.oracle_set_threads(C.c_int(len(os.sched_getaffinity(0))))
     cores = lib.oracle_threads()
     rng = np.random.default_rng(0)
     f32 = lambda a: np.ascontiguousarray(a, np.float32)
     ptr = lambda a: a.ctypes.data_as(C.c_void_p)
-    if workload == "gdn_prefill_32k":
-        Hv, Hk, n = 32, 16, 2048
-        Cw = 2 * Hk * 128 + Hv * 128
-        qkv, z, ab = f32(rng.normal(size=(n, Cw))), f32(rng.normal(size=(n, Hv * 128))), f32(rng.normal(size=(n, 2 * Hv)))
-        conv, A_log = f32(rng.normal(size=(Cw, 4)) * 0.5), f32(np.clip(rng.normal(-1, 1.5, Hv), -5, 1.5))
-        dtb, gamma = f32(rng.normal(size=Hv) * 0.5), f32(1 + 0.1 * rng.normal(size=128))
-        state, out = np.zeros((Hv, 128, 128), np.float32), np.zeros((n, Hv * 128), np.float32)
-        t0 = time.perf_counter()
-        reps = 0
-        while True:
-            lib.oracle_gdn_layer(ptr(qkv), ptr(z), ptr(ab), ptr(conv), ptr(A_log), ptr(dtb), ptr(gamma), None, ptr(state), ptr(out),
-                                 n, Hv, Hk)
-            reps += 1
-            if time.perf_counter() - t0 > seconds_hint or reps >= 64:
-                break
-        dt = time.perf_counter() - t0
-        return {"value": n * reps / dt, "unit": "tokens/s", "cores": cores, "kind": "port",
-                "sample": "%d x %d tokens of the 32768-token layer (serial fp32 recurrence, all 32 heads), %.1f s" % (reps, n, dt)}
-    # decode: one session at a reduced number of steps, full 262,144-token context
-    Hq, Hkv, ctx = 16, 2, 262144
-    kc = rng.normal(size=(ctx, Hkv, 256)).astype(np.float16)
-    vc = rng.normal(size=(ctx, Hkv, 256)).astype(np.float16)
-    pool = f32(rng.normal(size=(ctx // 128) * 4096))
-    qn, gate, iq = f32(rng.normal(size=(Hq, 256))), f32(rng.normal(size=(Hq, 256))), f32(rng.normal(size=(4, 128)))
-    out, sel, nsel = np.zeros((Hq, 256), np.float32), np.zeros(512, np.int32), np.zeros(1, np.int32)
-    Hv, Hk = 32, 16
+    Hv, Hk, Hq, Hkv = 32, 16, 16, 2
     Cw = 2 * Hk * 128 + Hv * 128
-    g_in = [f32(rng.normal(size=(1, Cw))), f32(rng.normal(size=(1, Hv * 128))), f32(rng.normal(size=(1, 2 * Hv)))]
     conv, A_log = f32(rng.normal(size=(Cw, 4)) * 0.5), f32(np.clip(rng.normal(-1, 1.5, Hv), -5, 1.5))
     dtb, gamma = f32(rng.normal(size=Hv) * 0.5), f32(1 + 0.1 * rng.normal(size=128))
-    state, gout = f32(rng.normal(size=(Hv, 128, 128)) * 0.05), np.zeros((1, Hv * 128), np.float32)
-    if workload == "qsa_prefill_262k":      # a prefill row costs what a decode row costs: score, select, attend
-        t0 = time.perf_counter()
-        reps = 0
+
+    def gdn_rows(n):
+        qkv, z, ab = f32(rng.normal(size=(n, Cw))), f32(rng.normal(size=(n, Hv * 128))), f32(rng.normal(size=(n, 2 * Hv)))
+        state, out = f32(rng.normal(size=(Hv, 128, 128)) * 0.05), np.zeros((n, Hv * 128), np.float32)
+        return lambda: lib.oracle_gdn_layer(ptr(qkv), ptr(z), ptr(ab), ptr(conv), ptr(A_log), ptr(dtb), ptr(gamma), None, ptr(state), ptr(out), n, Hv, Hk)
+
+    def qsa_row(ctx):
+        kc = rng.normal(size=(ctx, Hkv, 256)).astype(np.float16); vc = rng.normal(size=(ctx, Hkv, 256)).astype(np.float16)
+        pool = f32(rng.normal(size=((ctx + 127) // 128) * 4096))
+        qn, gate, iq = f32(rng.normal(size=(Hq, 256))), f32(rng.normal(size=(Hq, 256))), f32(rng.normal(size=(4, 128)))
+        out, sel, nsel = np.zeros((Hq, 256), np.float32), np.zeros(512, np.int32), np.zeros(1, np.int32)
+        return lambda p=ctx - 1: lib.oracle_qsa_decode_row(ptr(qn), ptr(gate), ptr(iq), int(p), ptr(kc), ptr(vc), ptr(pool), ptr(out), ptr(sel), ptr(nsel), Hq, Hkv)
+
+    def run(fn, units, what):
+        fn()                                              # warm the caches and the thread pool
+        t0, reps = time.perf_counter(), 0
         while True:
-            lib.oracle_qsa_decode_row(ptr(qn), ptr(gate), ptr(iq), ctx - 1 - reps % 2048, ptr(kc), ptr(vc), ptr(pool), ptr(out), ptr(sel),
-                                      ptr(nsel), Hq, Hkv)
+            fn()
             reps += 1
-            if time.perf_counter() - t0 > seconds_hint or reps >= 2048:
+            dt = time.perf_counter() - t0
+            if dt >= seconds:
                 break
-        dt = time.perf_counter() - t0
-        return {"value": reps / dt, "unit": "tokens/s", "cores": cores, "kind": "port",
-                "sample": "%d rows of the 2,048-row part at 262,144 context (score, top-512, attention), %.1f s" % (reps, dt)}
-    t0 = time.perf_counter()
-    reps = 0
-    while True:
-        lib.oracle_qsa_decode_row(ptr(qn), ptr(gate), ptr(iq), ctx - 1, ptr(kc), ptr(vc), ptr(pool), ptr(out), ptr(sel), ptr(nsel), Hq, Hkv)
-        lib.oracle_gdn_layer(ptr(g_in[0]), ptr(g_in[1]), ptr(g_in[2]), ptr(conv), ptr(A_log), ptr(dtb), ptr(gamma), None, ptr(state),
-                             ptr(gout), 1, Hv, Hk)
-        reps += 1
-        if time.perf_counter() - t0 > seconds_hint or reps >= 2000:
-            break
-    dt = time.perf_counter() - t0
-    return {"value": reps / dt, "unit": "tokens/s", "cores": cores, "kind": "port",
-            "sample": "%d session-steps of one session at 262,144 context (QSA row + GDN update), %.1f s" % (reps, dt)}
+        return {"value": units * reps / dt, "unit": WORKLOADS[workload].unit if workload in WORKLOADS else "tokens/s", "cores": cores, "kind": "port",
+                "sample": "%d x %s, %.1f s" % (reps, what, dt)}
+
+    if workload == "gdn_prefill_32k":
+        return run(gdn_rows(2048), 2048, "2048 tokens of the 32768-token layer (serial fp32 recurrence, all 32 heads)")
+    if workload in ("qsa_prefill_262k", "qsa_attend_262k_drift", "qsa_prefill_262k_split_kv"):
+        row = qsa_row(262144)
+        what = "8 rows of the 2,048-row part at 262,144 context (score, top-512, attention)"
+        return run(lambda: [row(262143 - i) for i in range(8)], 8, what)
+    if workload == "decode_262k":
+        row, upd = qsa_row(262144), gdn_rows(1)
+        return run(lambda: (row(), upd()), 1, "1 session-step at 262,144 context (QSA row + GDN update)")
+    if workload == "verify_131k":
+        row, upd = qsa_row(131072), gdn_rows(9)
+        return run(lambda: ([row(131071 - i) for i in range(9)], upd()), 9, "one 9-row span at 131,072 context (9 QSA rows + 9 GDN rows)")
+    if workload == "prefill_262k_stack":
+        # per token of the stack: 3 GDN tokens + 1 QSA row at a context drawn evenly from the sequence
+        row, upd = qsa_row(262144), gdn_rows(64)
+        ctxs = [int(c) for c in np.linspace(2048, 262143, 8)]
+        def fn():
+            for _ in range(3):
+                upd()
+            for c in ctxs * 8:
+                row(c)
+        return run(fn, 64, "64 tokens of the stack (3 x 64 GDN tokens + 64 QSA rows at contexts spread over the sequence)")
+    raise ValueError(workload)
 
 
 def run_reference(args, workload):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    vals = []
-    cb = None
+    vals, cb = [], None
     for _ in range(max(1, min(args.steps, 3))):
-        cb = cpu_baseline(workload, seconds_hint=8.0)
+        cb = cpu_baseline(workload, seconds=6.0)
         vals.append(cb["value"])
     v = float(np.mean(vals))
     cb["value"] = v
@@ -467,19 +823,146 @@ def run_reference(args, workload):
     print(json.dumps(line))
 
 
+def load_tensor_peak():
+    try:
+        p = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        return float(p["bf16_tflops"]), "measured"
+    except Exception:
+        return BF16_PEAK_FALLBACK, "fallback"
+
+
+def measure(wl, steps, warmup, world, dist, sampler=None):
+    """Runs one workload: device-timed steps, the host-buffer leg, per-kernel times.  Returns the figures of the line."""
+    import torch
+    from crucible_strix_halo_b200 import capi
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def timed(fn, n):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device="cuda")
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    for _ in range(max(warmup, 3) if steps > 2 else max(warmup, 1)):
+        wl.step()
+    if sampler:
+        sampler.start()
+    ms = timed(wl.step, steps)
+    clocks = sampler.stop() if sampler else None
+    for _ in range(2 if steps > 2 else 1):
+        wl.step_e2e()
+    ms_e2e = timed(wl.step_e2e, steps)
+    capi.lib.cr_profile_enable(1)
+    barrier()
+    psteps = min(steps, 5)
+    for _ in range(psteps):
+        capi.lib.cr_profile_begin(C.c_void_p(torch.cuda.current_stream().cuda_stream))
+        (wl.step_profile if hasattr(wl, "step_profile") else wl.step_eager)()
+    prof = capi.profile_collect()
+    capi.lib.cr_profile_enable(0)
+    status = capi.lib.cr_device_status()
+    peak, peak_kind = load_peaks()
+    tpeak, tpeak_kind = load_tensor_peak()
+    dominant = max(prof, key=lambda k: prof[k][0]) if prof else None
+    dom_ms, dom_calls = prof.get(dominant, (0.0, 0))
+    per_launch_ms = dom_ms / dom_calls if dom_calls else None
+    launches_per_step = dom_calls / psteps if dom_calls else 1
+    dominant_bytes = wl.kernel_bytes.get(dominant, wl.alg_bytes)
+    achieved = (dominant_bytes / launches_per_step) / (per_launch_ms * 1e-3) / 1e9 if per_launch_ms else None
+    traffic = None
+    if dominant in NCU_TRAFFIC.get(wl.name, {}):
+        per, val = NCU_TRAFFIC[wl.name][dominant]
+        traffic = val * (wl.units_per_step if per == "token" else 1.0) / launches_per_step
+    step_ms = ms / steps
+    step_frac = (wl.alg_bytes / peak / 1e9) / (step_ms * 1e-3)
+    roof = {"bound": "hbm", "achieved": wl.alg_bytes / (step_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s", "frac": step_frac,
+            "frac_is": "step: algorithmic bytes of the step / ms_per_step / peak",
+            "peak_source": (peak_kind + " (of measured copy bandwidth)") if peak_kind == "measured" else "fallback",
+            "traffic": traffic, "step_algorithmic_bytes": wl.alg_bytes,
+            "dominant_kernel": {"name": dominant, "ms_per_launch": per_launch_ms, "algorithmic_bytes_per_launch": dominant_bytes / launches_per_step,
+                                "achieved_gbs": achieved, "frac": (achieved / peak) if achieved else None},
+            "kernels": {k: {"ms_per_step": v[0] / psteps, "launches_per_step": v[1] / psteps} for k, v in prof.items()}}
+    if getattr(wl, "alg_flops", None):
+        tf = wl.alg_flops / (step_ms * 1e-3) / 1e12
+        roof["tensor"] = {"useful_tflops": tf, "peak": tpeak, "frac": tf / tpeak, "peak_source": tpeak_kind + " (cuBLAS bf16, burst)",
+                          "step_useful_flops": wl.alg_flops}
+    total_units = wl.units_per_step * world * steps
+    return {"metric": wl.metric, "value": total_units / (ms * 1e-3), "unit": wl.unit, "steps": steps, "ms_per_step": step_ms,
+            "dtype": wl.dtype, "config": wl.config(),
+            "e2e": {"value": total_units / (ms_e2e * 1e-3), "unit": wl.unit, "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h,
+                    "ms_per_step": ms_e2e / steps},
+            "gpu_launches": int(sum(v[1] for v in prof.values()) * steps / psteps), "roofline": roof, "device_status": status}, clocks
+
+
+def measure_split_kv(rank, world, dist, steps=5, warmup=3):
+    import torch
+    wl = SplitKvPrefill262k(rank, world)
+    for _ in range(warmup):
+        wl.step()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    res = {}
+    for name, fn in (("device", wl.step), ("e2e", wl.step_e2e)):
+        fn()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device="cuda")
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        res[name] = float(ms.item()) / steps
+    for _ in range(steps):
+        wl.step_timed()
+    coll = torch.tensor(wl.coll_ms, device="cuda") / steps
+    if world > 1:
+        dist.all_reduce(coll, op=dist.ReduceOp.MAX)
+    out = {"metric": wl.metric, "value": wl.R / (res["device"] * 1e-3), "unit": wl.unit, "ms_per_step": res["device"], "scaling": "strong",
+           "steps": steps, "config": wl.config(),
+           "e2e": {"value": wl.R / (res["e2e"] * 1e-3), "unit": wl.unit, "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h, "ms_per_step": res["e2e"]},
+           "collectives_ms_per_step": {"all_gather_candidates": float(coll[0]), "all_gather_partials": float(coll[1])},
+           "wire_bytes_received_per_rank_per_step": wl.wire_bytes}
+    del wl
+    torch.cuda.empty_cache()
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--workload", default="gdn_prefill_32k", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--algo", default="auto", choices=["auto", "serial", "chunk"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-sub-workloads", action="store_true", help="headline only (no `workloads` object)")
     ap.add_argument("--seq", type=int, default=0, help="gdn_prefill_32k only: a shorter sequence, for profiler captures")
+    ap.add_argument("--parts", type=int, default=0, help="prefill_262k_stack only: run every n-th part, for profiler captures")
     args = ap.parse_args()
+    headline = args.workload or "gdn_prefill_32k"
     if args.impl == "reference":
-        return run_reference(args, args.workload)
+        return run_reference(args, headline)
 
     import torch
     import torch.distributed as dist
@@ -496,84 +979,51 @@ def main():
     algo = {"serial": capi.GDN_SERIAL_F32, "chunk": capi.GDN_CHUNK_TC}.get(args.algo)
     if algo is None:
         algo = capi.GDN_CHUNK_TC if capi.lib.cr_gdn_algo_available(capi.GDN_CHUNK_TC) else capi.GDN_SERIAL_F32
-    if args.seq and args.workload == "gdn_prefill_32k":
+    if args.seq and headline == "gdn_prefill_32k":
         GdnPrefill32k.T = args.seq
-    wl = WORKLOADS[args.workload](rank, algo)
 
-    def barrier():
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-            torch.cuda.synchronize()
+    def make(name):
+        if name == "prefill_262k_stack" and args.parts:
+            return PrefillStack262k(rank, algo, parts=list(range(args.parts - 1, 128, args.parts)))
+        return WORKLOADS[name](rank, algo)
 
-    def timed(fn, steps):
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(steps):
-            fn()
-        e1.record()
-        barrier()
-        ms = torch.tensor([e0.elapsed_time(e1)], device="cuda")
-        if world > 1:
-            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        return float(ms.item())
-
-    for _ in range(max(args.warmup, 3)):
-        wl.step()
-    sampler = ClockSampler(local)
+    wl = make(headline)
+    sampler = ClockSampler(local) if rank == 0 else None
+    res, clocks = measure(wl, args.steps, args.warmup, world, dist, sampler)
+    del wl
+    torch.cuda.empty_cache()
+    line = {"metric": res["metric"], "value": res["value"], "unit": res["unit"], "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": res["ms_per_step"], "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": res["dtype"], "data": "synthetic", "config": res["config"], "e2e": res["e2e"],
+            "gpu_launches": res["gpu_launches"], "clocks": clocks, "roofline": res["roofline"], "device_status": res["device_status"]}
+    if not args.no_cpu_baseline and rank == 0 and world == 1:
+        line["cpu_baseline"] = cpu_baseline(headline)
+    if args.workload is None and not args.no_sub_workloads:
+        subs = {}
+        if world == 1:
+            subs[headline] = {k: line[k] for k in ("metric", "value", "unit", "ms_per_step", "e2e", "roofline") if k in line}
+            if "cpu_baseline" in line:
+                subs[headline]["cpu_baseline"] = line["cpu_baseline"]
+            for name in SUB_WORKLOADS:
+                steps, warm = SUB_STEPS[name]
+                try:
+                    w2 = make(name)
+                    r2, _ = measure(w2, steps, warm, world, dist)
+                    del w2
+                    torch.cuda.empty_cache()
+                    if not args.no_cpu_baseline:
+                        r2["cpu_baseline"] = cpu_baseline(name)
+                    subs[name] = r2
+                except Exception as e:                      # a failing sub-workload must not cost the headline line
+                    subs[name] = {"error": "%s: %s" % (type(e).__name__, e)}
+        else:
+            try:
+                subs["qsa_prefill_262k_split_kv"] = measure_split_kv(rank, world, dist)
+            except Exception as e:
+                subs["qsa_prefill_262k_split_kv"] = {"error": "%s: %s" % (type(e).__name__, e)}
+        line["workloads"] = subs
     if rank == 0:
-        sampler.start()
-    ms = timed(wl.step, args.steps)
-    clocks = sampler.stop() if rank == 0 else None
-    # end to end: pinned host inputs -> device, step, result -> host, inside the timed region
-    for _ in range(2):
-        wl.step_e2e()
-    ms_e2e = timed(wl.step_e2e, args.steps)
-    # dominant kernel, timed live with events on the launching stream
-    capi.lib.cr_profile_enable(1)
-    barrier()
-    for _ in range(args.steps):
-        capi.lib.cr_profile_begin(C.c_void_p(torch.cuda.current_stream().cuda_stream))
-        (wl.step_profile if hasattr(wl, "step_profile") else wl.step_eager)()
-    prof = capi.profile_collect()
-    capi.lib.cr_profile_enable(0)
-    if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
-        return
-    peak, peak_kind = load_peaks()
-    # the dominant kernel is the one with the largest share of the measured kernel time
-    dominant = max(prof, key=lambda k: prof[k][0]) if prof else None
-    dom_ms, dom_calls = prof.get(dominant, (0.0, 0))
-    per_launch_ms = dom_ms / dom_calls if dom_calls else None
-    launches_per_step = dom_calls / args.steps if dom_calls else 1
-    dominant_bytes = wl.kernel_bytes.get(dominant, wl.alg_bytes)
-    achieved = (dominant_bytes / launches_per_step) / (per_launch_ms * 1e-3) / 1e9 if per_launch_ms else None
-    traffic = None
-    if dominant in NCU_TRAFFIC.get(args.workload, {}):
-        per, val = NCU_TRAFFIC[args.workload][dominant]
-        traffic = val * (wl.units_per_step if per == "token" else 1.0) / launches_per_step
-    launches = sum(v[1] for v in prof.values())   # library kernels per timed region (graph replays launch the same kernels)
-    total_units = wl.units_per_step * world * args.steps
-    line = {
-        "metric": wl.metric, "value": total_units / (ms * 1e-3), "unit": wl.unit, "n_gpus": world, "steps": args.steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic", "config": wl.config(),
-        "e2e": {"value": total_units / (ms_e2e * 1e-3), "unit": wl.unit, "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h,
-                "ms_per_step": ms_e2e / args.steps},
-        "gpu_launches": int(launches),
-        "clocks": clocks,
-        "roofline": {"bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": peak, "unit": "GB/s",
-                     "frac": (achieved / peak) if achieved else None, "peak_source": peak_kind + " (of measured copy bandwidth)"
-                     if peak_kind == "measured" else "fallback", "traffic": traffic,
-                     "algorithmic_bytes_per_launch": dominant_bytes / launches_per_step, "step_algorithmic_bytes": wl.alg_bytes,
-                     "step_frac_of_hbm_roofline": (wl.alg_bytes / peak / 1e9) / (ms / args.steps * 1e-3), "kernel_ms_per_launch": per_launch_ms,
-                     "kernels": {k: {"ms_per_step": v[0] / args.steps, "launches_per_step": v[1] / args.steps} for k, v in prof.items()}},
-    }
-    if not args.no_cpu_baseline:
-        line["cpu_baseline"] = cpu_baseline(args.workload)
-    print(json.dumps(line))
+        print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
 

@@ -89,6 +89,8 @@ _protos = {
     "cr_qsa_pool_floats": (C.c_size_t, [C.c_int]),
     "cr_qsa_cache_bytes": (C.c_int, [G, C.c_int, C.c_int, C.POINTER(C.c_size_t)]),
     "cr_rope_table_fill": (C.c_int, [P, P]),
+    "cr_rope_table_fill_yarn": (C.c_int, [P, C.c_int, P]),
+    "cr_qsa_prep_queries": (C.c_int, [G, C.POINTER(QsaArgs), C.c_int, P]),
     "cr_qsa_prep": (C.c_int, [G, C.POINTER(QsaArgs), C.c_int, P]),
     "cr_qsa_select": (C.c_int, [G, C.POINTER(QsaArgs), C.c_int, P, C.c_size_t, P]),
     "cr_qsa_attn": (C.c_int, [G, C.POINTER(QsaArgs), C.c_int, P, C.c_size_t, C.c_int, P]),

@@ -66,7 +66,7 @@ __global__ void __launch_bounds__(128) qsa_attn_split_kernel(const __grid_consta
   pdl_wait();
   const cr_qsa_args& a = P.span[blockIdx.z];
   const int r = blockIdx.y / P.Hkv, g = blockIdx.y % P.Hkv;
-  if (r >= a.R) return;
+  if (r >= a.R || qsa_row_is_tiled(P, r)) return;
   const int gqa = P.Hq / P.Hkv;
   const int t = threadIdx.x, w = t >> 5, l = t & 31;
   const int split = blockIdx.x;
@@ -220,7 +220,7 @@ __global__ void __launch_bounds__(256) qsa_merge_kernel(const __grid_constant__ 
   pdl_wait();
   const cr_qsa_args& a = P.span[blockIdx.z];
   const int h = blockIdx.x, r = blockIdx.y, d = threadIdx.x;
-  if (r >= a.R) return;
+  if (r >= a.R || qsa_row_is_tiled(P, r)) return;
   const int row = P.base[blockIdx.z] + r;
   __shared__ float ob[256];
   auto rec = [&](int p) -> const float* {
@@ -285,7 +285,7 @@ __global__ void __launch_bounds__(256) qsa_merge_kernel(const __grid_constant__ 
 }
 
 cr_status qsa_attn_launch(const cr_geometry* g, const cr_qsa_args* spans, int n_spans, float* partials, int splits,
-                          int p0, int p1, cudaStream_t stream) {
+                          int p0, int p1, cudaStream_t stream, const QsaTileSplit* tiles) {
   use_stream(stream);
   CR_REQUIRE(splits >= 4 && splits <= 32, "qsa attention: %d KV splits unsupported (4..32)", splits);
   int row_base = 0;
@@ -294,6 +294,7 @@ cr_status qsa_attn_launch(const cr_geometry* g, const cr_qsa_args* spans, int n_
     QsaParams P;
     qsa_fill_params(P, g, spans + s0, n);
     for (int s = 0; s < n; ++s) P.base[s] += row_base;
+    if (tiles) { P.tile_count = tiles->count; P.tile_rows = tiles->rows; P.tile_max = tiles->max; }
     const int Rmax = qsa_max_rows(spans + s0, n);
     static PerDeviceOnce configured;
     if (cr_status st = once_per_device(configured, [] {
@@ -313,7 +314,7 @@ cr_status qsa_attn_launch(const cr_geometry* g, const cr_qsa_args* spans, int n_
 }
 
 cr_status qsa_merge_launch(const cr_geometry* g, const cr_qsa_args* spans, int n_spans, const float* partials, int nparts,
-                           bool part_major, float* partial_out, cr_out_format fmt, cudaStream_t stream) {
+                           bool part_major, float* partial_out, cr_out_format fmt, cudaStream_t stream, const QsaTileSplit* tiles) {
   use_stream(stream);
   CR_REQUIRE(nparts >= 1 && nparts <= 32, "qsa merge: %d partial records per (row, head) unsupported (1..32)", nparts);
   int rows_total = 0, row_base = 0;
@@ -323,6 +324,7 @@ cr_status qsa_merge_launch(const cr_geometry* g, const cr_qsa_args* spans, int n
     QsaParams P;
     qsa_fill_params(P, g, spans + s0, n);
     for (int s = 0; s < n; ++s) P.base[s] += row_base;
+    if (tiles) { P.tile_count = tiles->count; P.tile_rows = tiles->rows; P.tile_max = tiles->max; }
     const int Rmax = qsa_max_rows(spans + s0, n);
     CR_CUDA(launch_pdl(qsa_merge_kernel, dim3(g->q_heads, Rmax, n), dim3(256), 0, stream, P, partials, nparts, part_major ? 1 : 0, rows_total, partial_out, (int)fmt));
     CR_LAUNCH_CHECK("qsa_merge_kernel");

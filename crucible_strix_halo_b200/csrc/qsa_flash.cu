@@ -6,20 +6,21 @@
 // rows x heads are the 128 M rows of the tensor-core products.  A per-block row mask keeps every row's own selection
 // exact, and the causal rule (key position <= row position) cuts the tail block.
 //
-// qsa_union_build_kernel (one CTA per tile): every row contributes a sorted list (its selected blocks, or all
-// complete blocks when dense, plus its open tail block).  The union is formed by ranking: an element finds, by binary
-// search in the other rows' lists, which rows hold the same block (its mask), whether a lower row already owns it,
-// and how many owned blocks of every row precede it (its place in the output).  No array over the context is
-// needed, so the context length does not limit it (the reference keeps a byte per block in 64 KB of LDS and falls
-// back to row-wise attention past about 196K positions, engine/layers/qsa_union_lds.h:7-11).
+// qsa_union_build_kernel (one CTA per tile): every row contributes its selected blocks (or all complete blocks when
+// dense) plus its open tail block as keys (block, row); sorting the keys puts the rows of a block side by side, and
+// the first key of every run emits (block, OR of the row bits).  No array over the context is needed, so the context
+// length does not limit it (the reference keeps a byte per block in 64 KB of LDS and falls back to row-wise
+// attention past about 196K positions, engine/layers/qsa_union_lds.h:7-11).
 //
-// qsa_flash_tc_kernel (one CTA per (tile, KV head), 9 warps, 64 keys per step):
-//   loader warps (4)   gather the K and V rows of 16 blocks per step with 16-byte cp.async into two stages.  Both
-//                      tiles land as 16-byte units at (piece * 64 + key) * 16: for K that is the K-major operand
-//                      [key][channel], for V the MN-major operand [key][channel] (channels contiguous), so neither
-//                      is transposed anywhere.  Two warps serve the even steps and two the odd steps.
-//   issuer warp        S = Q K^T (16 tcgen05.mma kind::f16, M 128 x N 64 x K 16) into one of two TMEM accumulators,
-//                      one step ahead of the softmax; O += P V (4 MMAs, N 256) once the probabilities are written.
+// qsa_flash_tc_kernel (one CTA per (tile, KV head), 11 warps, 64 keys per step):
+//   loader warps (6)   gather the K and V rows of 16 blocks per step with 16-byte cp.async into three stages, two
+//                      warps per stage.  Both tiles land as 16-byte units at (piece * 64 + key) * 16: for K that is
+//                      the K-major operand [key][channel], for V the MN-major operand [key][channel] (channels
+//                      contiguous), so neither is transposed anywhere.
+//   issuer warp        S = Q K^T (16 tcgen05.mma kind::f16, M 128 x N 64 x K 16, the query tile being the A operand
+//                      in tensor memory, which leaves the shared memory to the K/V stages) into one of two TMEM
+//                      accumulators, one step ahead of the softmax; O += P V (4 MMAs, N 256) once the probabilities
+//                      are written.  An event loop issues whichever is ready.
 //   softmax warps (4)  thread = TMEM lane = (row, head): reads S, applies mask and causality, keeps a running
 //                      reference maximum that moves only when a logit exceeds it by more than 2^8 (the accumulator is
 //                      rescaled in TMEM then, which is rare after the first steps), writes P as fp16 into a K-major
@@ -37,13 +38,14 @@ CR_DEFINE_STATUS_WORD(qsa_flash)
 
 constexpr int kFlKeys = 64;                         // keys per step
 constexpr int kFlBlocks = kFlKeys / 4;              // union entries per step
-constexpr int kFlThreads = 32 * 9;
-constexpr int kFlQBytes = 128 * 256 * 2;            // [32 channel pieces][128 rows][8 halves]
+constexpr int kFlStages = 3;                        // K/V stages in flight
+constexpr int kFlThreads = 32 * (4 + 2 * kFlStages + 1);   // 4 softmax warps, 2 loader warps per stage, 1 issuer warp
+constexpr int kFlIssuer = 4 + 2 * kFlStages;
 constexpr int kFlKBytes = kFlKeys * 256 * 2;        // [32 channel pieces][64 keys][8 halves]
 constexpr int kFlPBytes = 128 * kFlKeys * 2;        // [8 key pieces][128 rows][8 halves]
-constexpr size_t kFlashSmem = kFlQBytes + 4 * kFlKBytes + 2 * kFlPBytes + 128;
-constexpr uint32_t kColO = 0, kColS = 256;          // TMEM columns: O 0-255, S of step j at 256 + 64 (j & 1)
-constexpr int kUbLen = 520;                         // list slots per row in the union builder (512 + tail + sentinel)
+constexpr size_t kFlashSmem = 2 * kFlStages * kFlKBytes + 2 * kFlPBytes + 128;
+// TMEM columns: O 0-255, S of step j at 256 + 64 (j & 1), the query tile (two fp16 channels per column) at 384-511
+constexpr uint32_t kColO = 0, kColS = 256, kColQ = 384;
 constexpr int kUbThreads = 1024;
 
 struct FlashParams {
@@ -53,6 +55,7 @@ struct FlashParams {
   const int* count;       // [tiles]
   float* gated;           // gated fp32 [R][Hq * 256] when the output transform runs as a second kernel, else null
   int cap, RT, Hq, Hkv, fmt;
+  int flash_max;          // tiles whose union list is longer are left to the row-wise kernels
 };
 
 int qsa_union_rows(const cr_geometry* g) {
@@ -63,78 +66,77 @@ int qsa_union_rows(const cr_geometry* g) {
 int qsa_union_cap(int RT) { return (RT * 513 + 15) / 16 * 16; }
 
 // ---- union lists -------------------------------------------------------------------------------------------
-__device__ __forceinline__ int lower_bound_i(const int* a, int n, int v) {
-  int lo = 0, hi = n;
-  while (lo < hi) {
-    const int mid = (lo + hi) >> 1;
-    if (a[mid] < v) lo = mid + 1; else hi = mid;
-  }
-  return lo;
-}
-
-__global__ void __launch_bounds__(kUbThreads) qsa_union_build_kernel(cr_qsa_args a, int2* list, int* count, int cap, int RT) {
-  extern __shared__ __align__(16) int ub[];
-  int* L = ub;                          // [RT][kUbLen] sorted block ids of every row
-  int* M = L + 16 * kUbLen;             // [RT][kUbLen] row mask of the elements that own their block, else 0
-  int* Pre = M + 16 * kUbLen;           // [RT][kUbLen] owned elements before index i (entry len = the row's total)
-  __shared__ int len[16];
+// One CTA per tile.  Every (block, row) pair of the tile becomes a 32-bit key block * 16 + row; the keys are sorted
+// in shared memory (bitonic network), which puts the rows of one block side by side.  The first key of every block
+// gathers the row bits of its run (at most 16 keys) and takes its place in the output from a prefix sum over the
+// run heads.
+__global__ void __launch_bounds__(kUbThreads) qsa_union_build_kernel(cr_qsa_args a, int2* list, int* count, int cap, int RT, int n_pad) {
+  extern __shared__ __align__(16) unsigned ukeys[];      // n_pad keys (a power of two >= RT * 513)
+  __shared__ unsigned red[33];
   const int t = threadIdx.x, w = t >> 5, l = t & 31;
   const int tile = blockIdx.x, row0 = tile * RT;
-  if (w < 16) {
-    int n = 0;
-    const int gr = row0 + w;
-    if (w < RT && gr < a.R) {
-      const int p = a.pos0 + gr, nb = (p + 1) / 4, ns = a.nsel[gr];
-      n = ns < 0 ? nb : CR_SEL_BLOCKS;
-      const int* sel = a.sel + (size_t)gr * CR_SEL_BLOCKS;
-      for (int i = l; i < n; i += 32) L[w * kUbLen + i] = ns < 0 ? i : sel[i];
-      if ((p + 1) % 4 != 0) { if (l == 0) L[w * kUbLen + n] = nb; ++n; }      // the open block holds the tail tokens
-    }
-    if (l == 0) len[w] = n;
-  }
+  constexpr unsigned kNone = 0xFFFFFFFFu;                // padding: sorts last
+  for (int i = t; i < n_pad; i += kUbThreads) ukeys[i] = kNone;
   __syncthreads();
-  for (int e = t; e < RT * kUbLen; e += kUbThreads) {
-    const int r = e / kUbLen, i = e % kUbLen;
-    int mask = 0;
-    if (i < len[r]) {
-      const int b = L[e];
-      bool own = true;
-      mask = 1 << r;
-      for (int r2 = 0; r2 < RT; ++r2) {
-        if (r2 == r || len[r2] == 0) continue;
-        const int at = lower_bound_i(L + r2 * kUbLen, len[r2], b);
-        if (at < len[r2] && L[r2 * kUbLen + at] == b) { mask |= 1 << r2; if (r2 < r) own = false; }
+  if (w < RT && row0 + w < a.R) {                         // one warp per row: slots [513 w, 513 w + 513)
+    const int gr = row0 + w, p = a.pos0 + gr, nb = (p + 1) / 4, ns = a.nsel[gr];
+    const int n = ns < 0 ? nb : CR_SEL_BLOCKS;           // dense rows attend every complete block (at most 512 of them)
+    const int* sel = a.sel + (size_t)gr * CR_SEL_BLOCKS;
+    unsigned* mine = ukeys + w * 513;
+    for (int i = l; i < n; i += 32) mine[i] = ((unsigned)(ns < 0 ? i : sel[i]) << 4) | (unsigned)w;
+    if ((p + 1) % 4 != 0 && l == 0) mine[n] = ((unsigned)nb << 4) | (unsigned)w;   // the open block holds the tail tokens
+  }
+  // ascending bitonic sort
+  for (int k = 2; k <= n_pad; k <<= 1) {
+    for (int j = k >> 1; j > 0; j >>= 1) {
+      __syncthreads();
+      for (int q = t; q < (n_pad >> 1); q += kUbThreads) {
+        const int i = ((q & ~(j - 1)) << 1) | (q & (j - 1));
+        const unsigned x = ukeys[i], y = ukeys[i + j];
+        const bool up = (i & k) == 0;
+        if ((x > y) == up) { ukeys[i] = y; ukeys[i + j] = x; }
       }
-      if (!own) mask = 0;
-    }
-    M[e] = mask;
-  }
-  __syncthreads();
-  if (w < RT) {                          // one warp per row: running count of owned elements
-    int run = 0;
-    for (int i0 = 0; i0 <= len[w]; i0 += 32) {
-      const int i = i0 + l;
-      const unsigned own = __ballot_sync(0xffffffffu, i < len[w] && M[w * kUbLen + i] != 0);
-      if (i <= len[w]) Pre[w * kUbLen + i] = run + __popc(own & ((1u << l) - 1u));
-      run += __popc(own);
     }
   }
   __syncthreads();
+  // run heads: thread t owns the keys [t * per, (t + 1) * per)
+  const int per = n_pad / kUbThreads;
+  int heads = 0;
+  for (int i = t * per; i < (t + 1) * per; ++i) {
+    const unsigned k = ukeys[i];
+    heads += k != kNone && (i == 0 || (ukeys[i - 1] >> 4) != (k >> 4));
+  }
+  // exclusive prefix sum of `heads` over the block
+  unsigned inc = (unsigned)heads;
+#pragma unroll
+  for (int s = 1; s < 32; s <<= 1) {
+    const unsigned o = __shfl_up_sync(0xffffffffu, inc, s);
+    if (l >= s) inc += o;
+  }
+  if (l == 31) red[w] = inc;
+  __syncthreads();
+  if (w == 0) {
+    const unsigned mine = red[l];
+    unsigned winc = mine;
+#pragma unroll
+    for (int s = 1; s < 32; s <<= 1) {
+      const unsigned o = __shfl_up_sync(0xffffffffu, winc, s);
+      if (l >= s) winc += o;
+    }
+    red[l] = winc - mine;
+    if (l == 31) red[32] = winc;
+  }
+  __syncthreads();
+  int at = (int)(red[w] + inc) - heads;
   int2* out = list + (size_t)tile * cap;
-  for (int e = t; e < RT * kUbLen; e += kUbThreads) {
-    const int mask = M[e];
-    if (!mask) continue;
-    const int b = L[e];
-    int rank = 0;
-    for (int r2 = 0; r2 < RT; ++r2)
-      if (len[r2]) rank += Pre[r2 * kUbLen + lower_bound_i(L + r2 * kUbLen, len[r2], b)];
-    out[rank] = make_int2(b, mask);
+  for (int i = t * per; i < (t + 1) * per; ++i) {
+    const unsigned k = ukeys[i];
+    if (k == kNone || (i != 0 && (ukeys[i - 1] >> 4) == (k >> 4))) continue;
+    int mask = 0;
+    for (int e = i; e < n_pad && (ukeys[e] >> 4) == (k >> 4); ++e) mask |= 1 << (ukeys[e] & 15u);
+    out[at++] = make_int2((int)(k >> 4), mask);
   }
-  if (t == 0) {
-    int total = 0;
-    for (int r = 0; r < RT; ++r) total += Pre[r * kUbLen + len[r]];
-    count[tile] = total;
-  }
+  if (t == 0) count[tile] = (int)red[32];
 }
 
 // ---- flash ---------------------------------------------------------------------------------------------------
@@ -150,48 +152,61 @@ __device__ __forceinline__ void fl_mbar_arrive(uint64_t* bar) {
 // grid (tiles, Hkv).
 __global__ void __launch_bounds__(kFlThreads, 1) qsa_flash_tc_kernel(const __grid_constant__ FlashParams P) {
   extern __shared__ __align__(128) unsigned char sm[];
-  unsigned char* Qs = sm;
-  unsigned char* Ks = Qs + kFlQBytes;                    // two stages
-  unsigned char* Vs = Ks + 2 * kFlKBytes;                // two stages
-  unsigned char* Ps = Vs + 2 * kFlKBytes;                // two buffers
-  __shared__ __align__(8) uint64_t bars[8];
-  __shared__ int blk_s[2][kFlBlocks], mask_s[2][kFlBlocks];
+  unsigned char* Ks = sm;                                // kFlStages stages
+  unsigned char* Vs = Ks + kFlStages * kFlKBytes;        // kFlStages stages
+  unsigned char* Ps = Vs + kFlStages * kFlKBytes;        // two buffers
+  __shared__ __align__(8) uint64_t bars[2 * kFlStages + 4];
+  __shared__ int blk_s[kFlStages][kFlBlocks], mask_s[kFlStages][kFlBlocks];
   __shared__ uint32_t tmem_slot;
   __shared__ volatile int dead;
-  uint64_t *kvFull = &bars[0], *sFull = &bars[2], *pFull = &bars[4], *pvDone = &bars[6];
+  uint64_t *kvFull = &bars[0], *pvDone = &bars[kFlStages], *sFull = &bars[2 * kFlStages], *pFull = &bars[2 * kFlStages + 2];
   const cr_qsa_args& a = P.a;
   const int t = threadIdx.x, w = t >> 5, l = t & 31;
   const int tile = blockIdx.x, g = blockIdx.y, row0 = tile * P.RT;
   const int gqa = P.Hq / P.Hkv;
   const int cnt = P.count[tile];
   const int n = (cnt + kFlBlocks - 1) / kFlBlocks;
-  if (n == 0) return;                                    // a tile without rows
+  if (n == 0 || cnt > P.flash_max) return;               // a tile without rows, or one the row-wise kernels serve
   const int last_pos = a.pos0 + a.R - 1;                 // newest position the cache holds
 
   if (t == 0) {
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < kFlStages; ++i) {
       umma::mbar_init(&kvFull[i], 2);                    // the two loader warps of the stage
+      umma::mbar_init(&pvDone[i], 1);                    // every MMA that read the stage has completed
+    }
+    for (int i = 0; i < 2; ++i) {
       umma::mbar_init(&sFull[i], 1);
       umma::mbar_init(&pFull[i], 4);                     // one arrival per softmax warp
-      umma::mbar_init(&pvDone[i], 1);
     }
     umma::mbar_fence_init();
     dead = 0;
   }
-  if (w == 8) umma::tmem_alloc(&tmem_slot, 512);
-  // query tile: M row m = (row m / gqa of the tile, head m % gqa of the group), fp16, K-major
-  for (int u = t; u < 128 * 32; u += kFlThreads) {
-    const int piece = u & 31, m = u >> 5, r = m / gqa, hq = m % gqa;
-    uint4 v = make_uint4(0u, 0u, 0u, 0u);
-    if (r < P.RT && row0 + r < a.R)
-      v = *reinterpret_cast<const uint4*>(P.q_hi + ((size_t)(row0 + r) * P.Hq + g * gqa + hq) * 256 + piece * 8);
-    *reinterpret_cast<uint4*>(Qs + ((size_t)piece * 128 + m) * 16) = v;
-  }
-  umma::fence_async_smem();
+  if (w == kFlIssuer) umma::tmem_alloc(&tmem_slot, 512);
   umma::fence_before_sync();
   __syncthreads();
   umma::fence_after_sync();
   const uint32_t tm = tmem_slot;
+  // Query tile into tensor memory: M row m = (row m / gqa of the tile, head m % gqa of the group) = TMEM lane m, the
+  // 256 fp16 channels of the row as 128 columns (the A operand of S = Q K^T is read from tensor memory).
+  if (w < 4) {
+    const int m = t, r = m / gqa, hq = m % gqa;
+    const bool have = r < P.RT && row0 + r < a.R;
+    const uint4* src = reinterpret_cast<const uint4*>(P.q_hi + ((size_t)(have ? row0 + r : 0) * P.Hq + g * gqa + hq) * 256);
+#pragma unroll 1
+    for (int c8 = 0; c8 < 4; ++c8) {
+      float v[32];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const uint4 x = have ? src[c8 * 8 + i] : make_uint4(0u, 0u, 0u, 0u);
+        v[4 * i] = __uint_as_float(x.x); v[4 * i + 1] = __uint_as_float(x.y); v[4 * i + 2] = __uint_as_float(x.z); v[4 * i + 3] = __uint_as_float(x.w);
+      }
+      umma::tmem_st32(umma::tmem_addr(tm, w, kColQ + 32 * c8), v);
+    }
+    umma::tmem_st_wait();
+  }
+  umma::fence_before_sync();
+  __syncthreads();
+  umma::fence_after_sync();
   bool gave_up = false;
   auto wait = [&](uint64_t* bar, uint32_t parity) {
     if (gave_up) return;
@@ -202,80 +217,84 @@ __global__ void __launch_bounds__(kFlThreads, 1) qsa_flash_tc_kernel(const __gri
     __syncwarp();
   };
 
-  if (w == 8) {
+  if (w == kFlIssuer) {
     // ------------------------------------------------------------------ issuer
     if (l == 0) {
       constexpr uint32_t idS = umma::idesc_f16(128, kFlKeys, false, false), idO = umma::idesc_f16(128, 256, false, true);
-      const uint64_t dQ = umma::smem_desc(Qs, 128 * 16, 128);
       auto issue_S = [&](int j) {
-        const int s = j & 1;
-        const uint64_t dK = umma::smem_desc(Ks + s * kFlKBytes, kFlKeys * 16, 128);
+        const uint64_t dK = umma::smem_desc(Ks + (j % kFlStages) * kFlKBytes, kFlKeys * 16, 128);
 #pragma unroll
-        for (int ks = 0; ks < 16; ++ks)                  // 16 channels per MMA = two 16-byte pieces of every row
-          umma::mma_f16_ss(tm + kColS + 64 * s, dQ + (uint64_t)(ks * 2 * 128), dK + (uint64_t)(ks * 2 * kFlKeys), idS, ks > 0);
-        umma::commit(&sFull[s]);
+        for (int ks = 0; ks < 16; ++ks)                  // 16 channels per MMA: 8 columns of Q, two 16-byte pieces of every key
+          umma::mma_f16_ts(tm + kColS + 64 * (j & 1), tm + kColQ + 8 * ks, dK + (uint64_t)(ks * 2 * kFlKeys), idS, ks > 0);
+        umma::commit(&sFull[j & 1]);
       };
-      wait(&kvFull[0], 0);
-      umma::fence_after_sync();
-      if (!gave_up) issue_S(0);
-      for (int j = 0; j < n; ++j) {
-        const int s = j & 1;
-        if (j + 1 < n) {
-          wait(&kvFull[(j + 1) & 1], ((j + 1) >> 1) & 1);
-          if (gave_up || dead) break;
+      // Event loop: S of step ns (one step ahead of the softmax at most, its accumulator being free once the
+      // probabilities of step ns - 2 are written) as soon as its tiles have landed, O += P V of step np as soon as its
+      // probabilities are written; neither waits for the other's barrier.
+      auto ready = [&](uint64_t* bar, uint32_t parity) { return umma::mbar_try(umma::smem_u32(bar), parity); };
+      auto now_ns = [] { uint64_t v; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(v)); return v; };
+      int ns = 0, np = 0, idle = 0;
+      uint64_t t_idle = 0;
+      while (np < n) {
+        if (ns < n && ns <= np + 1 && ready(&kvFull[ns % kFlStages], (ns / kFlStages) & 1)) {
           umma::fence_after_sync();
-          issue_S(j + 1);                                 // its accumulator was read by the softmax of step j - 1
-        }
-        wait(&pFull[s], (j >> 1) & 1);
-        if (gave_up || dead) break;
-        umma::fence_after_sync();
-        const uint64_t dP = umma::smem_desc(Ps + s * kFlPBytes, 128 * 16, 128);
-        const uint64_t dV = umma::smem_desc(Vs + s * kFlKBytes, 128, kFlKeys * 16);   // MN-major: step along keys 128 B, along channels 1 KB
+          issue_S(ns);
+          ++ns; idle = 0;
+        } else if (np < ns && ready(&pFull[np & 1], (np >> 1) & 1)) {
+          const int st = np % kFlStages;
+          umma::fence_after_sync();
+          const uint64_t dP = umma::smem_desc(Ps + (np & 1) * kFlPBytes, 128 * 16, 128);
+          const uint64_t dV = umma::smem_desc(Vs + st * kFlKBytes, 128, kFlKeys * 16);   // MN-major: step along keys 128 B, along channels 1 KB
 #pragma unroll
-        for (int kk = 0; kk < kFlKeys / 16; ++kk)
-          umma::mma_f16_ss(tm + kColO, dP + (uint64_t)(kk * 2 * 128), dV + (uint64_t)(kk * 16), idO, (j > 0 || kk > 0) ? 1u : 0u);
-        umma::commit(&pvDone[s]);
+          for (int kk = 0; kk < kFlKeys / 16; ++kk)
+            umma::mma_f16_ss(tm + kColO, dP + (uint64_t)(kk * 2 * 128), dV + (uint64_t)(kk * 16), idO, (np > 0 || kk > 0) ? 1u : 0u);
+          umma::commit(&pvDone[st]);
+          ++np; idle = 0;
+        } else if ((++idle & 63) == 0) {                  // nothing ready: look at the clock now and then
+          const uint64_t t1 = now_ns();
+          if (idle == 64) t_idle = t1;
+          if (dead || t1 - t_idle > 2000000000ull) { dead = 1; g_qsa_flash_status = 1; break; }
+        }
       }
     }
   } else if (w >= 4) {
-    // ------------------------------------------------------------------ loaders: warps 4,5 even steps, warps 6,7 odd steps
-    const int s = (w - 4) >> 1, lw = (w - 4) & 1;
-    const __half* kc = reinterpret_cast<const __half*>(a.c.k);
-    const __half* vc = reinterpret_cast<const __half*>(a.c.v);
+    // ------------------------------------------------------------------ loaders: two warps per stage
+    const int st = (w - 4) >> 1, lw = (w - 4) & 1;
+    const __half* kc = reinterpret_cast<const __half*>(a.c.k) + (size_t)g * 256 + (l & 1) * 8;
+    const __half* vc = reinterpret_cast<const __half*>(a.c.v) + (size_t)g * 256 + (l & 1) * 8;
     const int2* lst = P.list + (size_t)tile * P.cap;
-    for (int j = s; j < n; j += 2) {
-      if (j >= 2) warp_wait(&pvDone[s], ((j - 2) >> 1) & 1);          // the MMAs of step j - 2 have read the stage
+    const size_t row_halves = (size_t)P.Hkv * 256;
+    unsigned char* kd = Ks + st * kFlKBytes;
+    unsigned char* vd = Vs + st * kFlKBytes;
+    for (int j = st; j < n; j += kFlStages) {
+      if (j >= kFlStages) warp_wait(&pvDone[st], ((j - kFlStages) / kFlStages) & 1);   // the MMAs of the stage's last step are done
       if (dead) break;
-      int blk[4];
-#pragma unroll
-      for (int kq = 0; kq < 4; ++kq) {
-        const int idx = j * kFlBlocks + kq * 4 + (l >> 3);
-        blk[kq] = idx < cnt ? lst[idx].x : 0;
-      }
       if (lw == 0 && l < kFlBlocks) {
         const int idx = j * kFlBlocks + l;
         const int2 e = idx < cnt ? lst[idx] : make_int2(0, 0);
-        blk_s[s][l] = e.x;
-        mask_s[s][l] = e.y;
+        blk_s[st][l] = e.x;
+        mask_s[st][l] = e.y;
       }
-      unsigned char* kd = Ks + s * kFlKBytes;
-      unsigned char* vd = Vs + s * kFlKBytes;
-#pragma unroll 8
-      for (int it = 0; it < 32; ++it) {
-        const int kg = it & 3, pp = lw * 8 + (it >> 2);
-        const int key = kg * 16 + (l >> 1), piece = 2 * pp + (l & 1);
-        const int pos = blk[kg] * 4 + (key & 3);
+      // lane l serves key 16 kg + l / 2 (kg = 0..3) and the channel pieces 2 pp + l % 2, pp = 8 lw .. 8 lw + 7
+#pragma unroll
+      for (int kg = 0; kg < 4; ++kg) {
+        const int key = kg * 16 + (l >> 1), idx = j * kFlBlocks + (key >> 2);
+        const int pos = (idx < cnt ? lst[idx].x : 0) * 4 + (key & 3);
         const bool valid = pos <= last_pos;
-        const size_t src = valid ? ((size_t)pos * P.Hkv + g) * 256 + piece * 8 : 0;
-        const size_t dst = ((size_t)piece * kFlKeys + key) * 16;
-        fl_cp_async16(kd + dst, kc + src, valid);
-        fl_cp_async16(vd + dst, vc + src, valid);
+        const size_t src = valid ? (size_t)pos * row_halves : 0;
+        const size_t dst = ((size_t)(l & 1) * kFlKeys + key) * 16;
+#pragma unroll
+        for (int p8 = 0; p8 < 8; ++p8) {
+          const int pp = lw * 8 + p8;
+          fl_cp_async16(kd + dst + (size_t)pp * (2 * kFlKeys * 16), kc + src + pp * 16, valid);
+          fl_cp_async16(vd + dst + (size_t)pp * (2 * kFlKeys * 16), vc + src + pp * 16, valid);
+        }
       }
       asm volatile("cp.async.commit_group;\n" ::);
       asm volatile("cp.async.wait_group 0;\n" ::: "memory");
       umma::fence_async_smem();
       __syncwarp();
-      if (l == 0) fl_mbar_arrive(&kvFull[s]);
+      if (l == 0) fl_mbar_arrive(&kvFull[st]);
     }
   } else {
     // ------------------------------------------------------------------ softmax warps: thread = TMEM lane m
@@ -285,8 +304,8 @@ __global__ void __launch_bounds__(kFlThreads, 1) qsa_flash_tc_kernel(const __gri
     constexpr float kScale = 0.0625f * 1.4426950408889634f;            // logits / 16, in powers of two
     float m_ref = -INFINITY, lsum = 0.f;
     for (int j = 0; j < n; ++j) {
-      const int s = j & 1;
-      warp_wait(&kvFull[s], (j >> 1) & 1);                             // block ids and masks of the step are visible
+      const int s = j & 1, st = j % kFlStages;
+      warp_wait(&kvFull[st], (j / kFlStages) & 1);                     // block ids and masks of the step are visible
       warp_wait(&sFull[s], (j >> 1) & 1);
       umma::fence_after_sync();
       float sv[kFlKeys];
@@ -302,8 +321,8 @@ __global__ void __launch_bounds__(kFlThreads, 1) qsa_flash_tc_kernel(const __gri
       float tmax = -INFINITY;
 #pragma unroll
       for (int b = 0; b < kFlBlocks; ++b) {
-        const int base = blk_s[s][b] * 4;
-        const bool mine = rowok && ((mask_s[s][b] >> r) & 1);
+        const int base = blk_s[st][b] * 4;
+        const bool mine = rowok && ((mask_s[st][b] >> r) & 1);
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
           const int c = 4 * b + k;
@@ -319,7 +338,7 @@ __global__ void __launch_bounds__(kFlThreads, 1) qsa_flash_tc_kernel(const __gri
         lsum *= factor;
         m_ref = nref;
         if (j > 0) {                                                    // O holds the steps before this one
-          warp_wait(&pvDone[(j - 1) & 1], ((j - 1) >> 1) & 1);
+          warp_wait(&pvDone[(j - 1) % kFlStages], ((j - 1) / kFlStages) & 1);
           umma::fence_after_sync();
 #pragma unroll 1
           for (int c8 = 0; c8 < 8; ++c8) {
@@ -332,7 +351,7 @@ __global__ void __launch_bounds__(kFlThreads, 1) qsa_flash_tc_kernel(const __gri
           umma::tmem_st_wait();
         }
       }
-      if (j >= 2) warp_wait(&pvDone[s], ((j - 2) >> 1) & 1);            // the MMAs of step j - 2 have read this P buffer
+      if (j >= 2) warp_wait(&pvDone[(j - 2) % kFlStages], ((j - 2) / kFlStages) & 1);   // the MMAs of step j - 2 have read this P buffer
       unsigned char* pd = Ps + s * kFlPBytes;
       float add = 0.f;
 #pragma unroll
@@ -355,7 +374,7 @@ __global__ void __launch_bounds__(kFlThreads, 1) qsa_flash_tc_kernel(const __gri
       if (l == 0) fl_mbar_arrive(&pFull[s]);
     }
     // ---------------------------------------------------------------- epilogue
-    warp_wait(&pvDone[(n - 1) & 1], ((n - 1) >> 1) & 1);
+    warp_wait(&pvDone[(n - 1) % kFlStages], ((n - 1) / kFlStages) & 1);
     umma::fence_after_sync();
     const bool ok = rowok && lsum > 0.f && !dead;
     const float inv = ok ? 1.f / lsum : 0.f;
@@ -405,13 +424,14 @@ __global__ void __launch_bounds__(kFlThreads, 1) qsa_flash_tc_kernel(const __gri
   }
   umma::fence_before_sync();
   __syncthreads();
-  if (w == 8) umma::tmem_dealloc(tm, 512);
+  if (w == kFlIssuer) umma::tmem_dealloc(tm, 512);
 }
 
 // The reference's out-projection input from gated fp32 rows: fp16(WHT128(RoundH(RoundH(o) * suh)) / sqrt(128))
 // (engine/layers/qsa_long.h:476-489).  grid (Hq, R), 64 threads: a warp per 128-channel group.
-__global__ void __launch_bounds__(64) qsa_out_transform_kernel(cr_qsa_args a, const float* gated, int Hq) {
+__global__ void __launch_bounds__(64) qsa_out_transform_kernel(cr_qsa_args a, const float* gated, int Hq, const int* tile_count, int RT, int flash_max) {
   const int h = blockIdx.x, r = blockIdx.y, half = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (tile_count[r / RT] > flash_max) return;             // a row of the row-wise kernels, which transform their own output
   const int W = Hq * 256, c0 = h * 256 + half * 128 + lane * 4;
   const float4 o = *reinterpret_cast<const float4*>(gated + (size_t)r * W + c0);
   const __half* suh = reinterpret_cast<const __half*>(a.suh_o) + c0;
@@ -425,21 +445,22 @@ __global__ void __launch_bounds__(64) qsa_out_transform_kernel(cr_qsa_args a, co
 
 cr_status qsa_union_build_launch(const cr_geometry* g, const cr_qsa_args& a, int2* list, int* count, cudaStream_t stream) {
   static PerDeviceOnce configured;
-  constexpr int smem = 3 * 16 * kUbLen * (int)sizeof(int);
   if (cr_status st = once_per_device(configured, [] {
-        CR_CUDA(cudaFuncSetAttribute(qsa_union_build_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        CR_CUDA(cudaFuncSetAttribute(qsa_union_build_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 16384 * (int)sizeof(unsigned)));
         return CR_OK;
       })) return st;
   const int RT = qsa_union_rows(g), tiles = (a.R + RT - 1) / RT;
+  int n_pad = kUbThreads;
+  while (n_pad < RT * 513) n_pad <<= 1;
   use_stream(stream);
-  qsa_union_build_kernel<<<tiles, kUbThreads, smem, stream>>>(a, list, count, qsa_union_cap(RT), RT);
+  qsa_union_build_kernel<<<tiles, kUbThreads, (size_t)n_pad * sizeof(unsigned), stream>>>(a, list, count, qsa_union_cap(RT), RT, n_pad);
   CR_LAUNCH_CHECK("qsa_union_build_kernel");
   return CR_OK;
 }
 
 // Attention of the rows of `a` over the union lists; `gated` (rows x Hq x 256 floats) is needed for CR_OUT_EXL3_WHT.
 cr_status qsa_flash_launch(const cr_geometry* g, const cr_qsa_args& a, const __half* q_hi, const int2* list, const int* count,
-                           float* gated, cr_out_format fmt, cudaStream_t stream) {
+                           float* gated, cr_out_format fmt, int flash_max, cudaStream_t stream) {
   static PerDeviceOnce configured;
   if (cr_status st = once_per_device(configured, [] {
         CR_CUDA(cudaFuncSetAttribute(qsa_flash_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFlashSmem));
@@ -450,13 +471,14 @@ cr_status qsa_flash_launch(const cr_geometry* g, const cr_qsa_args& a, const __h
   P.RT = qsa_union_rows(g); P.cap = qsa_union_cap(P.RT);
   P.Hq = g->q_heads; P.Hkv = g->kv_heads; P.fmt = (int)fmt;
   P.gated = fmt == CR_OUT_EXL3_WHT ? gated : nullptr;
+  P.flash_max = flash_max;
   CR_REQUIRE(fmt != CR_OUT_EXL3_WHT || gated, "qsa flash: the EXL3 output needs the gated fp32 scratch");
   const int tiles = (a.R + P.RT - 1) / P.RT;
   use_stream(stream);
   qsa_flash_tc_kernel<<<dim3(tiles, g->kv_heads), kFlThreads, kFlashSmem, stream>>>(P);
   CR_LAUNCH_CHECK("qsa_flash_tc_kernel");
   if (fmt == CR_OUT_EXL3_WHT) {
-    qsa_out_transform_kernel<<<dim3(g->q_heads, a.R), 64, 0, stream>>>(a, gated, g->q_heads);
+    qsa_out_transform_kernel<<<dim3(g->q_heads, a.R), 64, 0, stream>>>(a, gated, g->q_heads, count, P.RT, flash_max);
     CR_LAUNCH_CHECK("qsa_out_transform_kernel");
   }
   return CR_OK;

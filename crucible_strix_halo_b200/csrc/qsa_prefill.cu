@@ -15,12 +15,17 @@ int qsa_union_rows(const cr_geometry* g);
 int qsa_union_cap(int RT);
 cr_status qsa_union_build_launch(const cr_geometry* g, const cr_qsa_args& a, int2* list, int* count, cudaStream_t stream);
 cr_status qsa_flash_launch(const cr_geometry* g, const cr_qsa_args& a, const __half* q_hi, const int2* list, const int* count,
-                           float* gated, cr_out_format fmt, cudaStream_t stream);
+                           float* gated, cr_out_format fmt, int flash_max, cudaStream_t stream);
 
-// Scratch of a part: [split-KV partials of the row-wise kernel; also the gated fp32 rows of the EXL3 transform]
-// [union lists, 2 ints per entry][union counts].  The list area is sized for tiles of 8 rows, the smallest tile.
+// Scratch of a part: [split-KV partials of the row-wise kernels][gated fp32 rows for the EXL3 transform of the tiled
+// kernel][union lists, 2 ints per entry][union counts].  The list area is sized for tiles of 8 rows, the smallest tile.
 static size_t partial_bytes(const cr_geometry* g, int rows) { return (size_t)rows * g->q_heads * kPrefillSplits * CR_QSA_PART * sizeof(float); }
+static size_t gated_bytes(const cr_geometry* g, int rows) { return (size_t)rows * g->q_heads * 256 * sizeof(float); }
 static size_t list_ints(int rows) { return (size_t)((rows + 7) / 8) * qsa_union_cap(8) * 2; }
+// A tile goes to the tiled tensor-core kernel when its rows share enough blocks: at most this many union entries per
+// row of the tile (of 513 possible).  Measured on B200 at 262,144 context: a step of 16 entries costs the tiled kernel
+// about 3 us per (tile, KV head) when its gathers miss L2, the row-wise kernels about 69 SM-us per (row, KV head).
+constexpr int kFlashEntriesPerRow = 320;
 
 static cr_status check_part(const cr_geometry* g, const cr_qsa_prefill_args* args, int skip, cr_out_format fmt, const char* who) {
   CR_REQUIRE(args, "%s: null args", who);
@@ -52,11 +57,18 @@ static cr_status attend(const cr_geometry* g, const cr_qsa_prefill_args* args, c
                         cudaStream_t stream) {
   char* scratch = (char*)args->scratch;
   if (options().qsa_union_rows >= 0 && args->q_hi) {
-    int2* list = reinterpret_cast<int2*>(scratch + ((partial_bytes(g, q.R) + 15) & ~(size_t)15));
+    float* gated = reinterpret_cast<float*>(scratch + partial_bytes(g, q.R));
+    int2* list = reinterpret_cast<int2*>(scratch + partial_bytes(g, q.R) + gated_bytes(g, q.R));
     int* count = reinterpret_cast<int*>(list + list_ints(q.R) / 2);
+    const int RT = qsa_union_rows(g);
+    const QsaTileSplit tiles = {count, RT, options().qsa_union_rows > 0 ? INT_MAX : kFlashEntriesPerRow * RT};   // an explicit tile size forces the tiled kernel
     if (cr_status s = qsa_union_build_launch(g, q, list, count, stream)) return s;
-    return qsa_flash_launch(g, q, reinterpret_cast<const __half*>(args->q_hi) + (size_t)skip * g->q_heads * 256, list, count,
-                            reinterpret_cast<float*>(scratch), fmt, stream);
+    if (cr_status s = qsa_flash_launch(g, q, reinterpret_cast<const __half*>(args->q_hi) + (size_t)skip * g->q_heads * 256, list, count,
+                                       gated, fmt, tiles.max, stream)) return s;
+    if (tiles.max == INT_MAX) return CR_OK;
+    // the tiles with little sharing: row-wise split-KV attention (its CTAs of tiled rows exit at once)
+    if (cr_status s = qsa_attn_launch(g, &q, 1, (float*)scratch, kPrefillSplits, 0, INT_MAX, stream, &tiles)) return s;
+    return qsa_merge_launch(g, &q, 1, (const float*)scratch, kPrefillSplits, false, nullptr, fmt, stream, &tiles);
   }
   if (cr_status s = qsa_attn_launch(g, &q, 1, (float*)scratch, kPrefillSplits, 0, INT_MAX, stream)) return s;
   return qsa_merge_launch(g, &q, 1, (const float*)scratch, kPrefillSplits, false, nullptr, fmt, stream);
@@ -65,7 +77,7 @@ static cr_status attend(const cr_geometry* g, const cr_qsa_prefill_args* args, c
 
 extern "C" size_t cr_qsa_prefill_scratch_bytes(const cr_geometry* g, int rows) {
   if (!g || rows < 1) return 0;
-  return ((cr::partial_bytes(g, rows) + 15) & ~(size_t)15) + cr::list_ints(rows) * sizeof(int) + (size_t)((rows + 7) / 8) * sizeof(int);
+  return cr::partial_bytes(g, rows) + cr::gated_bytes(g, rows) + cr::list_ints(rows) * sizeof(int) + (size_t)((rows + 7) / 8) * sizeof(int);
 }
 
 extern "C" size_t cr_qsa_union_list_ints(const cr_geometry* g, int rows) {

@@ -1,21 +1,21 @@
 // Exact top-512 of a row of indexer scores for sm_100a (the job of LaunchQsaTop, engine/layers/qsa_long.h:111-380):
 // the 512 best blocks in the total order (score descending, block id ascending), emitted in ascending block id.
 //
-// Method: sample, filter, sort, mark, compact.  One CTA of 1024 threads per row.
-//   1. Scores are >= +0, so their fp32 bit patterns order like unsigned integers.  A strided sample of S values
-//      (2048..8192, at least one in 32) is sorted in shared memory; the value at a rank a few standard deviations
-//      below where the 512th best is expected becomes a cut.
-//   2. One pass over the row gathers every value strictly above the cut (typically 700 to 1500 of them) into a
-//      shared-memory list, packed as 64-bit keys (bit pattern, inverted index) whose descending order is the total
-//      order.  If at least 512 and at most 4096 values passed, the best 512 of the row are among them: exact, whatever
-//      the sample was.
-//   3. The list is sorted (bitonic network), its first 512 entries set their bit in a bitmap over the row, and the
-//      bitmap is compacted in index order: a prefix sum over word popcounts gives every thread its output offset.
-//   Rows of at most 4096 values skip 1 and 2: everything is sorted.
-//   When the cut fails (fewer than 512 above it: ties at the cut or an unlucky sample; or more than 4096), the row
-//   takes the slow exact path: a binary search over the 31 value bits for the 512th best bit pattern, counting with
-//   plain reductions (no atomics, so a row of identical scores costs the same as any other), then the values above
-//   it plus the first ties in index order.
+// Method: group maxima, pivot, filter, bisect, mark, compact.  One CTA of 1024 threads per row.
+//   1. Scores are >= +0, so their fp32 bit patterns order like unsigned integers (key = pattern + 1; 0 = no element).
+//      Thread t reads the elements t, t + 1024, ... (its group) and keeps their maximum.
+//   2. The pivot is the 512th largest of the 1024 group maxima, found by bisection over the key bits: 31 block-wide
+//      counts, no sorting and no atomics.  At least 512 elements are >= the pivot (those maxima themselves), so every
+//      element that can be among the best 512, ties included, is >= the pivot; with unrelated scores about 700 are.
+//   3. A second pass gathers the elements >= the pivot into a shared-memory list (warp-aggregated appends).
+//   4. The 512th largest key of the list is found by the same bisection; keys above it are taken, and of the keys
+//      equal to it the lowest indices (counted among the ties).
+//   5. The taken elements set their bit in a bitmap over the row, which is compacted in index order: a prefix sum over
+//      word popcounts gives every thread its output offset.
+//   Rows of at most 4096 elements skip 1-3: every element goes into the list.
+//   When more than 4096 elements pass the pivot (long runs of equal scores), the row takes the slow exact path: the
+//   same bisection over the whole row, counting with plain reductions, then the values above the 512th best pattern
+//   plus its first ties in index order from a second bitmap.
 // The same routine serves a whole row, a rank's block range (candidates with their scores, for split-KV across
 // devices, engine/layers/qsa_long.h:228-234) and the merge of gathered candidates.
 #include <climits>
@@ -24,8 +24,8 @@
 namespace cr {
 
 constexpr int kSelThreads = 1024;
-constexpr int kMaxSelectCount = 262144;   // elements of one selection: the tie bitmap of the slow path shares the 32 KB sort buffer
-constexpr int kSortCap = 4096;            // 64-bit keys in the sort buffer (32 KB); also 8192 32-bit sample values
+constexpr int kMaxSelectCount = 262144;   // elements of one selection: the tie bitmap of the slow path shares the 32 KB of the candidate list
+constexpr int kSortCap = 4096;            // entries of the candidate list (32 KB)
 
 // ---- element sources ---------------------------------------------------------------------------------------
 // A source maps an element index i in [0, count) to (bit pattern, block id, valid).  Index order is block-id order.
@@ -92,129 +92,130 @@ __device__ __forceinline__ unsigned block_exclusive_scan(unsigned v, unsigned* r
   *total = red[32];
   return red[w] + inc - v;
 }
-// Descending bitonic sort of n (a power of two, n >= 2) keys in shared memory by the whole block.
-template <typename K>
-__device__ __forceinline__ void bitonic_sort_desc(K* a, int n) {
-  for (int k = 2; k <= n; k <<= 1) {
-    for (int j = k >> 1; j > 0; j >>= 1) {
-      __syncthreads();
-      for (int p = threadIdx.x; p < (n >> 1); p += kSelThreads) {
-        const int i = ((p & ~(j - 1)) << 1) | (p & (j - 1));     // pair (i, i + j)
-        const K x = a[i], y = a[i + j];
-        const bool down = (i & k) == 0;                           // this run sorts descending
-        if ((x < y) == down) { a[i] = y; a[i + j] = x; }
-      }
-    }
-  }
-  __syncthreads();
-}
-__device__ __forceinline__ int pow2_at_least(int n) {
-  int p = 2;
-  while (p < n) p <<= 1;
-  return p;
-}
-__device__ __forceinline__ unsigned long long pack_key(unsigned bits, int i) {
-  return ((unsigned long long)bits << 32) | (unsigned long long)(0xFFFFFFFFu - (unsigned)i);
-}
-__device__ __forceinline__ int key_index(unsigned long long k) { return (int)(0xFFFFFFFFu - (unsigned)(k & 0xFFFFFFFFull)); }
-
-// Shared memory of one CTA: sort buffer (32 KB), bitmap over the row's elements (count bits), small arrays.
+// Shared memory of one CTA: candidate list (32 KB), bitmap over the row's elements (count bits), small arrays.
 struct SelectSmem {
-  unsigned long long* keys;    // kSortCap 64-bit keys; also the sample (32-bit values) and the slow path's tie bitmap
+  uint2* cand;                 // kSortCap (key, index) pairs; the slow path keeps its tie bitmap here instead
   unsigned* bitmap;            // ceil(count / 32) words
   unsigned* red;               // 33 words
   unsigned* counter;           // 1 word
 };
 
-// Marks the `want` best elements of [0, count) in sm.bitmap (bit i = element i selected).  want <= count.
+constexpr int kBatch = 8;      // loads a thread issues before it uses any of them
+
+// Calls f(i, key) for the elements i = t, t + 1024, ... < count of this thread, key = bit pattern + 1 (0: no element).
+// Loads are issued kBatch at a time.  WARP_UNIFORM: f is also called with key 0 for indices past the end, so that all
+// lanes of a warp make the same number of calls (f may use warp-collective operations).
+template <bool WARP_UNIFORM, typename Src, typename F>
+__device__ __forceinline__ void for_each_key(const Src& src, int count, F&& f) {
+  const int lane = threadIdx.x & 31;
+  for (int i0 = threadIdx.x; i0 - lane < count; i0 += kSelThreads * kBatch) {   // the same trip count for a whole warp
+    unsigned key[kBatch];
+#pragma unroll
+    for (int k = 0; k < kBatch; ++k) {
+      const int i = i0 + k * kSelThreads;
+      unsigned bits = 0u;
+      key[k] = (i < count && src.get(i, bits)) ? bits + 1u : 0u;
+    }
+#pragma unroll
+    for (int k = 0; k < kBatch; ++k) {
+      const int i = i0 + k * kSelThreads;
+      if (WARP_UNIFORM ? (i - lane < count) : (i < count)) f(i, key[k]);
+    }
+  }
+}
+
+// The largest T with at least `want` keys >= T, over keys spread one per thread (mine; 0 = none).
+__device__ __forceinline__ unsigned bisect_one_per_thread(unsigned mine, int want) {
+  unsigned T = 0u;
+  for (int bit = 30; bit >= 0; --bit) {
+    const unsigned trial = T | (1u << bit);
+    if (__syncthreads_count(mine >= trial) >= want) T = trial;
+  }
+  return T;
+}
+// The same over the candidate list: thread t holds the list entries t, t + 1024, ... (at most 4).
+__device__ __forceinline__ unsigned bisect_list(const uint2* cand, int m, int want) {
+  unsigned k[4];
+#pragma unroll
+  for (int q = 0; q < 4; ++q) { const int i = threadIdx.x + q * kSelThreads; k[q] = i < m ? cand[i].x : 0u; }
+  unsigned T = 0u;
+  for (int bit = 30; bit >= 0; --bit) {
+    const unsigned trial = T | (1u << bit);
+    const int c = (k[0] >= trial) + (k[1] >= trial) + (k[2] >= trial) + (k[3] >= trial);
+    int total;
+    if (m <= kSelThreads) total = __syncthreads_count(c);
+    else total = __syncthreads_count(c & 1) + 2 * __syncthreads_count(c & 2) + 4 * __syncthreads_count(c & 4);
+    if (total >= want) T = trial;
+  }
+  return T;
+}
+
+// Marks the `want` best elements of [0, count) in sm.bitmap (bit i = element i selected).  want <= valid elements.
 template <typename Src>
 __device__ __forceinline__ void select_mark(const Src& src, int count, int want, const SelectSmem& sm) {
   const int t = threadIdx.x, l = t & 31;
   const int words = (count + 31) >> 5;
   for (int i = t; i < words; i += kSelThreads) sm.bitmap[i] = 0u;
-  auto mark_sorted_prefix = [&](int n_sorted) {                   // the first `want` keys of the sorted buffer
-    (void)n_sorted;
-    __syncthreads();
-    for (int i = t; i < want; i += kSelThreads) {
-      const int e = key_index(sm.keys[i]);
-      atomicOr(&sm.bitmap[e >> 5], 1u << (e & 31));
-    }
-    __syncthreads();
-  };
-  if (count <= kSortCap) {
-    // ---- everything fits: sort it all
-    const int n = pow2_at_least(count);
-    for (int i = t; i < n; i += kSelThreads) {
-      unsigned bits = 0u;
-      const bool ok = i < count && src.get(i, bits);
-      sm.keys[i] = ok ? pack_key(bits, i) : 0ull;                  // padding sorts last (a real key is never 0)
-    }
-    bitonic_sort_desc(sm.keys, n);
-    mark_sorted_prefix(n);
-    return;
-  }
-  // ---- 1. sample and cut
-  int S = pow2_at_least((count + 31) / 32);
-  S = S < 2048 ? 2048 : (S > 2 * kSortCap ? 2 * kSortCap : S);
-  unsigned* sample = reinterpret_cast<unsigned*>(sm.keys);
-  for (int s = t; s < S; s += kSelThreads) {
-    const int i = (int)(((long long)s * count) / S);
-    unsigned bits = 0u;
-    if (!src.get(i, bits)) bits = 0u;
-    sample[s] = bits;
-  }
-  bitonic_sort_desc(sample, S);
-  const float expect = (float)want * (float)S / (float)count;     // sample rank where the want-th best is expected
-  int rho = (int)ceilf(expect + 5.5f * sqrtf(expect) + 2.f);
-  rho = rho > S ? S : rho;
-  const unsigned cut = sample[rho - 1];
-  __syncthreads();                                                 // the sample is dead: the buffer becomes the list
   if (t == 0) *sm.counter = 0u;
+  unsigned pivot = 1u;                                             // every element passes
+  if (count > kSortCap) {
+    unsigned mine = 0u;
+    for_each_key<false>(src, count, [&](int, unsigned key) { mine = key > mine ? key : mine; });
+    pivot = bisect_one_per_thread(mine, want);                     // 0 when fewer than `want` groups hold an element
+    if (pivot == 0u) pivot = 1u;
+  }
   __syncthreads();
-  // ---- 2. gather everything strictly above the cut
-  for (int i0 = 0; i0 < count; i0 += kSelThreads) {
-    const int i = i0 + t;
-    unsigned bits = 0u;
-    const bool pass = i < count && src.get(i, bits) && bits > cut;
+  // ---- the elements >= pivot, as (key, index) pairs
+  for_each_key<true>(src, count, [&](int i, unsigned key) {
+    const bool pass = key >= pivot;
     const unsigned m = __ballot_sync(0xffffffffu, pass);
     if (m) {
       unsigned base = 0u;
       if (l == 0) base = atomicAdd(sm.counter, (unsigned)__popc(m));
       base = __shfl_sync(0xffffffffu, base, 0);
       const unsigned at = base + __popc(m & ((1u << l) - 1u));
-      if (pass && at < (unsigned)kSortCap) sm.keys[at] = pack_key(bits, i);
+      if (pass && at < (unsigned)kSortCap) sm.cand[at] = make_uint2(key, (unsigned)i);
     }
-  }
+  });
   __syncthreads();
-  const int got = (int)*sm.counter;
-  if (got >= want && got <= kSortCap) {
-    // ---- 3. the best `want` are all in the list
-    const int n = pow2_at_least(got);
-    for (int i = got + t; i < n; i += kSelThreads) sm.keys[i] = 0ull;
-    bitonic_sort_desc(sm.keys, n);
-    mark_sorted_prefix(n);
+  const int m = (int)*sm.counter;
+  if (m <= kSortCap) {
+    // ---- the 512th largest key of the list, then the keys above it and its first ties
+    const unsigned T = bisect_list(sm.cand, m, want);
+    int gt = 0, eq = 0;
+    for (int i = t; i < m; i += kSelThreads) { const unsigned k = sm.cand[i].x; gt += k > T; eq += k == T; }
+    const int n_gt = (int)block_sum_u32((unsigned)gt, sm.red), n_eq = (int)block_sum_u32((unsigned)eq, sm.red);
+    const int need = want - n_gt;                                  // ties to take: 1 <= need <= n_eq
+    for (int i = t; i < m; i += kSelThreads) {
+      const uint2 c = sm.cand[i];
+      bool take = c.x > T;
+      if (c.x == T) {
+        if (need >= n_eq) take = true;
+        else {                                                     // rank among the ties by index
+          int before = 0;
+          for (int j = 0; j < m; ++j) { const uint2 o = sm.cand[j]; before += (o.x == T && o.y < c.y); }
+          take = before < need;
+        }
+      }
+      if (take) atomicOr(&sm.bitmap[c.y >> 5], 1u << (c.y & 31));
+    }
+    __syncthreads();
     return;
   }
-  // ---- slow exact path: T = the largest bit pattern with at least `want` elements >= T
+  // ---- slow exact path: T = the largest key with at least `want` elements >= T
   unsigned T = 0u;
   for (int bit = 30; bit >= 0; --bit) {
     const unsigned trial = T | (1u << bit);
     unsigned c = 0u;
-    for (int i = t; i < count; i += kSelThreads) {
-      unsigned bits;
-      if (src.get(i, bits) && bits >= trial) ++c;
-    }
+    for_each_key<false>(src, count, [&](int, unsigned key) { c += key >= trial; });
     if (block_sum_u32(c, sm.red) >= (unsigned)want) T = trial;
   }
-  unsigned* ties = reinterpret_cast<unsigned*>(sm.keys);           // bitmap of the elements equal to T (<= 32 KB)
+  unsigned* ties = reinterpret_cast<unsigned*>(sm.cand);           // bitmap of the elements equal to T (<= 32 KB)
   unsigned above = 0u;
-  for (int i0 = 0; i0 < words * 32; i0 += kSelThreads) {           // a warp covers one bitmap word per iteration
-    const int i = i0 + t;
-    unsigned bits = 0u;
-    const bool ok = i < count && src.get(i, bits);
-    const unsigned gt = __ballot_sync(0xffffffffu, ok && bits > T), eq = __ballot_sync(0xffffffffu, ok && bits == T);
+  for_each_key<true>(src, count, [&](int i, unsigned key) {        // a warp covers one bitmap word per call
+    const unsigned gt = __ballot_sync(0xffffffffu, key > T), eq = __ballot_sync(0xffffffffu, key == T);
     if (l == 0 && (i >> 5) < words) { sm.bitmap[i >> 5] = gt; ties[i >> 5] = eq; above += __popc(gt); }
-  }
+  });
   const unsigned n_above = block_sum_u32(above, sm.red);
   const unsigned need = (unsigned)want - n_above;                  // ties to take, lowest indices first
   // every thread owns a run of consecutive words: ties before the run decide how many of its own it takes
@@ -261,7 +262,7 @@ __device__ __forceinline__ void select_emit(const Src& src, int count, const Sel
 
 __device__ __forceinline__ SelectSmem carve(unsigned char* raw, int max_count) {
   SelectSmem sm;
-  sm.keys = reinterpret_cast<unsigned long long*>(raw);
+  sm.cand = reinterpret_cast<uint2*>(raw);
   sm.bitmap = reinterpret_cast<unsigned*>(raw + (size_t)kSortCap * 8);
   sm.red = sm.bitmap + ((max_count + 31) >> 5);
   sm.counter = sm.red + 33;

@@ -118,6 +118,8 @@ __host__ __device__ constexpr uint32_t idesc_tf32(int M, int N, bool a_mn, bool 
          ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 
+// D[tmem] (+)= A[tmem] B[smem] with fp16 operands: A in tensor memory, lane = row, two K elements per 32-bit column.
+__device__ __forceinline__ void mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate);
 // Instruction descriptor for kind::f16 with fp16 operands (format 0), fp32 accumulation.  a_mn / b_mn: the operand is
 // MN-major (its M or N index is the contiguous one in shared memory) instead of K-major.
 __host__ __device__ constexpr uint32_t idesc_f16(int M, int N, bool a_mn, bool b_mn) {
@@ -145,6 +147,15 @@ __device__ __forceinline__ void mma_tf32_ss(uint32_t d_tmem, uint64_t a_desc, ui
 // The mbarrier receives one arrival when every MMA issued so far by this thread has completed.
 __device__ __forceinline__ void commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
 }
 
 // ---- TMEM -> registers -----------------------------------------------------------------------------------

@@ -73,19 +73,34 @@ __global__ void __launch_bounds__(128) umma_f16_test_kernel(const __half* A, con
     *reinterpret_cast<uint4*>(Bs + ((size_t)nc * K + k) * 16) = *reinterpret_cast<const uint4*>(B + (size_t)k * N + nc * 8);
   }
   if (t == 0) { umma::mbar_init(&bar, 1); umma::mbar_fence_init(); }
-  if (w == 0) umma::tmem_alloc(&tmem_slot, 256);
+  if (w == 0) umma::tmem_alloc(&tmem_slot, 512);
   umma::fence_async_smem();
   umma::fence_before_sync();
   __syncthreads();
   umma::fence_after_sync();
   const uint32_t tmem = tmem_slot;
+  const bool a_tmem = (variant & 2) != 0;
+  if (a_tmem) {   // A from tensor memory: lane = row, column c of the operand holds elements 2c (low half) and 2c + 1
+    for (int c0 = 0; c0 < K / 2; c0 += 16) {
+      float v[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i)
+        v[i] = c0 + i < K / 2 ? __uint_as_float(*reinterpret_cast<const unsigned*>(A + (size_t)t * K + 2 * (c0 + i))) : 0.f;
+      umma::tmem_st16(umma::tmem_addr(tmem, w, 256 + c0), v);
+    }
+    umma::tmem_st_wait();
+    umma::fence_before_sync();
+    __syncthreads();
+    umma::fence_after_sync();
+  }
   if (t == 0) {
     const uint32_t idesc = umma::idesc_f16(128, N, false, true);
     const uint32_t step_n = (uint32_t)K * 16u, step_k = 128u;
     for (int k0 = 0; k0 < K; k0 += 16) {
       const uint64_t da = umma::smem_desc(As + (size_t)(k0 / 8) * 128 * 16, 128 * 16, 128);
-      const uint64_t db = variant == 0 ? umma::smem_desc(Bs + (size_t)k0 * 16, step_n, step_k) : umma::smem_desc(Bs + (size_t)k0 * 16, step_k, step_n);
-      umma::mma_f16_ss(tmem, da, db, idesc, k0 > 0);
+      const uint64_t db = (variant & 1) == 0 ? umma::smem_desc(Bs + (size_t)k0 * 16, step_n, step_k) : umma::smem_desc(Bs + (size_t)k0 * 16, step_k, step_n);
+      if (a_tmem) umma::mma_f16_ts(tmem, tmem + 256 + k0 / 2, db, idesc, k0 > 0);
+      else umma::mma_f16_ss(tmem, da, db, idesc, k0 > 0);
     }
     umma::commit(&bar);
   }
@@ -102,7 +117,7 @@ __global__ void __launch_bounds__(128) umma_f16_test_kernel(const __half* A, con
   if (!ok && t == 0) *status = 1;
   umma::fence_before_sync();
   __syncthreads();
-  if (w == 0) umma::tmem_dealloc(tmem, 256);
+  if (w == 0) umma::tmem_dealloc(tmem, 512);
 }
 
 CR_DEFINE_STATUS_WORD(debug_wait)
@@ -134,7 +149,7 @@ extern "C" cr_status cr_debug_umma_f16_gemm(const uint16_t* A, const uint16_t* B
   using namespace cr;
   CR_REQUIRE(A && B && D && status, "cr_debug_umma_f16_gemm: null buffer");
   CR_REQUIRE(K >= 16 && K % 16 == 0 && K <= 128 && N >= 32 && N % 32 == 0 && N <= 256, "cr_debug_umma_f16_gemm: K in 16..128 step 16, N in 32..256 step 32");
-  CR_REQUIRE(variant == 0 || variant == 1, "cr_debug_umma_f16_gemm: variant 0 or 1");
+  CR_REQUIRE(variant >= 0 && variant <= 3, "cr_debug_umma_f16_gemm: variant 0..3");
   const size_t smem = (size_t)(128 + N) * K * 2;
   CR_CUDA(cudaFuncSetAttribute(umma_f16_test_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   use_stream((cudaStream_t)stream);

@@ -88,7 +88,7 @@ class GdnPrefillPlan:
 class QsaWeights:
     """Per-layer constants of a QSA layer: (1 + w) norm vectors, RoPE table, optional suh."""
 
-    def __init__(self, g: Geometry, q_norm1, k_norm1, iq_norm1, ik_norm1, suh=None, device="cuda"):
+    def __init__(self, g: Geometry, q_norm1, k_norm1, iq_norm1, ik_norm1, suh=None, device="cuda", rope_factor=1):
         f = dict(device=device, dtype=torch.float32)
         self.g = g
         self.q_norm1 = torch.as_tensor(q_norm1).to(**f).contiguous()
@@ -97,7 +97,8 @@ class QsaWeights:
         self.ik_norm1 = torch.as_tensor(ik_norm1).to(**f).contiguous()
         self.suh = None if suh is None else torch.as_tensor(suh).to(device=device, dtype=torch.float16).contiguous()
         self.rope = torch.empty(64, **f)
-        check(lib.cr_rope_table_fill(dptr(self.rope), _stream()))
+        check(lib.cr_rope_table_fill_yarn(dptr(self.rope), rope_factor, _stream()))   # factor 1: the plain table
+        torch.cuda.current_stream().synchronize()
 
 
 class QsaSession:
@@ -122,11 +123,11 @@ class QsaSession:
         return self.ik_pool.view(-1, 128, 32).transpose(1, 2).reshape(-1, 128)[:nb]
 
 
-def qsa_args(w: QsaWeights, s: QsaSession, q, k, v, idx, out, pos0, context=None, pack_rows=0, pack_off=0):
+def qsa_args(w: QsaWeights, s: QsaSession, q, k, v, idx, out, pos0, context=None, pack_rows=0, pack_off=0, mrope=None):
     R = q.shape[0]
     return QsaArgs(dptr(q), dptr(k), dptr(v), dptr(idx), dptr(w.q_norm1), dptr(w.k_norm1), dptr(w.iq_norm1),
                    dptr(w.ik_norm1), s.cache_struct(), dptr(s.scores), s.sstride, dptr(s.sel), dptr(s.nsel),
-                   dptr(w.suh), dptr(out), pos0, R, dptr(context), pack_rows, pack_off, None, dptr(w.rope))
+                   dptr(w.suh), dptr(out), pos0, R, dptr(context), pack_rows, pack_off, dptr(mrope), dptr(w.rope))
 
 
 class QsaStepPlan:

@@ -176,8 +176,9 @@ typedef struct {
   int pos0, R;
   float* context;         /* optional un-gated fp32 [R][Hq][256] */
   int pack_rows, pack_off;
-  const int* mrope;       /* must be NULL (multimodal positions: CR_ERR_UNSUPPORTED) */
-  const float* rope;      /* 64-float table: [0,32) inverse frequencies, [32] cos/sin multiplier */
+  const int* mrope;       /* NULL for text; else [capacity][4] (t, h, w, unused) positions of every cache position
+                             (SequenceState::mrope, engine/runtime/sequence_state.h:33-35; Rope64Axes, ops.h:515-541) */
+  const float* rope;      /* 64-float table: [0,32) inverse frequencies, [32] cos/sin multiplier (plain or YaRN) */
 } cr_qsa_args;
 
 /* Scratch sizing (engine/layers/qsa_long.h:226, :396; engine/layers/ops.h:420;
@@ -191,11 +192,19 @@ cr_status cr_qsa_cache_bytes(const cr_geometry* g, int ctx, int bounded, size_t 
 
 /* Replaces RopePlainFillKernel / PlainRopeTable (engine/layers/ops.h:469-493). */
 cr_status cr_rope_table_fill(float* table, void* stream);
+/* The YaRN rows of FillRopeTables (engine/layers/ops.h:476-484; engine/layers/rope_tables.h; RopeMode Yarn2 / Yarn4,
+ * engine/runtime/rope_mode.h:13-21): the table for contexts of factor x 262,144 positions, computed instead of stored.
+ * factor 1 gives the plain table. */
+cr_status cr_rope_table_fill_yarn(float* table, int factor, void* stream);
 
 /* Replaces QsaPrepKernel + QsaPoolKernel (+ QsaRetainRawKernel) for decode / verify rows
  * (engine/layers/ops.h:561-601, :610-645): q and indexer-query heads normed + roped in place, K/V rows to the
  * fp16 cache, raw indexer key cached, blocks completed by these rows pooled. */
 cr_status cr_qsa_prep(const cr_geometry* g, const cr_qsa_args* spans, int n_spans, void* stream);
+
+/* The query half of cr_qsa_prep alone (q and indexer-query heads normed + roped in place, nothing cached), for up to
+ * 2048 rows.  No counterpart in the reference. */
+cr_status cr_qsa_prep_queries(const cr_geometry* g, const cr_qsa_args* spans, int n_spans, void* stream);
 
 /* Replaces LaunchQsaSelect (engine/layers/qsa_long.h:383-387): indexer scores (rows with more than 512
  * complete blocks) + exact top-512 in the order (score desc, block id asc), emitted ascending;

@@ -161,6 +161,15 @@ def main(ref_root):
         print("ref/oracle.py layer functions not recorded:", e)
         out["layers"] = np.array(0)
 
+    # (7) the YaRN rows of engine/layers/rope_tables.h (generated constants: 32 inverse frequencies + multiplier per mode)
+    import re
+    text = open(os.path.join(ref_root, "engine", "layers", "rope_tables.h")).read()
+    rows = re.findall(r"\{\s*//\s*factor\s+(\d+).*?\n(.*?)\},", text, re.S)
+    for factor, body in rows:
+        vals = [float.fromhex(v.rstrip("f")) for v in re.findall(r"0x[0-9a-fA-F.]+p[+-]\d+f", body)]
+        assert len(vals) == 33
+        out["yarn_table_%s" % factor] = np.array(vals, np.float32)
+
     dst = os.path.join(os.path.dirname(os.path.abspath(__file__)), "ref_vectors.npz")
     np.savez_compressed(dst, **out)
     print("wrote", dst, os.path.getsize(dst), "bytes")

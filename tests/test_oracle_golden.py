@@ -187,3 +187,33 @@ def test_qsa_dense_rows_match_the_references_own_layer_function():
             exact[r, h] = (pr / pr.sum()) @ v64[:r + 1, h // 12]
     exact = (exact * ao.sigmoid(q64[..., D:])).reshape(n, -1)
     np.testing.assert_allclose(exact, ref, rtol=1e-9, atol=1e-11)
+
+
+@pytest.mark.parametrize("factor", [2, 4])
+def test_yarn_tables_match_the_references_rows(factor):
+    """The YaRN rows of engine/layers/rope_tables.h (32 inverse frequencies + the cos/sin multiplier), recomputed: equal to
+    one or two units in the last place of float32 (the rows were generated with torch's float32 power function)."""
+    ref = G["yarn_table_%d" % factor]
+    inv, mult = ao.yarn_table(factor)
+    np.testing.assert_allclose(inv, ref[:32], rtol=4e-7, atol=0)
+    np.testing.assert_allclose(mult, ref[32], rtol=1e-7)
+    plain, one = ao.yarn_table(1)
+    np.testing.assert_array_equal(inv[:8], plain[:8])                  # fast frequencies are kept
+    np.testing.assert_allclose(inv[24:], plain[24:] / factor, rtol=2e-7)   # slow ones are divided by the factor
+
+
+def test_multimodal_rope_with_equal_axes_is_the_text_rotation():
+    """Rope64Axes with t = h = w equals Rope64 (engine/layers/ops.h:515-536); distinct axes rotate frequency j by the h
+    position when j % 3 == 1, by w when j % 3 == 2 and j < 30."""
+    rng = np.random.default_rng(4)
+    x = rng.normal(size=(5, 3, 256))
+    pos = np.array([0., 7., 300., 4096., 99999.])
+    axes = np.stack([pos, pos, pos], -1)
+    np.testing.assert_allclose(ao.rope64(x, pos, axes=axes), ao.rope64(x, pos), rtol=0, atol=1e-15)
+    axes = np.stack([pos, pos + 3, pos + 11], -1)
+    got = ao.rope64(x, pos, axes=axes)
+    inv = ao.rope_inv_freq(ao.GEOM_BENCH)
+    for j, which in ((0, 0), (1, 1), (2, 2), (29, 2), (30, 0), (31, 1)):
+        ang = axes[:, which] * inv[j]
+        want = x[:, :, j] * np.cos(ang)[:, None] - x[:, :, j + 32] * np.sin(ang)[:, None]
+        np.testing.assert_allclose(got[:, :, j], want, rtol=1e-12, atol=1e-12)

@@ -480,3 +480,57 @@ def test_merge_rejects_more_partials_than_it_combines():
     a = (capi.QsaArgs * 1)(layers.qsa_args(w, ses, q, kv, kv, idx, out, 10))
     parts = torch.zeros(33, 1, 16, 258, device="cuda")
     assert capi.lib.cr_qsa_merge_partials(C.byref(g), a, 33, parts.data_ptr(), capi.OUT_RAW_F32, None) == capi.ERR_INVALID
+
+
+@pytest.mark.parametrize("factor", [2, 4])
+def test_yarn_table_and_multimodal_positions_match_oracle(factor):
+    """YaRN tables (cr_rope_table_fill_yarn) against the reference's stored rows, then decode steps and a prefill part in
+    which the table and a multimodal position table (distinct t / h / w per cache position) drive every rotation: q, k,
+    indexer queries and pooled keys, against the oracle."""
+    import os
+    capi, layers, g, og, rng, norms, suh, _ = _setup(16, seed=19)
+    w = layers.QsaWeights(g, *norms, suh=suh, rope_factor=factor)
+    golden = np.load(os.path.join(os.path.dirname(__file__), "golden", "ref_vectors.npz"))["yarn_table_%d" % factor]
+    t = w.rope.cpu().numpy()
+    np.testing.assert_allclose(t[:33], golden, rtol=4e-7, atol=0)
+    assert not t[33:].any()
+    table = (t[:32].astype(np.float64), float(t[32]))
+    ctx = 2600
+    mro = np.zeros((ctx, 4), np.int32)
+    mro[:, 0] = np.arange(ctx)                                    # text positions, then an image patch grid from 40 on
+    mro[:, 1] = np.arange(ctx); mro[:, 2] = np.arange(ctx)
+    mro[40:296, 0] = 40; mro[40:296, 1] = 40 + np.arange(256) // 16; mro[40:296, 2] = 40 + np.arange(256) % 16
+    mro[296:, :3] = (np.arange(296, ctx) - 296 + 56)[:, None]
+    mro_d = dev(mro, torch.int32)
+    ses, oc = layers.QsaSession(g, ctx), ao.QsaCache(og, ctx)
+    R = 2300
+    ses.scores = torch.zeros(2048, ses.sstride, device="cuda"); ses.sel = torch.zeros(2048, 512, device="cuda", dtype=torch.int32)
+    ses.nsel = torch.zeros(2048, device="cuda", dtype=torch.int32)
+    plan = layers.QsaPrefillPlan(w, 2048)
+    q, k, v, idx = _rows(rng, og, R)
+    sample = [0, 41, 100, 295, 296, 1000, 2047]
+    ref, sels, scs, _, _ = ao.qsa_rows(q, k, v, idx, norms, oc, 0, og, return_detail=True, rows=sample + [2299], table=table, mrope=mro)
+    outs = []
+    for p0, n in ((0, 2048), (2048, R - 2048)):
+        keep = [dev(t_[p0:p0 + n]) for t_ in (q, k, v, idx)]          # the argument block holds raw pointers: keep the tensors alive
+        a = capi.QsaPrefillArgs(layers.qsa_args(w, ses, *keep, plan.out, p0, mrope=mro_d),
+                                capi.dptr(plan.q_hi), capi.dptr(plan.scratch), plan.scratch.numel())
+        capi.check(capi.lib.cr_qsa_prefill(C.byref(g), C.byref(a), 0, capi.OUT_RAW_F32, None))
+        outs.append(plan.out[:n].cpu().numpy().copy())
+    out = np.concatenate(outs)
+    np.testing.assert_allclose(ses.pool_rows(R // 4).cpu().numpy(), oc.pool_rows(R // 4), rtol=0, atol=2e-3)
+    np.testing.assert_allclose(ses.k[:R].float().cpu().numpy(), oc.k[:R].astype(np.float32), rtol=0, atol=4e-3)
+    for o, r in enumerate(sample + [2299]):
+        if sels[o] is not None and not np.array_equal(ses.sel[r - 2048].cpu().numpy(), sels[o]):
+            assert ao.selection_agrees(scs[o], ses.sel[r - 2048].cpu().numpy(), sels[o])
+            continue
+        assert_close_attn(out[r], ref[o], max_abs=PREFILL_ABS, cos=0.99999, what="row %d" % r)
+    # a decode step on top, same tables
+    row = _rows(rng, og, 1)
+    refd = ao.qsa_rows(*row, norms, oc, R, og, table=table, mrope=mro)
+    ses.scores = torch.zeros(1, ses.sstride, device="cuda")
+    sp = layers.QsaStepPlan(w, 1)
+    keep = [dev(t_) for t_ in row]
+    arr = (capi.QsaArgs * 1)(layers.qsa_args(w, ses, *keep, plan.out, R, mrope=mro_d))
+    capi.check(capi.lib.cr_qsa_step(C.byref(g), arr, 1, capi.dptr(sp.scratch), sp.scratch.numel(), capi.OUT_RAW_F32, None))
+    assert_close_attn(plan.out[:1].cpu().numpy(), refd, max_abs=1e-3, cos=0.99999, what="decode row")
