@@ -46,6 +46,7 @@ __device__ __forceinline__ void split8(const float (&x)[8], uint4& hi, uint4& lo
 }
 
 // grid (row tiles, splits, spans).
+template <bool RANGED>
 __global__ void __launch_bounds__(kScThreads, 1) qsa_score_tc_kernel(const __grid_constant__ QsaParams P) {
   extern __shared__ __align__(128) unsigned char sm[];
   unsigned char* Qop = sm;
@@ -60,8 +61,8 @@ __global__ void __launch_bounds__(kScThreads, 1) qsa_score_tc_kernel(const __gri
   const int rows = min(kScRows, a.R - r0);
   const int nb_all = (a.pos0 + r0 + rows) / 4;            // blocks visible to the last row of the tile
   if (nb_all <= CR_SEL_BLOCKS) return;
-  const int nb_hi = min(nb_all, P.b_hi);                  // the scored range [b_lo, b_hi) of a rank
-  const int tile_lo = P.b_lo / kScBlocks, tiles = (nb_hi + kScBlocks - 1) / kScBlocks - tile_lo;
+  const int nb_hi = RANGED ? min(nb_all, P.b_hi) : nb_all;   // RANGED: the scored range [b_lo, b_hi) of a rank
+  const int tile_lo = RANGED ? P.b_lo / kScBlocks : 0, tiles = (nb_hi + kScBlocks - 1) / kScBlocks - tile_lo;
   if (tiles <= 0) return;
   const int t0 = tile_lo + (int)((long long)tiles * blockIdx.y / gridDim.y), t1 = tile_lo + (int)((long long)tiles * (blockIdx.y + 1) / gridDim.y);
   if (t0 >= t1) return;
@@ -182,7 +183,7 @@ __global__ void __launch_bounds__(kScThreads, 1) qsa_score_tc_kernel(const __gri
       umma::fence_before_sync();
       __syncwarp();
       if (l == 0) umma::mbar_arrive_relaxed(&accFree[buf]);
-      if (b < nb_hi && b >= P.b_lo) {
+      if (b < nb_hi && (!RANGED || b >= P.b_lo)) {
         float* dst = a.scores + (size_t)r0 * a.sstride + b;
 #pragma unroll
         for (int c = 0; c < kScRows; ++c)
@@ -198,7 +199,8 @@ __global__ void __launch_bounds__(kScThreads, 1) qsa_score_tc_kernel(const __gri
 cr_status qsa_score_tc_launch(const QsaParams& P, int Rmax, int n, cudaStream_t stream) {
   static PerDeviceOnce configured;
   if (cr_status st = once_per_device(configured, [] {
-        CR_CUDA(cudaFuncSetAttribute(qsa_score_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kScoreSmem));
+        CR_CUDA(cudaFuncSetAttribute(qsa_score_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kScoreSmem));
+        CR_CUDA(cudaFuncSetAttribute(qsa_score_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kScoreSmem));
         return CR_OK;
       })) return st;
   const int row_tiles = (Rmax + kScRows - 1) / kScRows;
@@ -216,7 +218,8 @@ cr_status qsa_score_tc_launch(const QsaParams& P, int Rmax, int n, cudaStream_t 
     const double cost = (double)waves / sp;
     if (cost < best - 1e-9) { best = cost; splits = sp; }
   }
-  qsa_score_tc_kernel<<<dim3(row_tiles, splits, n), kScThreads, kScoreSmem, stream>>>(P);
+  if (P.b_lo > 0 || P.b_hi < INT_MAX) qsa_score_tc_kernel<true><<<dim3(row_tiles, splits, n), kScThreads, kScoreSmem, stream>>>(P);
+  else qsa_score_tc_kernel<false><<<dim3(row_tiles, splits, n), kScThreads, kScoreSmem, stream>>>(P);
   CR_LAUNCH_CHECK("qsa_score_tc_kernel");
   return CR_OK;
 }

@@ -19,7 +19,10 @@
 // The same routine serves a whole row, a rank's block range (candidates with their scores, for split-KV across
 // devices, engine/layers/qsa_long.h:228-234) and the merge of gathered candidates.
 #include <climits>
+#include <cooperative_groups.h>
 #include "qsa.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace cr {
 
@@ -133,13 +136,16 @@ __device__ __forceinline__ unsigned bisect_one_per_thread(unsigned mine, int wan
   }
   return T;
 }
-// The same over the candidate list: thread t holds the list entries t, t + 1024, ... (at most 4).
-__device__ __forceinline__ unsigned bisect_list(const uint2* cand, int m, int want) {
+// The same over the candidate list: thread t holds the list entries t, t + 1024, ... (at most 4).  Every key lies in
+// [lo, hi]: the bits above the first bit in which lo and hi differ are settled, and the search starts below them.
+__device__ __forceinline__ unsigned bisect_list(const uint2* cand, int m, int want, unsigned lo, unsigned hi) {
   unsigned k[4];
 #pragma unroll
   for (int q = 0; q < 4; ++q) { const int i = threadIdx.x + q * kSelThreads; k[q] = i < m ? cand[i].x : 0u; }
-  unsigned T = 0u;
-  for (int bit = 30; bit >= 0; --bit) {
+  if (lo >= hi) return lo;
+  const int top = 31 - __clz(lo ^ hi);                             // the first differing bit
+  unsigned T = lo & ~((2u << top) - 1u);
+  for (int bit = top; bit >= 0; --bit) {
     const unsigned trial = T | (1u << bit);
     const int c = (k[0] >= trial) + (k[1] >= trial) + (k[2] >= trial) + (k[3] >= trial);
     int total;
@@ -149,6 +155,35 @@ __device__ __forceinline__ unsigned bisect_list(const uint2* cand, int m, int wa
   }
   return T;
 }
+
+// The list sm.cand[0, m) holds (key, index) pairs that include the `want` best elements of the row (want <= m <= kSortCap):
+// marks those in sm.bitmap.  The want-th largest key by bisection; keys above it are taken, and of the keys equal to it
+// the lowest indices (counted among the ties).
+__device__ __forceinline__ void select_from_list(int m, int want, const SelectSmem& sm, unsigned lo = 0u, unsigned hi = 0x7FFFFFFFu) {
+  const int t = threadIdx.x;
+  const unsigned T = bisect_list(sm.cand, m, want, lo, hi);
+  int gt = 0, eq = 0;
+  for (int i = t; i < m; i += kSelThreads) { const unsigned k = sm.cand[i].x; gt += k > T; eq += k == T; }
+  const int n_gt = (int)block_sum_u32((unsigned)gt, sm.red), n_eq = (int)block_sum_u32((unsigned)eq, sm.red);
+  const int need = want - n_gt;                                    // ties to take: 1 <= need <= n_eq
+  for (int i = t; i < m; i += kSelThreads) {
+    const uint2 c = sm.cand[i];
+    bool take = c.x > T;
+    if (c.x == T) {
+      if (need >= n_eq) take = true;
+      else {                                                       // rank among the ties by index
+        int before = 0;
+        for (int j = 0; j < m; ++j) { const uint2 o = sm.cand[j]; before += (o.x == T && o.y < c.y); }
+        take = before < need;
+      }
+    }
+    if (take) atomicOr(&sm.bitmap[c.y >> 5], 1u << (c.y & 31));
+  }
+  __syncthreads();
+}
+
+template <typename Src>
+__device__ __forceinline__ void select_slow(const Src& src, int count, int want, const SelectSmem& sm);
 
 // Marks the `want` best elements of [0, count) in sm.bitmap (bit i = element i selected).  want <= valid elements.
 template <typename Src>
@@ -179,29 +214,15 @@ __device__ __forceinline__ void select_mark(const Src& src, int count, int want,
   });
   __syncthreads();
   const int m = (int)*sm.counter;
-  if (m <= kSortCap) {
-    // ---- the 512th largest key of the list, then the keys above it and its first ties
-    const unsigned T = bisect_list(sm.cand, m, want);
-    int gt = 0, eq = 0;
-    for (int i = t; i < m; i += kSelThreads) { const unsigned k = sm.cand[i].x; gt += k > T; eq += k == T; }
-    const int n_gt = (int)block_sum_u32((unsigned)gt, sm.red), n_eq = (int)block_sum_u32((unsigned)eq, sm.red);
-    const int need = want - n_gt;                                  // ties to take: 1 <= need <= n_eq
-    for (int i = t; i < m; i += kSelThreads) {
-      const uint2 c = sm.cand[i];
-      bool take = c.x > T;
-      if (c.x == T) {
-        if (need >= n_eq) take = true;
-        else {                                                     // rank among the ties by index
-          int before = 0;
-          for (int j = 0; j < m; ++j) { const uint2 o = sm.cand[j]; before += (o.x == T && o.y < c.y); }
-          take = before < need;
-        }
-      }
-      if (take) atomicOr(&sm.bitmap[c.y >> 5], 1u << (c.y & 31));
-    }
-    __syncthreads();
-    return;
-  }
+  if (m >= want && m <= kSortCap) { select_from_list(m, want, sm, pivot); return; }
+  select_slow(src, count, want, sm);
+}
+
+// The slow exact path over the whole row; sm.bitmap zero on entry.
+template <typename Src>
+__device__ __forceinline__ void select_slow(const Src& src, int count, int want, const SelectSmem& sm) {
+  const int t = threadIdx.x, l = t & 31;
+  const int words = (count + 31) >> 5;
   // ---- slow exact path: T = the largest key with at least `want` elements >= T
   unsigned T = 0u;
   for (int bit = 30; bit >= 0; --bit) {
@@ -287,6 +308,123 @@ __global__ void __launch_bounds__(kSelThreads) qsa_topk_kernel(const __grid_cons
   if (threadIdx.x == 0) a.nsel[r] = CR_SEL_BLOCKS;
 }
 
+// Sorts the 32 values of a warp (one per lane) so that lane 0 holds the largest: a bitonic network of shuffles.
+__device__ __forceinline__ unsigned warp_sort_desc(unsigned v) {
+  const int l = threadIdx.x & 31;
+#pragma unroll
+  for (int k = 2; k <= 32; k <<= 1) {
+#pragma unroll
+    for (int j = k >> 1; j > 0; j >>= 1) {
+      const unsigned o = __shfl_xor_sync(0xffffffffu, v, j);
+      const bool down = (l & k) == 0, low_lane = (l & j) == 0;       // in a descending run the lower lane keeps the larger value
+      v = (low_lane == down) ? (v > o ? v : o) : (v < o ? v : o);
+    }
+  }
+  return v;
+}
+// Descending bitonic sort of 128 values in shared memory by one warp.
+__device__ __forceinline__ void warp_sort128_desc(unsigned* a) {
+  const int l = threadIdx.x & 31;
+  for (int k = 2; k <= 128; k <<= 1)
+    for (int j = k >> 1; j > 0; j >>= 1) {
+      __syncwarp();
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int q = l + 32 * h, i = ((q & ~(j - 1)) << 1) | (q & (j - 1));
+        const unsigned x = a[i], y = a[i + j];
+        if ((x < y) == ((i & k) == 0)) { a[i] = y; a[i + j] = x; }
+      }
+    }
+  __syncwarp();
+}
+
+// The selection of one row by a cluster of 8 CTAs, for launches of few rows (decode and verify steps), where the time
+// of one row is what counts: every CTA keeps an eighth of the row in registers (one read of the row, spread over 8
+// SMs).  Pivot: every warp sorts its threads' maxima and lists the best four, a CTA offers the 64th largest of its 128
+// listed values (64 of its elements are >= it; usually it is the CTA's 64th largest element), the cluster takes the
+// smallest offer of its CTAs (512 elements are >= it; about 600 of 65,536 unrelated scores are).  Every CTA lists
+// its elements >= the pivot in its own shared memory; CTA 0 collects the lists through distributed shared memory and
+// finishes as the single-CTA kernel does.  grid (8 x rows, spans).
+template <int PT>
+__global__ void __cluster_dims__(8, 1, 1) __launch_bounds__(kSelThreads, 1) qsa_topk_cluster_kernel(const __grid_constant__ QsaParams P, int max_count) {
+  extern __shared__ __align__(16) unsigned char raw[];
+  __shared__ unsigned offer_s, max_s, count_s;                     // read by the other CTAs of the cluster
+  __shared__ unsigned top4[128];
+  pdl_release();
+  pdl_wait();
+  cg::cluster_group cluster = cg::this_cluster();
+  const int rank = (int)cluster.block_rank();
+  const cr_qsa_args& a = P.span[blockIdx.y];
+  const int r = blockIdx.x / 8, t = threadIdx.x, l = t & 31;
+  if (r >= a.R) return;                                            // the same for the whole cluster
+  const int nb = (a.pos0 + r + 1) / 4;
+  if (nb <= CR_SEL_BLOCKS) { if (rank == 0 && t == 0) a.nsel[r] = -1; return; }
+  const SelectSmem sm = carve(raw, max_count);
+  const float* sc = a.scores + (size_t)r * a.sstride;
+  const int chunk = (((nb + 7) / 8) + kSelThreads - 1) / kSelThreads * kSelThreads;   // elements per CTA, a multiple of 1024
+  const int base = rank * chunk;
+  unsigned u[PT];
+  unsigned mine = 0u;
+#pragma unroll
+  for (int k = 0; k < PT; ++k) {
+    const int i = base + k * kSelThreads + t;
+    u[k] = (k * kSelThreads < chunk && i < nb) ? __float_as_uint(sc[i]) + 1u : 0u;
+    mine = u[k] > mine ? u[k] : mine;
+  }
+  const int words = (nb + 31) >> 5;
+  if (rank == 0) for (int i = t; i < words; i += kSelThreads) sm.bitmap[i] = 0u;
+  if (t == 0) *sm.counter = 0u;
+  const unsigned sorted = warp_sort_desc(mine);
+  if (l < 4) top4[(t >> 5) * 4 + l] = sorted;
+  __syncthreads();
+  if (t < 32) {
+    warp_sort128_desc(top4);
+    if (t == 0) { offer_s = top4[63]; max_s = top4[0]; }
+  }
+  cluster.sync();
+  unsigned pivot = 0xFFFFFFFFu, largest = 0u;
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    const unsigned x = *cluster.map_shared_rank(&offer_s, c), y = *cluster.map_shared_rank(&max_s, c);
+    pivot = x < pivot ? x : pivot;
+    largest = y > largest ? y : largest;
+  }
+  if (pivot == 0u) pivot = 1u;                                     // a CTA with fewer than 64 threads that hold an element: everything passes
+#pragma unroll
+  for (int k = 0; k < PT; ++k) {
+    const bool pass = u[k] >= pivot && u[k] != 0u;
+    const unsigned m = __ballot_sync(0xffffffffu, pass);
+    if (m) {
+      unsigned at = 0u;
+      if (l == 0) at = atomicAdd(sm.counter, (unsigned)__popc(m));
+      at = __shfl_sync(0xffffffffu, at, 0) + __popc(m & ((1u << l) - 1u));
+      if (pass && at < (unsigned)kSortCap) sm.cand[at] = make_uint2(u[k], (unsigned)(base + k * kSelThreads + t));
+    }
+  }
+  __syncthreads();
+  if (t == 0) count_s = *sm.counter;
+  cluster.sync();
+  if (rank == 0) {
+    int total = 0, first[9];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) { first[c] = total; total += (int)*cluster.map_shared_rank(&count_s, c); }
+    first[8] = total;
+    if (total <= kSortCap) {
+      for (int c = 1; c < 8; ++c) {
+        const uint2* theirs = cluster.map_shared_rank(sm.cand, c);
+        for (int i = t; i < first[c + 1] - first[c]; i += kSelThreads) sm.cand[first[c] + i] = theirs[i];
+      }
+    }
+    __syncthreads();
+    const RowSource src{sc, 0};
+    if (total >= CR_SEL_BLOCKS && total <= kSortCap) select_from_list(total, CR_SEL_BLOCKS, sm, pivot, largest);
+    else select_slow(src, nb, CR_SEL_BLOCKS, sm);
+    select_emit(src, nb, sm, a.sel + (size_t)r * CR_SEL_BLOCKS, nullptr);
+    if (t == 0) a.nsel[r] = CR_SEL_BLOCKS;
+  }
+  cluster.sync();                                                  // the lists stay until CTA 0 has copied them
+}
+
 // A rank's candidates among blocks [b0, b1): its best 512 (score, id), ascending id, unused slots -1.
 __global__ void __launch_bounds__(kSelThreads) qsa_candidates_kernel(const __grid_constant__ QsaParams P, int b0, int b1, float* cand_scores,
                                                                      int* cand_ids, int max_count) {
@@ -332,6 +470,8 @@ static cr_status select_configure() {
   return once_per_device(configured, [] {
     const int most = (int)select_smem_bytes(kMaxSelectCount);
     CR_CUDA(cudaFuncSetAttribute(qsa_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, most));
+    CR_CUDA(cudaFuncSetAttribute(qsa_topk_cluster_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, most));
+    CR_CUDA(cudaFuncSetAttribute(qsa_topk_cluster_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, most));
     CR_CUDA(cudaFuncSetAttribute(qsa_candidates_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, most));
     CR_CUDA(cudaFuncSetAttribute(qsa_merge_candidates_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, most));
     return CR_OK;
@@ -349,6 +489,12 @@ cr_status qsa_topk_launch(const cr_geometry* g, const cr_qsa_args* spans, int n_
     int nb_max = 0;
     for (int s = 0; s < n; ++s) nb_max = max(nb_max, (spans[s0 + s].pos0 + spans[s0 + s].R) / 4);
     CR_REQUIRE(nb_max <= kMaxSelectCount, "qsa select: %d blocks exceed the selectable range of %d", nb_max, kMaxSelectCount);
+    if ((long long)Rmax * n <= 64 && nb_max >= 16384) {             // few long rows: 8 SMs per row
+      if (nb_max <= 65536) CR_CUDA(launch_pdl(qsa_topk_cluster_kernel<8>, dim3(8 * Rmax, n), dim3(kSelThreads), select_smem_bytes(nb_max), stream, P, nb_max));
+      else CR_CUDA(launch_pdl(qsa_topk_cluster_kernel<32>, dim3(8 * Rmax, n), dim3(kSelThreads), select_smem_bytes(nb_max), stream, P, nb_max));
+      CR_LAUNCH_CHECK("qsa_topk_cluster_kernel");
+      continue;
+    }
     CR_CUDA(launch_pdl(qsa_topk_kernel, dim3(Rmax, n), dim3(kSelThreads), select_smem_bytes(nb_max), stream, P, nb_max));
     CR_LAUNCH_CHECK("qsa_topk_kernel");
   }
