@@ -952,7 +952,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS) + ["qsa_prefill_262k_split_kv"])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--algo", default="auto", choices=["auto", "serial", "chunk"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -981,6 +981,15 @@ def main():
         algo = capi.GDN_CHUNK_TC if capi.lib.cr_gdn_algo_available(capi.GDN_CHUNK_TC) else capi.GDN_SERIAL_F32
     if args.seq and headline == "gdn_prefill_32k":
         GdnPrefill32k.T = args.seq
+
+    if headline == "qsa_prefill_262k_split_kv":            # the strong-scaling workload alone (any number of ranks)
+        res = measure_split_kv(rank, world, dist, steps=args.steps, warmup=max(args.warmup, 3))
+        res.update(n_gpus=world, warmup=max(args.warmup, 3), higher_is_better=True, vs_baseline=None, dtype=SplitKvPrefill262k.dtype, data="synthetic")
+        if rank == 0:
+            print(json.dumps(res))
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
     def make(name):
         if name == "prefill_262k_stack" and args.parts:

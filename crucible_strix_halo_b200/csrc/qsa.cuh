@@ -20,7 +20,9 @@ __device__ __forceinline__ bool qsa_row_is_tiled(const QsaParams& P, int r) {
   return P.tile_count && P.tile_count[r / P.tile_rows] <= P.tile_max;
 }
 
-cr_status qsa_validate(const cr_geometry* g, const cr_qsa_args* spans, int n_spans, int max_rows, const char* who);
+// score_blocks >= 0: the score stride must cover that many blocks (a rank's own range, or 0 for entries that never touch
+// the scores) instead of every block of the rows.
+cr_status qsa_validate(const cr_geometry* g, const cr_qsa_args* spans, int n_spans, int max_rows, const char* who, int score_blocks = -1);
 int qsa_max_rows(const cr_qsa_args* spans, int n);
 void qsa_fill_params(QsaParams& P, const cr_geometry* g, const cr_qsa_args* spans, int n);
 cr_status qsa_prep_launch(const cr_geometry* g, const cr_qsa_args* spans, int n_spans, int u0, __half* q_hi, int q_skip,

@@ -72,11 +72,29 @@ __global__ void __launch_bounds__(128) qsa_attn_split_kernel(const __grid_consta
   const int split = blockIdx.x;
   const int p = a.pos0 + r, ns = a.nsel[r], nb = (p + 1) / 4;
   const int n = ns < 0 ? p + 1 : ns * 4 + (p + 1) % 4;
-  // tiles of 32 attended indices are dealt evenly: the first (tiles % splits) splits take one more
-  const int tiles = (n + kTile - 1) / kTile, tb = tiles / splits, trem = tiles % splits;
-  const int begin = (split * tb + min(split, trem)) * kTile, end = min(begin + (tb + (split < trem ? 1 : 0)) * kTile, n);
-  const int cnt = min(max(end - begin, 0), kMaxSplitPos);     // n <= 2051 and splits >= 4: at most 17 tiles
   const int* sel = a.sel + (size_t)r * CR_SEL_BLOCKS;
+  // Attended indices run through ascending positions (selected blocks, then the tail), so the positions inside a rank's
+  // window [p0, p1) are one contiguous range [t_lo, t_hi) of them: only that range is split and visited.
+  int t_lo = 0, t_hi = n;
+  if (p0 > 0 || p1 <= p) {
+    if (ns < 0) { t_lo = min(p0, n); t_hi = min(p1, n); }
+    else {
+      auto first_block_at_least = [&](int blk) {          // index of the first selected block >= blk
+        int lo = 0, hi = ns;
+        while (lo < hi) { const int mid = (lo + hi) >> 1; if (sel[mid] < blk) lo = mid + 1; else hi = mid; }
+        return lo;
+      };
+      t_lo = 4 * first_block_at_least((p0 + 3) / 4);
+      t_hi = 4 * first_block_at_least(p1 / 4 + (p1 % 4 ? 1 : 0));
+      if (nb * 4 >= p0 && nb * 4 < p1) t_hi = n;          // the tail tokens 4 nb .. p
+      else if (nb * 4 < p0) t_lo = t_hi;                  // a window past every attended position
+    }
+  }
+  const int n_win = max(t_hi - t_lo, 0);
+  // tiles of 32 attended indices are dealt evenly: the first (tiles % splits) splits take one more
+  const int tiles = (n_win + kTile - 1) / kTile, tb = tiles / splits, trem = tiles % splits;
+  const int begin = t_lo + (split * tb + min(split, trem)) * kTile, end = min(begin + (tb + (split < trem ? 1 : 0)) * kTile, t_hi);
+  const int cnt = min(max(end - begin, 0), kMaxSplitPos);     // n <= 2051 and splits >= 4: at most 17 tiles
 
   for (int i = t; i < cnt; i += 128) {
     int pos = qsa_position(sel, begin + i, ns, nb);
@@ -384,7 +402,7 @@ extern "C" cr_status cr_qsa_step(const cr_geometry* g, const cr_qsa_args* spans,
 extern "C" cr_status cr_qsa_shard_attn(const cr_geometry* g, const cr_qsa_args* a, int p0, int p1, float* partials, void* scratch,
                                        size_t scratch_bytes, void* stream) {
   using namespace cr;
-  if (cr_status s = qsa_validate(g, a, 1, CR_MAX_PREFILL_ROWS, "cr_qsa_shard_attn")) return s;
+  if (cr_status s = qsa_validate(g, a, 1, CR_MAX_PREFILL_ROWS, "cr_qsa_shard_attn", 0)) return s;
   CR_REQUIRE(partials && p0 >= 0 && p1 >= p0, "cr_qsa_shard_attn: bad position window or null output");
   const int splits = a->R <= CR_MAX_STEP_ROWS ? CR_QSA_SPLITS : 4;
   const size_t need = (size_t)a->R * g->q_heads * splits * CR_QSA_PART * sizeof(float);
@@ -396,7 +414,7 @@ extern "C" cr_status cr_qsa_shard_attn(const cr_geometry* g, const cr_qsa_args* 
 extern "C" cr_status cr_qsa_merge_partials(const cr_geometry* g, const cr_qsa_args* a, int ranks, const float* partials,
                                            cr_out_format fmt, void* stream) {
   using namespace cr;
-  if (cr_status s = qsa_validate(g, a, 1, CR_MAX_PREFILL_ROWS, "cr_qsa_merge_partials")) return s;
+  if (cr_status s = qsa_validate(g, a, 1, CR_MAX_PREFILL_ROWS, "cr_qsa_merge_partials", 0)) return s;
   if (cr_status s = check_out(a, 1, fmt, "cr_qsa_merge_partials")) return s;
   CR_REQUIRE(partials && ranks >= 1 && ranks <= 32, "cr_qsa_merge_partials: need gathered partials of 1..32 ranks");
   return qsa_merge_launch(g, a, 1, partials, ranks, true, nullptr, fmt, (cudaStream_t)stream);

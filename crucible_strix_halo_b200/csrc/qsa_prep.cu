@@ -139,14 +139,15 @@ __global__ void qsa_retain_raw_kernel(const __grid_constant__ QsaParams P) {
   a.c.ik_raw[raw_offset(a.c.raw_slots, a.pos0 + row, dim)] = a.idx[(size_t)row * 640 + 512 + dim];
 }
 
-cr_status qsa_validate(const cr_geometry* g, const cr_qsa_args* spans, int n_spans, int max_rows, const char* who) {
+cr_status qsa_validate(const cr_geometry* g, const cr_qsa_args* spans, int n_spans, int max_rows, const char* who, int score_blocks) {
   if (cr_status s = check_geometry(g)) return s;
   CR_REQUIRE(spans && n_spans >= 1, "%s: no spans", who);
   for (int s = 0; s < n_spans; ++s) {
     const cr_qsa_args& a = spans[s];
     CR_REQUIRE(a.R >= 1 && a.R <= max_rows, "%s: span %d has R=%d, need 1..%d", who, s, a.R, max_rows);
     CR_REQUIRE(a.pos0 >= 0, "%s: span %d has negative pos0", who, s);
-    CR_REQUIRE(a.sstride >= (a.pos0 + a.R) / 4, "%s: span %d score stride %d < %d blocks", who, s, a.sstride, (a.pos0 + a.R) / 4);
+    const int need_stride = score_blocks >= 0 ? score_blocks : (a.pos0 + a.R) / 4;   // entries that score a block range need that range only
+    CR_REQUIRE(a.sstride >= need_stride, "%s: span %d score stride %d < %d blocks", who, s, a.sstride, need_stride);
     CR_REQUIRE(a.q && a.k && a.v && a.idx && a.q_norm1 && a.k_norm1 && a.iq_norm1 && a.ik_norm1 && a.c.k && a.c.v &&
                a.c.ik_raw && a.c.ik_pool && a.sel && a.nsel && a.rope, "%s: span %d has a null buffer", who, s);
     CR_REQUIRE(a.scores || (a.pos0 + a.R) / 4 <= CR_SEL_BLOCKS, "%s: span %d needs a score buffer", who, s);
@@ -248,7 +249,7 @@ extern "C" cr_status cr_rope_table_fill_yarn(float* table, int factor, void* str
 // in the single-device reference.
 extern "C" cr_status cr_qsa_prep_queries(const cr_geometry* g, const cr_qsa_args* spans, int n_spans, void* stream) {
   using namespace cr;
-  if (cr_status s = qsa_validate(g, spans, n_spans, CR_MAX_PREFILL_ROWS, "cr_qsa_prep_queries")) return s;
+  if (cr_status s = qsa_validate(g, spans, n_spans, CR_MAX_PREFILL_ROWS, "cr_qsa_prep_queries", 0)) return s;
   return qsa_prep_launch(g, spans, n_spans, 0, nullptr, 0, (cudaStream_t)stream, true);
 }
 

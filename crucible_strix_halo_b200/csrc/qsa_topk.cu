@@ -506,7 +506,8 @@ cr_status qsa_topk_launch(const cr_geometry* g, const cr_qsa_args* spans, int n_
 extern "C" cr_status cr_qsa_shard_candidates(const cr_geometry* g, const cr_qsa_args* a, int b0, int b1, float* cand_scores,
                                              int* cand_ids, void* stream) {
   using namespace cr;
-  if (cr_status s = qsa_validate(g, a, 1, CR_MAX_PREFILL_ROWS, "cr_qsa_shard_candidates")) return s;
+  CR_REQUIRE(a && b0 >= 0 && b1 >= b0, "cr_qsa_shard_candidates: bad block range");
+  if (cr_status s = qsa_validate(g, a, 1, CR_MAX_PREFILL_ROWS, "cr_qsa_shard_candidates", (b1 < (a->pos0 + a->R) / 4 ? b1 : (a->pos0 + a->R) / 4) - b0)) return s;
   CR_REQUIRE(cand_scores && cand_ids && b0 >= 0 && b1 >= b0 && b1 - b0 <= kMaxSelectCount, "cr_qsa_shard_candidates: bad block range or null output");
   if (cr_status st = select_configure()) return st;
   QsaParams P;
@@ -521,7 +522,8 @@ extern "C" cr_status cr_qsa_shard_candidates(const cr_geometry* g, const cr_qsa_
 extern "C" cr_status cr_qsa_shard_select(const cr_geometry* g, const cr_qsa_args* a, int b0, int b1, float* cand_scores, int* cand_ids,
                                          void* stream) {
   using namespace cr;
-  if (cr_status s = qsa_validate(g, a, 1, CR_MAX_PREFILL_ROWS, "cr_qsa_shard_select")) return s;
+  CR_REQUIRE(a && b0 >= 0 && b1 >= b0, "cr_qsa_shard_select: bad block range");
+  if (cr_status s = qsa_validate(g, a, 1, CR_MAX_PREFILL_ROWS, "cr_qsa_shard_select", (b1 < (a->pos0 + a->R) / 4 ? b1 : (a->pos0 + a->R) / 4) - b0)) return s;
   CR_REQUIRE(cand_scores && cand_ids && b0 >= 0 && b1 >= b0 && b1 - b0 <= kMaxSelectCount, "cr_qsa_shard_select: bad block range or null output");
   if (cr_status s = qsa_score_launch(g, a, 1, (cudaStream_t)stream, b0, b1)) return s;
   return cr_qsa_shard_candidates(g, a, b0, b1, cand_scores, cand_ids, stream);
@@ -530,7 +532,7 @@ extern "C" cr_status cr_qsa_shard_select(const cr_geometry* g, const cr_qsa_args
 extern "C" cr_status cr_qsa_merge_candidates(const cr_geometry* g, const cr_qsa_args* a, int ranks, const float* cand_scores,
                                              const int* cand_ids, void* stream) {
   using namespace cr;
-  if (cr_status s = qsa_validate(g, a, 1, CR_MAX_PREFILL_ROWS, "cr_qsa_merge_candidates")) return s;
+  if (cr_status s = qsa_validate(g, a, 1, CR_MAX_PREFILL_ROWS, "cr_qsa_merge_candidates", 0)) return s;
   CR_REQUIRE(cand_scores && cand_ids && ranks >= 1 && ranks <= 16, "cr_qsa_merge_candidates: need 1..16 ranks and candidate buffers");
   if (cr_status st = select_configure()) return st;
   QsaParams P;

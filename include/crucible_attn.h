@@ -285,8 +285,9 @@ cr_status cr_qsa_prefill_attend(const cr_geometry* g, const cr_qsa_prefill_args*
 cr_status cr_qsa_shard_candidates(const cr_geometry* g, const cr_qsa_args* a, int b0, int b1,
                                   float* cand_scores, int* cand_ids, void* stream);
 /* The same with the scoring in front: scores of blocks [b0, b1) only (the rank reads nothing but its own part of the
- * pool; the cache pointers of a->c may be bases biased so that absolute positions index the rank's own storage), then
- * the candidates.  Scores outside [b0, b1) are left untouched. */
+ * pool; the cache pointers of a->c and a->scores may be bases biased so that absolute positions and block ids index the
+ * rank's own storage, in which case a->sstride only has to cover b1 - b0 blocks), then the candidates.  Scores outside
+ * [b0, b1) are left untouched. */
 cr_status cr_qsa_shard_select(const cr_geometry* g, const cr_qsa_args* a, int b0, int b1,
                               float* cand_scores, int* cand_ids, void* stream);
 /* Global selection from the gathered candidates of all ranks [ranks][rows][512]; writes a->sel / a->nsel. */
