@@ -385,20 +385,21 @@ class QsaPrefill262k:
 
 
 
-def drift_selections(torch, R, nb0, gen, drift=0.25):
+def drift_selections(R, nb0, seed, drift=0.25):
     """Selections that drift from row to row: a 512-block set of which every member is replaced with probability
-    `drift` per row by a block drawn uniformly from the nb0 complete blocks; ascending ids per row [R, 512] int32."""
-    cur = torch.randperm(nb0, device="cuda", generator=gen)[:512]
-    rows = []
-    for _ in range(R):
-        keep = torch.rand(512, device="cuda", generator=gen) >= drift
-        cur = torch.where(keep, cur, torch.randint(0, nb0, (512,), device="cuda", generator=gen))
-        u = torch.unique(cur)
-        while u.numel() < 512:                               # a replacement hit a member: draw again
-            u = torch.unique(torch.cat([u, torch.randint(0, nb0, (512 - u.numel(),), device="cuda", generator=gen)]))
-        cur = u[:512]
-        rows.append(cur)
-    return torch.stack(rows).int()
+    `drift` per row by a block drawn uniformly from the nb0 complete blocks; ascending ids per row, [R, 512] int32."""
+    rng = np.random.default_rng(seed)
+    cur = np.sort(rng.choice(nb0, 512, replace=False))
+    rows = np.empty((R, 512), np.int32)
+    for r in range(R):
+        keep = cur[rng.random(512) >= drift]
+        while True:                                           # refill with fresh blocks until 512 distinct ones
+            cur = np.union1d(keep, rng.integers(0, nb0, 512 - len(keep)))
+            if len(cur) == 512:
+                break
+            keep = cur
+        rows[r] = cur
+    return rows
 
 
 class QsaAttendDrift(QsaPrefill262k):
@@ -411,9 +412,8 @@ class QsaAttendDrift(QsaPrefill262k):
     def __init__(self, rank, algo):
         super().__init__(rank, algo)
         torch, capi, layers = self.torch, self.capi, self.layers
-        gen = torch.Generator(device="cuda").manual_seed(3500 + rank)
         R = self.R
-        self.ses.sel.copy_(drift_selections(torch, R, (self.POS0 + 1) // 4, gen))
+        self.ses.sel.copy_(torch.from_numpy(drift_selections(R, (self.POS0 + 1) // 4, 3500 + rank)))
         self.ses.nsel.fill_(512)
         self.plan.q_hi.copy_(self.inp["q"][:, :, :256].half())
         self.args = capi.QsaPrefillArgs(layers.qsa_args(self.w, self.ses, self.inp["q"], self.inp["k"], self.inp["v"], self.inp["idx"], self.plan.out, self.POS0),

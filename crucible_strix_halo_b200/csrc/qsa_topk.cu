@@ -382,13 +382,19 @@ __global__ void __cluster_dims__(8, 1, 1) __launch_bounds__(kSelThreads, 1) qsa_
     if (t == 0) { offer_s = top4[63]; max_s = top4[0]; }
   }
   cluster.sync();
-  unsigned pivot = 0xFFFFFFFFu, largest = 0u;
+  if (t < 8) {                                                     // eight threads fetch the offers of the eight CTAs
+    unsigned x = *cluster.map_shared_rank(&offer_s, t), y = *cluster.map_shared_rank(&max_s, t);
 #pragma unroll
-  for (int c = 0; c < 8; ++c) {
-    const unsigned x = *cluster.map_shared_rank(&offer_s, c), y = *cluster.map_shared_rank(&max_s, c);
-    pivot = x < pivot ? x : pivot;
-    largest = y > largest ? y : largest;
+    for (int o = 4; o > 0; o >>= 1) {
+      const unsigned xo = __shfl_xor_sync(0xffu, x, o), yo = __shfl_xor_sync(0xffu, y, o);
+      x = xo < x ? xo : x;
+      y = yo > y ? yo : y;
+    }
+    if (t == 0) { sm.red[0] = x; sm.red[1] = y; }
   }
+  __syncthreads();
+  unsigned pivot = sm.red[0];
+  const unsigned largest = sm.red[1];
   if (pivot == 0u) pivot = 1u;                                     // a CTA with fewer than 64 threads that hold an element: everything passes
 #pragma unroll
   for (int k = 0; k < PT; ++k) {
