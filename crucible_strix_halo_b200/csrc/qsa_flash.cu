@@ -12,7 +12,7 @@
 // length does not limit it (the reference keeps a byte per block in 64 KB of LDS and falls back to row-wise
 // attention past about 196K positions, engine/layers/qsa_union_lds.h:7-11).
 //
-// qsa_flash_tc_kernel (one CTA per (tile, KV head), 11 warps, 64 keys per step):
+// qsa_flash_tc_kernel (one CTA per (tile, KV head), 15 warps, 64 keys per step):
 //   loader warps (6)   gather the K and V rows of 16 blocks per step with 16-byte cp.async into three stages, two
 //                      warps per stage.  Both tiles land as 16-byte units at (piece * 64 + key) * 16: for K that is
 //                      the K-major operand [key][channel], for V the MN-major operand [key][channel] (channels
@@ -21,9 +21,11 @@
 //                      in tensor memory, which leaves the shared memory to the K/V stages) into one of two TMEM
 //                      accumulators, one step ahead of the softmax; O += P V (4 MMAs, N 256) once the probabilities
 //                      are written.  An event loop issues whichever is ready.
-//   softmax warps (4)  thread = TMEM lane = (row, head): reads S, applies mask and causality, keeps a running
-//                      reference maximum that moves only when a logit exceeds it by more than 2^8 (the accumulator is
-//                      rescaled in TMEM then, which is rare after the first steps), writes P as fp16 into a K-major
+//   softmax warps (8)  two warps per TMEM lane quarter, thread = (row, head) x half of the step's 64 keys: reads S,
+//                      applies mask and causality (a 32-bit visibility word per step), keeps a running reference
+//                      maximum that moves only when a logit exceeds it by more than 2^8 (the accumulator is rescaled
+//                      in TMEM then, which is rare after the first steps; the two halves agree on the row maximum
+//                      through shared memory and a 64-thread named barrier), writes P as fp16 into a K-major
 //                      shared-memory tile, sums it.
 //   epilogue           O / sum, optional un-gated context, sigmoid gate, output format.
 // q and P are fp16 with fp32 accumulation, the reference's prefill numerics (prefill_qsa_union.h:680-684).
@@ -39,8 +41,9 @@ CR_DEFINE_STATUS_WORD(qsa_flash)
 constexpr int kFlKeys = 64;                         // keys per step
 constexpr int kFlBlocks = kFlKeys / 4;              // union entries per step
 constexpr int kFlStages = 3;                        // K/V stages in flight
-constexpr int kFlThreads = 32 * (4 + 2 * kFlStages + 1);   // 4 softmax warps, 2 loader warps per stage, 1 issuer warp
-constexpr int kFlIssuer = 4 + 2 * kFlStages;
+constexpr int kFlSoftmax = 8;                       // softmax warps: two per TMEM lane quarter, 32 keys of a step each
+constexpr int kFlThreads = 32 * (kFlSoftmax + 2 * kFlStages + 1);   // + 2 loader warps per stage + 1 issuer warp
+constexpr int kFlIssuer = kFlSoftmax + 2 * kFlStages;
 constexpr int kFlKBytes = kFlKeys * 256 * 2;        // [32 channel pieces][64 keys][8 halves]
 constexpr int kFlPBytes = 128 * kFlKeys * 2;        // [8 key pieces][128 rows][8 halves]
 constexpr size_t kFlashSmem = 2 * kFlStages * kFlKBytes + 2 * kFlPBytes + 128;
@@ -156,7 +159,8 @@ __global__ void __launch_bounds__(kFlThreads, 1) qsa_flash_tc_kernel(const __gri
   unsigned char* Vs = Ks + kFlStages * kFlKBytes;        // kFlStages stages
   unsigned char* Ps = Vs + kFlStages * kFlKBytes;        // two buffers
   __shared__ __align__(8) uint64_t bars[2 * kFlStages + 4];
-  __shared__ int blk_s[kFlStages][kFlBlocks], mask_s[kFlStages][kFlBlocks];
+  __shared__ unsigned seen_s[kFlStages][16][2];          // per stage and row of the tile: which of the step's 64 keys the row sees
+  __shared__ float half_max[2][2][128];                  // [step parity][half][lane]: exchange between the two warps of a TMEM lane quarter
   __shared__ uint32_t tmem_slot;
   __shared__ volatile int dead;
   uint64_t *kvFull = &bars[0], *pvDone = &bars[kFlStages], *sFull = &bars[2 * kFlStages], *pFull = &bars[2 * kFlStages + 2];
@@ -176,7 +180,7 @@ __global__ void __launch_bounds__(kFlThreads, 1) qsa_flash_tc_kernel(const __gri
     }
     for (int i = 0; i < 2; ++i) {
       umma::mbar_init(&sFull[i], 1);
-      umma::mbar_init(&pFull[i], 4);                     // one arrival per softmax warp
+      umma::mbar_init(&pFull[i], kFlSoftmax);            // one arrival per softmax warp
     }
     umma::mbar_fence_init();
     dead = 0;
@@ -257,9 +261,9 @@ __global__ void __launch_bounds__(kFlThreads, 1) qsa_flash_tc_kernel(const __gri
         }
       }
     }
-  } else if (w >= 4) {
+  } else if (w >= kFlSoftmax) {
     // ------------------------------------------------------------------ loaders: two warps per stage
-    const int st = (w - 4) >> 1, lw = (w - 4) & 1;
+    const int st = (w - kFlSoftmax) >> 1, lw = (w - kFlSoftmax) & 1;
     const __half* kc = reinterpret_cast<const __half*>(a.c.k) + (size_t)g * 256 + (l & 1) * 8;
     const __half* vc = reinterpret_cast<const __half*>(a.c.v) + (size_t)g * 256 + (l & 1) * 8;
     const int2* lst = P.list + (size_t)tile * P.cap;
@@ -269,11 +273,23 @@ __global__ void __launch_bounds__(kFlThreads, 1) qsa_flash_tc_kernel(const __gri
     for (int j = st; j < n; j += kFlStages) {
       if (j >= kFlStages) warp_wait(&pvDone[st], ((j - kFlStages) / kFlStages) & 1);   // the MMAs of the stage's last step are done
       if (dead) break;
-      if (lw == 0 && l < kFlBlocks) {
-        const int idx = j * kFlBlocks + l;
+      if (lw == 0) {
+        // Lane b < 16 holds entry b of the step; lane r < 16 then builds the word of row r: bit 4 b + k is set when the
+        // row's bit of block b's mask is set and token k of the block is not in the row's future (only the open tail
+        // block of a row can hold such tokens).  The softmax threads read one word per step.
+        const int idx = j * kFlBlocks + (l & 15);
         const int2 e = idx < cnt ? lst[idx] : make_int2(0, 0);
-        blk_s[st][l] = e.x;
-        mask_s[st][l] = e.y;
+        const int prow = a.pos0 + row0 + (l & 15);
+        const bool rowok = (l & 15) < P.RT && row0 + (l & 15) < a.R;
+        unsigned lo_w = 0u, hi_w = 0u;
+#pragma unroll
+        for (int b = 0; b < kFlBlocks; ++b) {
+          const int blk = __shfl_sync(0xffffffffu, e.x, b), msk = __shfl_sync(0xffffffffu, e.y, b);
+          const int lim = prow - blk * 4;                             // tokens 0 .. lim of the block are visible
+          const unsigned nib = (rowok && ((msk >> (l & 15)) & 1)) ? (lim >= 3 ? 0xFu : (lim < 0 ? 0u : (2u << lim) - 1u)) : 0u;
+          if (b < 8) lo_w |= nib << (4 * b); else hi_w |= nib << (4 * (b - 8));
+        }
+        if (l < 16) { seen_s[st][l][0] = lo_w; seen_s[st][l][1] = hi_w; }
       }
       // lane l serves key 16 kg + l / 2 (kg = 0..3) and the channel pieces 2 pp + l % 2, pp = 8 lw .. 8 lw + 7
 #pragma unroll
@@ -297,51 +313,42 @@ __global__ void __launch_bounds__(kFlThreads, 1) qsa_flash_tc_kernel(const __gri
       if (l == 0) fl_mbar_arrive(&kvFull[st]);
     }
   } else {
-    // ------------------------------------------------------------------ softmax warps: thread = TMEM lane m
-    const int m = t, r = m / gqa, hq = m % gqa;
+    // ------------------------------------------------------------------ softmax warps: thread = (TMEM lane m, half of the step's keys)
+    // Warps w and w + 4 share the lanes 32 (w % 4) .. +31; warp w takes the keys 0-31 of a step, warp w + 4 the keys 32-63.
+    const int m = t & 127, hf = t >> 7, r = m / gqa, hq = m % gqa;
     const bool rowok = r < P.RT && row0 + r < a.R;
-    const int prow = a.pos0 + row0 + r;
+    const int pair_bar = 1 + (w & 3);                                   // named barrier of the two warps of a lane quarter
+    auto pair_sync = [&] { asm volatile("bar.sync %0, 64;\n" ::"r"(pair_bar) : "memory"); };
     constexpr float kScale = 0.0625f * 1.4426950408889634f;            // logits / 16, in powers of two
     float m_ref = -INFINITY, lsum = 0.f;
     for (int j = 0; j < n; ++j) {
       const int s = j & 1, st = j % kFlStages;
       warp_wait(&kvFull[st], (j / kFlStages) & 1);                     // block ids and masks of the step are visible
+      const unsigned seen = r < 16 ? seen_s[st][r][hf] : 0u;             // which of this thread's 32 keys its row sees
       warp_wait(&sFull[s], (j >> 1) & 1);
       umma::fence_after_sync();
-      float sv[kFlKeys];
-      {
-        float half_[32];
-        umma::tmem_ld32(umma::tmem_addr(tm, w, kColS + 64 * s), half_);
-#pragma unroll
-        for (int c = 0; c < 32; ++c) sv[c] = half_[c];
-        umma::tmem_ld32(umma::tmem_addr(tm, w, kColS + 64 * s + 32), half_);
-#pragma unroll
-        for (int c = 0; c < 32; ++c) sv[32 + c] = half_[c];
-      }
+      float sv[32];
+      umma::tmem_ld32(umma::tmem_addr(tm, w, kColS + 64 * s + 32 * hf), sv);
       float tmax = -INFINITY;
 #pragma unroll
-      for (int b = 0; b < kFlBlocks; ++b) {
-        const int base = blk_s[st][b] * 4;
-        const bool mine = rowok && ((mask_s[st][b] >> r) & 1);
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const int c = 4 * b + k;
-          const bool vis = mine && base + k <= prow;
-          sv[c] = vis ? sv[c] * kScale : -INFINITY;
-          tmax = fmaxf(tmax, sv[c]);
-        }
+      for (int c = 0; c < 32; ++c) {
+        sv[c] = (seen >> c) & 1u ? sv[c] * kScale : -INFINITY;
+        tmax = fmaxf(tmax, sv[c]);
       }
+      half_max[s][hf][m] = tmax;                                        // (parity: the partner may still be reading the step before)
+      pair_sync();
+      tmax = fmaxf(tmax, half_max[s][hf ^ 1][m]);                       // the row's maximum over all 64 keys of the step
       const bool move = tmax > m_ref + 8.f;                             // also the first visible key (m_ref = -inf)
       if (__any_sync(0xffffffffu, move)) {
         const float nref = move ? tmax : m_ref;
         const float factor = move ? exp2f(m_ref - nref) : 1.f;          // 0 when nothing was accumulated yet
         lsum *= factor;
         m_ref = nref;
-        if (j > 0) {                                                    // O holds the steps before this one
+        if (j > 0) {                                                    // O holds the steps before this one; each warp rescales half of it
           warp_wait(&pvDone[(j - 1) % kFlStages], ((j - 1) / kFlStages) & 1);
           umma::fence_after_sync();
 #pragma unroll 1
-          for (int c8 = 0; c8 < 8; ++c8) {
+          for (int c8 = 4 * hf; c8 < 4 * hf + 4; ++c8) {
             float o[32];
             umma::tmem_ld32(umma::tmem_addr(tm, w, kColO + 32 * c8), o);
 #pragma unroll
@@ -355,17 +362,19 @@ __global__ void __launch_bounds__(kFlThreads, 1) qsa_flash_tc_kernel(const __gri
       unsigned char* pd = Ps + s * kFlPBytes;
       float add = 0.f;
 #pragma unroll
-      for (int kc8 = 0; kc8 < kFlKeys / 8; ++kc8) {
+      for (int kc8 = 0; kc8 < 4; ++kc8) {
         unsigned pk[4];
 #pragma unroll
         for (int q2 = 0; q2 < 4; ++q2) {
-          const float s0 = sv[kc8 * 8 + 2 * q2], s1 = sv[kc8 * 8 + 2 * q2 + 1];
-          const float p0 = s0 > -INFINITY ? exp2f(s0 - m_ref) : 0.f, p1 = s1 > -INFINITY ? exp2f(s1 - m_ref) : 0.f;
+          float p0, p1;                                                // 2^(-inf) = 0: keys the row does not see drop out
+          asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p0) : "f"(sv[kc8 * 8 + 2 * q2] - m_ref));
+          asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p1) : "f"(sv[kc8 * 8 + 2 * q2 + 1] - m_ref));
+          if (m_ref == -INFINITY) p0 = p1 = 0.f;                       // -inf - -inf: nothing visible yet
           add += p0 + p1;
           const __half2 h = __floats2half2_rn(p0, p1);
           pk[q2] = *reinterpret_cast<const unsigned*>(&h);
         }
-        *reinterpret_cast<uint4*>(pd + ((size_t)kc8 * 128 + m) * 16) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        *reinterpret_cast<uint4*>(pd + ((size_t)(4 * hf + kc8) * 128 + m) * 16) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
       }
       lsum += add;
       umma::fence_async_smem();
@@ -373,7 +382,13 @@ __global__ void __launch_bounds__(kFlThreads, 1) qsa_flash_tc_kernel(const __gri
       __syncwarp();
       if (l == 0) fl_mbar_arrive(&pFull[s]);
     }
-    // ---------------------------------------------------------------- epilogue
+    // ---------------------------------------------------------------- epilogue: each warp of a pair writes half of the channels
+    float* half_sum = &half_max[n & 1][0][0];                           // the buffer the last step did not use
+    if (hf == 1) half_sum[m] = lsum;
+    pair_sync();
+    if (hf == 0) { lsum += half_sum[m]; half_sum[128 + m] = lsum; }
+    pair_sync();
+    lsum = half_sum[128 + m];
     warp_wait(&pvDone[(n - 1) % kFlStages], ((n - 1) / kFlStages) & 1);
     umma::fence_after_sync();
     const bool ok = rowok && lsum > 0.f && !dead;
@@ -382,7 +397,7 @@ __global__ void __launch_bounds__(kFlThreads, 1) qsa_flash_tc_kernel(const __gri
     const size_t W = (size_t)P.Hq * 256;
     const float* gate = a.q + ((size_t)gr * P.Hq + h) * 512 + 256;
 #pragma unroll 1
-    for (int c8 = 0; c8 < 8; ++c8) {
+    for (int c8 = 4 * hf; c8 < 4 * hf + 4; ++c8) {
       float o[32];
       umma::tmem_ld32(umma::tmem_addr(tm, w, kColO + 32 * c8), o);     // warp-collective: every lane takes part
       if (!ok) continue;
