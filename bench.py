@@ -13,7 +13,8 @@ A step is one pass of the hot path over one batch of synthetic input.  Workloads
                       (a 512-block set, every member replaced with probability 0.25 per row), as real selections overlap
   verify_131k         speculative verify: 8 sessions x 131,072 context, 9-row spans (1 certain row + 8 drafts), QSA +
                       GDN with lazy commit, replay counts uniform 0..8
-  prefill_262k_stack  long cold prefill of 262,144 tokens through a 3:1 stack of GDN:QSA layers in 2,048-row parts
+  prefill_262k_stack  long cold prefill of 262,144 tokens through a 3:1 stack of GDN:QSA layers (16,384-row launches, QSA in
+                      2,048-row parts against the growing cache)
 With no --workload the line's headline is gdn_prefill_32k and a `workloads` object carries the figures of all of them
 (shorter runs).  Under torchrun (N > 1) every rank runs the headline on its own sequence (weak scaling, no data-path
 collective) and the `workloads` object carries qsa_prefill_262k_split_kv: ONE sequence whose KV positions are split
@@ -536,85 +537,98 @@ class Verify131k:
 
 
 class PrefillStack262k:
-    """configs[3]: cold prefill of 262,144 tokens through a 3:1 stack of GDN:QSA layers (4 layers), processed in
-    2,048-row parts against the growing cache: per part three cr_gdn_prefill calls (each layer its own state, ring and
-    weights) and one cr_qsa_prefill call.  A step is the whole sequence (128 parts).  The rows of every part are the same
-    seeded 2,048-row block per layer (the positions, the caches and the states differ from part to part)."""
+    """configs[3]: cold prefill of 262,144 tokens through a 3:1 stack of GDN:QSA layers (4 layers).  The host walks the
+    sequence in launches of 16,384 rows, layer by layer, as the reference's prefill does (launches of up to 16,384 rows,
+    engine/model/flashnext/prefill_launch.h:14-34): a GDN layer takes a launch in one cr_gdn_prefill call (its internal
+    parts pipeline the chunk-local and the scan kernels), the QSA layer runs in 2,048-row parts against the growing cache
+    (cr_qsa_prefill).  A step is the whole sequence.  Every launch reuses one seeded block of projection rows per layer
+    (positions, caches and states differ from launch to launch); the indexer rows get a launch-dependent mixture so that
+    the pooled keys do not repeat along the sequence."""
     name = "prefill_262k_stack"
-    T, PART = 262144, 2048
+    T, PART, LAUNCH = 262144, 2048, 16384
     unit, metric, dtype = "tokens/s", "gdn3_qsa1_stack_prefill_tokens_per_s_at_262k", "bf16 in (GDN) / fp32 in (QSA) / fp16 kv / fp32 state"
 
-    def __init__(self, rank, algo, parts=None):
+    def __init__(self, rank, algo, launches=None):
         import torch
         from crucible_strix_halo_b200 import capi, layers
         self.torch, self.capi, self.layers = torch, capi, layers
         g = capi.GEOM_BENCH
         gen = torch.Generator(device="cuda").manual_seed(6000 + rank)
         rn = lambda *s, std=1.0, mean=0.0: torch.randn(*s, device="cuda", generator=gen) * std + mean
-        R = self.PART
-        self.parts = parts if parts is not None else list(range(self.T // R))
+        R, L = self.PART, self.LAUNCH
+        self.launches = launches if launches is not None else list(range(self.T // L))
         self.algo = algo
         self.gw = [layers.GdnWeights(g, rn(g.gdn_channels, 4, std=0.5), rn(32, std=1.5, mean=-1).clamp(-5, 1.5), rn(32, std=0.5),
                                      1 + rn(128, std=0.1)) for _ in range(3)]
         self.gses = [layers.GdnSession(g) for _ in range(3)]
-        self.gplan = [layers.GdnPrefillPlan(w, R, in_dtype=capi.IN_BF16, fmt=capi.OUT_RAW_BF16) for w in self.gw]
-        self.g_in = [(rn(R, g.gdn_channels).bfloat16(), rn(R, 4096).bfloat16(), rn(R, 64).bfloat16()) for _ in range(3)]
+        self.gplan = layers.GdnPrefillPlan(self.gw[0], L, in_dtype=capi.IN_BF16, fmt=capi.OUT_RAW_BF16)     # one workspace for the three layers
+        self.g_in = [(rn(L, g.gdn_channels).bfloat16(), rn(L, 4096).bfloat16(), rn(L, 64).bfloat16()) for _ in range(3)]
         self.qw = layers.QsaWeights(g, 1 + rn(256, std=0.1), 1 + rn(256, std=0.1), 1 + rn(128, std=0.1), 1 + rn(128, std=0.1))
         self.qses = layers.QsaSession(g, self.T, max_rows=R)
         self.qplan = layers.QsaPrefillPlan(self.qw, R, fmt=capi.OUT_RAW_BF16)
-        self.q_in = {"q": rn(R, 16, 512), "k": rn(R, 512), "v": rn(R, 512), "idx": rn(R, 640)}
+        self.q_in = {"q": rn(L, 16, 512), "k": rn(L, 512), "v": rn(L, 512), "idx": rn(L, 640)}
+        self.idx_mix = [rn(L, 640) for _ in range(3)]                       # launch l uses idx + mixtures chosen by l % 2, l % 3, l % 5
         self.q_work = {n: torch.empty_like(self.q_in[n]) for n in ("q", "idx")}
-        self.units_per_step = len(self.parts) * R
-        per_tok_gdn = GDN_BYTES_PER_TOKEN
-        att = sum(min(p * R + r + 1, 2051) for p in self.parts for r in range(0, R, 64)) * 64       # attended positions, sampled rows
-        self.alg_bytes = 3 * per_tok_gdn * self.units_per_step + att * 2048 + sum(((p + 1) * R // 4) * 512 for p in self.parts if (p + 1) * R // 4 > 512)
-        self.alg_flops = 3 * 5.4e6 * self.units_per_step + att * 4 * 16 * 256 + sum(1024 * ((p * R + r + 1) // 4) for p in self.parts for r in range(0, R, 64)) * 64
+        self.q_out = torch.empty(L, 4096, device="cuda", dtype=torch.bfloat16)
+        if len(self.launches) < self.T // L:                                # a subset of launches: the rows below them are never
+            for t in (self.qses.k, self.qses.v, self.qses.ik_pool):          # written, so the caches get seeded values instead
+                t.copy_(torch.randn(t.shape, device="cuda", generator=gen).to(t.dtype))
+        self.units_per_step = len(self.launches) * L
+        rows = [l * L + r for l in self.launches for r in range(0, L, 64)]                           # sampled rows (every 64th)
+        att = sum(min(p + 1, 2051) for p in rows) * 64
+        self.alg_bytes = 3 * GDN_BYTES_PER_TOKEN * self.units_per_step + att * 2048 + sum(((p + 1) // 4) * 512 for p in rows if (p + 1) // 4 > 512) * 64 // 2048
+        self.alg_flops = 3 * 5.4e6 * self.units_per_step + att * 4 * 16 * 256 + sum(1024 * ((p + 1) // 4) for p in rows if (p + 1) // 4 > 512) * 64
         self.kernel_bytes = {}
         self.h_g = [tuple(t.cpu().pin_memory() for t in tpl) for tpl in self.g_in]
         self.h_q = {n: t.cpu().pin_memory() for n, t in self.q_in.items()}
-        self.h_out = torch.empty(4, R, 4096, dtype=torch.bfloat16).pin_memory()
-        self.h2d = (sum(t.numel() * 2 for tpl in self.h_g for t in tpl) + sum(t.numel() * 4 for t in self.h_q.values())) * len(self.parts)
-        self.d2h = self.h_out.numel() * 2 * len(self.parts)
+        self.h_out = torch.empty(4, L, 4096, dtype=torch.bfloat16).pin_memory()
+        self.h2d = (sum(t.numel() * 2 for tpl in self.h_g for t in tpl) + sum(t.numel() * 4 for t in self.h_q.values())) * len(self.launches)
+        self.d2h = self.h_out.numel() * 2 * len(self.launches)
 
     def _reset(self):
         for s in self.gses:
             s.state.zero_(); s.hist.zero_()
 
-    def _part(self, p, e2e=False):
-        R, capi = self.PART, self.capi
-        outs = []
-        for i in range(3):
-            qkv, z, ab = self.g_in[i]
+    def _launch(self, l, e2e=False):
+        R, L, torch = self.PART, self.LAUNCH, self.torch
+        for i in range(3):                                                   # layers 0-2: Gated DeltaNet, one call per launch
             if e2e:
                 for d, h in zip(self.g_in[i], self.h_g[i]):
                     d.copy_(h, non_blocking=True)
-            outs.append(self.gplan[i].run(self.gses[i], qkv, z, ab, p * R, self.algo))
-        for n, t in self.q_in.items():
+            qkv, z, ab = self.g_in[i]
+            self.gplan.w = self.gw[i]
+            out = self.gplan.run(self.gses[i], qkv, z, ab, l * L, self.algo)
+            if e2e:
+                self.h_out[i].copy_(out, non_blocking=True)
+        for n, t in self.q_in.items():                                       # layer 3: QSA in parts of 2,048 rows
             dst = self.q_work[n] if n in self.q_work else t
             if e2e:
                 dst.copy_(self.h_q[n], non_blocking=True)
             elif n in self.q_work:
                 dst.copy_(t)
-        outs.append(self.qplan.run(self.qses, self.q_work["q"], self.q_in["k"], self.q_in["v"], self.q_work["idx"], p * R))
+        self.q_work["idx"].add_(self.idx_mix[0], alpha=0.7 * (l % 2)).add_(self.idx_mix[1], alpha=0.5 * (l % 3)).add_(self.idx_mix[2], alpha=0.4 * (l % 5))
+        for p in range(L // R):
+            sl = slice(p * R, (p + 1) * R)
+            out = self.qplan.run(self.qses, self.q_work["q"][sl], self.q_in["k"][sl], self.q_in["v"][sl], self.q_work["idx"][sl], l * L + p * R)
+            self.q_out[sl].copy_(out)
         if e2e:
-            for i, o in enumerate(outs):
-                self.h_out[i].copy_(o, non_blocking=True)
+            self.h_out[3].copy_(self.q_out, non_blocking=True)
 
     def step(self):
         self._reset()
-        for p in self.parts:
-            self._part(p)
+        for l in self.launches:
+            self._launch(l)
 
     step_eager = step
 
     def step_e2e(self):
         self._reset()
-        for p in self.parts:
-            self._part(p, e2e=True)
+        for l in self.launches:
+            self._launch(l, e2e=True)
 
     def config(self):
-        return {"workload": self.name, "seq_len": self.T, "part_rows": self.PART, "parts_run": len(self.parts), "layers": "GDN, GDN, GDN, QSA",
-                "gdn_heads": "16qk/32v x128", "qsa_heads": "16q/2kv x256", "block": 4, "top_k_blocks": 512,
+        return {"workload": self.name, "seq_len": self.T, "launch_rows": self.LAUNCH, "qsa_part_rows": self.PART, "launches_run": len(self.launches),
+                "layers": "GDN, GDN, GDN, QSA", "gdn_heads": "16qk/32v x128", "qsa_heads": "16q/2kv x256", "block": 4, "top_k_blocks": 512,
                 "selections": "i.i.d. (random indexer)", "l2": "the K/V cache (0.5 GB) and the GDN inputs exceed the 126 MB L2"}
 
 
@@ -958,7 +972,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-sub-workloads", action="store_true", help="headline only (no `workloads` object)")
     ap.add_argument("--seq", type=int, default=0, help="gdn_prefill_32k only: a shorter sequence, for profiler captures")
-    ap.add_argument("--parts", type=int, default=0, help="prefill_262k_stack only: run every n-th part, for profiler captures")
+    ap.add_argument("--parts", type=int, default=0, help="prefill_262k_stack only: run every n-th 16,384-row launch, for profiler captures")
     args = ap.parse_args()
     headline = args.workload or "gdn_prefill_32k"
     if args.impl == "reference":
@@ -993,7 +1007,7 @@ def main():
 
     def make(name):
         if name == "prefill_262k_stack" and args.parts:
-            return PrefillStack262k(rank, algo, parts=list(range(args.parts - 1, 128, args.parts)))
+            return PrefillStack262k(rank, algo, launches=list(range(args.parts - 1, 16, args.parts)))
         return WORKLOADS[name](rank, algo)
 
     wl = make(headline)

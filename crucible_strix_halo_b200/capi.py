@@ -37,6 +37,10 @@ class Options(C.Structure):
     _fields_ = [("gdn_part_chunks", C.c_int), ("pdl", C.c_int), ("qsa_score_simt", C.c_int), ("qsa_union_rows", C.c_int)]
 
 
+class Span(C.Structure):
+    _fields_ = [("ptr", P), ("bytes", C.c_size_t)]
+
+
 class GdnArgs(C.Structure):
     _fields_ = [("qkv", P), ("z", P), ("x", P), ("ab", P), ("conv", P), ("A_log", P), ("dt_bias", P),
                 ("gamma", P), ("hist", P), ("state", P), ("suh_out", P), ("out", P), ("pend", P),
@@ -108,6 +112,9 @@ _protos = {
     "cr_qsa_merge_candidates": (C.c_int, [G, C.POINTER(QsaArgs), C.c_int, P, P, P]),
     "cr_qsa_shard_attn": (C.c_int, [G, C.POINTER(QsaArgs), C.c_int, C.c_int, P, P, C.c_size_t, P]),
     "cr_qsa_merge_partials": (C.c_int, [G, C.POINTER(QsaArgs), C.c_int, P, C.c_int, P]),
+    "cr_spans_bytes": (C.c_size_t, [C.POINTER(Span), C.c_int]),
+    "cr_state_save": (C.c_int, [C.POINTER(Span), C.c_int, P, C.c_size_t, P]),
+    "cr_state_restore": (C.c_int, [C.POINTER(Span), C.c_int, P, C.c_size_t, P]),
     "cr_debug_umma_gemm": (C.c_int, [P, P, P, C.c_int, C.c_int, P, P]),
     "cr_debug_umma_f16_gemm": (C.c_int, [P, P, P, C.c_int, C.c_int, C.c_int, P, P]),
     "cr_last_error": (C.c_char_p, []),

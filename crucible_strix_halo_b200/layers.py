@@ -171,3 +171,34 @@ class QsaPrefillPlan:
                            dptr(self.scratch), self.scratch.numel())
         check(lib.cr_qsa_prefill(C.byref(self.w.g), C.byref(a), skip, self.fmt, _stream()))
         return self.out[:R]
+
+
+def checkpoint_spans(gdn_sessions, qsa_sessions, position):
+    """The spans an in-slot checkpoint at `position` holds, in the reference's order (SlotCheckpointIO::Spans,
+    engine/runtime/slot_checkpoint_io.h:14-26 over VisitFixedState, engine/model/flashnext/fixed_state.h:17-23):
+    every GDN state, then every conv ring, then every pending-row buffer, then per QSA cache its compact raw ring and
+    the 128-position pool tile that holds `position` when the position lies inside one."""
+    tensors = [s.state for s in gdn_sessions] + [s.hist for s in gdn_sessions] + [s.pend for s in gdn_sessions]
+    for s in qsa_sessions:
+        if s.raw_slots:
+            tensors.append(s.ik_raw)
+        if position % 128:
+            tensors.append(s.ik_pool[position // 128 * 4096:(position // 128 + 1) * 4096])
+    return tensors
+
+
+class SlotCheckpoint:
+    """One device buffer that holds a list of spans (SlotCheckpointIO::Buffer, slot_checkpoint_io.h:33-48), filled and
+    read back by cr_state_save / cr_state_restore."""
+
+    def __init__(self, tensors, device="cuda"):
+        self.tensors = tensors                                # keeps the views alive
+        self.spans = (capi.Span * len(tensors))(*[capi.Span(t.data_ptr(), t.numel() * t.element_size()) for t in tensors])
+        self.bytes = lib.cr_spans_bytes(self.spans, len(tensors))
+        self.buffer = torch.empty(self.bytes, device=device, dtype=torch.uint8)
+
+    def save(self):
+        check(lib.cr_state_save(self.spans, len(self.tensors), dptr(self.buffer), self.bytes, _stream()))
+
+    def restore(self):
+        check(lib.cr_state_restore(self.spans, len(self.tensors), dptr(self.buffer), self.bytes, _stream()))

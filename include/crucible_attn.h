@@ -332,6 +332,28 @@ typedef struct {
 } cr_options;
 cr_status cr_get_options(cr_options* out);
 cr_status cr_set_options(const cr_options* in);
+/* ---- state snapshot / restore --------------------------------------------------------------------------------------
+ * A span of device memory in a snapshot list.  The lists themselves (which buffers, in which order) are the host's:
+ * include/crucible_state.hpp builds them the way SequenceState::FixedSpans, SlotCheckpointIO::Spans and
+ * QsaSnapshotSpans do (engine/runtime/sequence_state.h:56-60; engine/runtime/slot_checkpoint_io.h:14-26;
+ * engine/layers/cache_storage.h:85-95). */
+typedef struct {
+  void* ptr;                     /* 16-byte aligned */
+  size_t bytes;                  /* multiple of 16 (every buffer of this path is) */
+} cr_span;
+
+/* Sum of the spans' bytes = the size of the buffer a snapshot of them needs (SlotCheckpointIO::Bytes). */
+size_t cr_spans_bytes(const cr_span* spans, int n);
+
+/* Copies the spans, in order and back to back, into `buffer` (save) or out of it (restore): the copy loops of
+ * SlotCheckpointIO::Save / Restore (engine/runtime/slot_checkpoint_io.h:49-73) and CopySnapshotSpans
+ * (engine/runtime/snapshot_bytes.h:692-704) as one kernel per 96 spans on `stream`, in order with the forwards
+ * around it.  `buffer` is device memory, or pinned host memory the device can address (a conversation snapshot).
+ * The ledger (RetainedPrefix) and the token history that belong to a checkpoint are host data and stay with the
+ * caller.  CR_ERR_INVALID if the buffer is smaller than the spans, or a span is not 16-byte aligned and sized. */
+cr_status cr_state_save(const cr_span* spans, int n, void* buffer, size_t buffer_bytes, void* stream);
+cr_status cr_state_restore(const cr_span* spans, int n, const void* buffer, size_t buffer_bytes, void* stream);
+
 /* Number of kernels this library has launched in this process (for launch accounting in benches). */
 unsigned long long cr_kernel_launches(void);
 

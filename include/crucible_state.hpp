@@ -230,6 +230,22 @@ struct SequenceState {
     }
     return v;
   }
+  // The spans of a full snapshot that holds `length` positions, in the order a conversation snapshot stores them
+  // (engine/runtime/conversation_snapshot.h:47-58): the fixed state first, then per QSA layer K rows, V rows, raw keys
+  // (the whole ring when compact) and the pool tiles up to the one that holds length - 1.
+  std::vector<DeviceSpan> SnapshotSpans(size_t length) const {
+    const size_t row = size_t(geometry.kv_heads) * CR_HEAD_DIM * 2;
+    std::vector<DeviceSpan> v = FixedSpans();
+    for (const auto& kv : qc) {
+      const cr_qsa_cache& c = kv.second;
+      if (!length) continue;
+      v.push_back({c.k, length * row});
+      v.push_back({c.v, length * row});
+      v.push_back({c.ik_raw, size_t(c.raw_slots ? c.raw_slots : length) * kQsaRawDim * sizeof(float)});
+      v.push_back({c.ik_pool, (length + 127) / 128 * 4096 * sizeof(float)});
+    }
+    return v;
+  }
   // Bytes of a full snapshot that holds `length` positions (QsaSnapshotSpans, cache_storage.h:85-95): K and V rows
   // below length, the raw keys below length (or the whole ring), pool tiles up to the one holding length - 1.
   size_t SnapshotBytes(size_t length) const {
@@ -242,5 +258,12 @@ struct SequenceState {
     return total;
   }
 };
+
+// The same list as the C ABI takes it (cr_state_save / cr_state_restore).
+inline std::vector<cr_span> AbiSpans(const std::vector<DeviceSpan>& spans) {
+  std::vector<cr_span> v;
+  for (const DeviceSpan& s : spans) v.push_back({const_cast<void*>(s.pointer), s.bytes});
+  return v;
+}
 
 }  // namespace crucible

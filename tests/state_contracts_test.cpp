@@ -148,6 +148,15 @@ static void layout_cases() {
   assert(cp.size() == 108 + 3 && cp.back().pointer == kv + 3 + 2 * 4096 && cp.back().bytes == 4096u * 4);
   assert(st.SnapshotBytes(0) == total);
   assert(st.SnapshotBytes(130) == total + 2 * (2 * 130u * 1024 + 2u * 4096 * 4) + 130u * 512 + 16u * 512);
+  // the span list of a full snapshot adds up to the same bytes, fixed state first, and converts to the ABI's spans
+  const auto snap = st.SnapshotSpans(130);
+  size_t sum = 0;
+  for (const auto& s : snap) sum += s.bytes;
+  assert(snap.size() == 108 + 8 && snap.front().pointer == cells && sum == st.SnapshotBytes(130));
+  assert(snap[108].bytes == 130u * 1024 && snap[110].bytes == 130u * 512 && snap[114].bytes == 16u * 512 && snap[115].bytes == 2u * 4096 * 4);
+  assert(st.SnapshotSpans(0).size() == 108);
+  const auto abi = AbiSpans(snap);
+  assert(abi.size() == snap.size() && abi[110].ptr == kv + 2 && abi[110].bytes == snap[110].bytes);
 }
 
 int main() {
