@@ -41,12 +41,16 @@ GDN_BYTES_PER_TOKEN = (8192 + 4096) * 2 + 4096 * 2 + 2 * 32 * 4      # bf16 qkv 
 # profiles/, per unit of work (GDN: per token of a 7,104-token part; decode: per step of 4 sessions), scaled to
 # the launch by the units it processes (traffic grows in proportion to them).
 NCU_TRAFFIC = {
-    "gdn_prefill_32k": {"gdn_chunk_scan_tc_kernel": ("token", (526.546e6 + 102.534e6) / 7104),
-                        "gdn_chunk_local_kernel": ("token", (120.665e6 + 465.678e6) / 7104),
-                        "gdn_gate_kernel": ("token", (174.630e6 + 38.259e6) / 7104)},
-    "decode_262k": {"qsa_score_kernel": ("step", 134.26e6 + 4.22e6), "qsa_attn_split_kernel": ("step", 16.88e6),
-                    "qsa_topk_cluster_kernel": ("step", 1.07e6), "qsa_merge_kernel": ("step", 2.20e6), "qsa_prep_kernel": ("step", 0.13e6),
+    "gdn_prefill_32k": {"gdn_chunk_scan_tc_kernel": ("token", (526.36e6 + 102.34e6) / 7104),
+                        "gdn_chunk_local_kernel": ("token", (121.44e6 + 464.28e6) / 7104),
+                        "gdn_gate_kernel": ("token", (174.63e6 + 37.16e6) / 7104)},
+    "decode_262k": {"qsa_score_kernel": ("step", 134.25e6 + 3.57e6), "qsa_attn_split_kernel": ("step", 16.87e6),
+                    "qsa_topk_cluster_kernel": ("step", 1.11e6), "qsa_merge_kernel": ("step", 2.21e6), "qsa_prep_kernel": ("step", 0.13e6),
                     "gdn_step_kernel": ("step", 9.47e6)},
+    "qsa_prefill_262k": {"qsa_attn_split_kernel": ("step", 6737.66e6 + 135.26e6), "qsa_score_tc_kernel": ("step", 475.9e6),
+                         "qsa_topk_kernel": ("step", 537.4e6 + 7.0e6)},
+    "qsa_attend_262k_drift": {"qsa_flash_tc_kernel": ("step", 704.4e6 + 13.6e6)},
+    "verify_131k": {"qsa_attn_split_kernel": ("step", 281.55e6 + 29.26e6), "gdn_step_kernel": ("step", 23.2e6)},
 }
 DECODE_BYTES_PER_SESSION = 65536 * 512 + 2051 * 2048 + 2 * 2097152   # pool scan + K/V gather + GDN state in/out
 

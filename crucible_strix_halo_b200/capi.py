@@ -117,6 +117,7 @@ _protos = {
     "cr_state_restore": (C.c_int, [C.POINTER(Span), C.c_int, P, C.c_size_t, P]),
     "cr_debug_umma_gemm": (C.c_int, [P, P, P, C.c_int, C.c_int, P, P]),
     "cr_debug_umma_f16_gemm": (C.c_int, [P, P, P, C.c_int, C.c_int, C.c_int, P, P]),
+    "cr_debug_umma_kv_step": (C.c_int, [P, P, C.c_int, C.c_int, C.c_int, P, P, P, P, P, P, P]),
     "cr_last_error": (C.c_char_p, []),
     "cr_version": (C.c_int, []),
     "cr_device_status": (C.c_int, []),

@@ -374,6 +374,14 @@ cr_status cr_debug_umma_gemm(const float* A, const float* B, float* D, int K, in
  * strides is the step along N (0) or along K (1); the production kernel uses the one this check confirms. */
 cr_status cr_debug_umma_f16_gemm(const uint16_t* A, const uint16_t* B, float* D, int K, int N, int variant, int* status,
                                  void* stream);
+/* The same self-check for one step of the tiled prefill attention without its softmax: the K and V rows of 16
+ * four-token blocks (ids in `blocks`, device ints) of KV head `head` are copied from fp16 caches [rows][kv_heads][256]
+ * by tensor-map (TMA) boxes into 128-byte-swizzled shared-memory tiles; S[128][64] = Q K^T (Q[128][256] from tensor
+ * memory, the K tile K-major) and O[128][256] = Pm V (Pm[128][64], the V tile MN-major).  Blocks past `rows` read as
+ * zeros.  *status: 1 = a bounded wait gave up, 2 = shared memory not aligned for the swizzle. */
+cr_status cr_debug_umma_kv_step(const uint16_t* k_cache, const uint16_t* v_cache, int kv_heads, int rows, int head,
+                                const int* blocks, const uint16_t* Q, const uint16_t* Pm, float* S, float* O,
+                                int* status, void* stream);
 /* Test hook for the bounded waits: one CTA waits up to max_us microseconds on an mbarrier that nothing will ever
  * complete (no copy, no tensor-core work pending), then sets *status (device int) to 1, raises bit 3 of the device
  * status word and returns normally.  Shows that a wait that runs out ends the kernel and leaves the context

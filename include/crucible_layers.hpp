@@ -18,6 +18,7 @@ using QsaCache = cr_qsa_cache;        // engine/layers/ops.h:407-413
 using QsaArgs = cr_qsa_args;          // engine/layers/ops.h:422-446
 using GdnPrefill = cr_gdn_prefill_args;  // engine/layers/kernels/prefill_gdn.h:12-29
 using QsaPrefill = cr_qsa_prefill_args;  // engine/layers/kernels/prefill_qsa.h:24-32
+using QsaUnion = cr_qsa_union;           // engine/layers/kernels/prefill_qsa_union.h:18-21 (list entries are (block, row mask) pairs here)
 
 constexpr int kPend = CR_PEND_FLOATS;            // engine/layers/ops.h:231
 constexpr int kSelBlocks = CR_SEL_BLOCKS;        // geometry.h:66
@@ -44,8 +45,9 @@ constexpr size_t OutProjIndex(int r, int c, int width, int pack_rows, int pack_o
   return pack_rows ? ((size_t)(c >> 4) * pack_rows + pack_off + r) * 16 + (c & 15) : (size_t)r * width + c;
 }
 
-// engine/layers/ops.h:476-493
+// engine/layers/ops.h:476-493; the YaRN tables of engine/layers/rope_tables.h by their factor (1 = plain, 2, 4)
 inline cr_status FillRopeTables(float* tables, void* stream = nullptr) { return cr_rope_table_fill(tables, stream); }
+inline cr_status FillRopeTablesYarn(float* tables, int factor, void* stream = nullptr) { return cr_rope_table_fill_yarn(tables, factor, stream); }
 
 // ---- Gated DeltaNet ----------------------------------------------------------------------------------
 // engine/layers/gdn_rows.h:26-32 (state_cache is a gfx1151 cache-policy hint and is ignored here).
@@ -100,6 +102,18 @@ inline cr_status LaunchQsaPrefillCache(const Geometry& g, const QsaArgs& q, void
 inline cr_status LaunchQsaPrefillUnion(const Geometry& g, const QsaPrefill& a, void* stream = nullptr, int skip = 0,
                                        cr_out_format fmt = CR_OUT_EXL3_WHT) {
   return cr_qsa_prefill(&g, &a, skip, fmt, stream);
+}
+
+// engine/layers/kernels/prefill_qsa_union.h:745-748 (ints of the list area for `rows` output rows) and :25-68
+inline size_t QsaUnionListInts(const Geometry& g, int rows) { return cr_qsa_union_list_ints(&g, rows); }
+inline cr_status LaunchQsaUnionBuild(const Geometry& g, const QsaArgs& a, const QsaUnion& u, void* stream = nullptr) {
+  return cr_qsa_union_build(&g, &a, &u, stream);
+}
+// Attention of a part whose cache rows, queries and selections are in place (the QsaUnionStageKernel launch of
+// LaunchQsaPrefillUnion, prefill_qsa_union.h:795-806).
+inline cr_status LaunchQsaPrefillAttend(const Geometry& g, const QsaPrefill& a, void* stream = nullptr, int skip = 0,
+                                        cr_out_format fmt = CR_OUT_EXL3_WHT) {
+  return cr_qsa_prefill_attend(&g, &a, skip, fmt, stream);
 }
 
 }  // namespace crucible

@@ -63,3 +63,33 @@ def test_bounded_wait_runs_out_and_the_context_stays_usable():
     capi.check(capi.lib.cr_device_status_clear())
     assert capi.lib.cr_device_status() == 0 and capi.lib.cr_device_check() == capi.OK
     test_umma_gemm(64, 64)                                      # the context is intact
+
+
+@pytest.mark.parametrize("kv_heads,head,rows", [(2, 1, 4096), (2, 0, 130), (1, 0, 64)])
+def test_tensor_map_tiles_feed_both_products_of_an_attention_step(kv_heads, head, rows):
+    """Sixteen 4-token blocks of a K and a V cache copied by tensor-map boxes into 128-byte-swizzled tiles: the K tile
+    read K-major gives S = Q K^T, the same kind of tile read MN-major gives O = P V; positions past the cache read as
+    zeros.  Pins the copy layout and both descriptors of the tiled prefill attention."""
+    from crucible_strix_halo_b200 import capi
+    g = torch.Generator(device="cuda").manual_seed(rows)
+    kc = torch.randn(rows, kv_heads, 256, device="cuda", generator=g).half()
+    vc = torch.randn(rows, kv_heads, 256, device="cuda", generator=g).half()
+    nb = (rows + 3) // 4
+    blocks = torch.randperm(nb, device="cuda", generator=g)[:16].sort().values.int() if nb >= 16 else torch.arange(16, device="cuda").int()
+    blocks[-1] = nb - 1                                           # the last block may hang over the end of the cache
+    if rows == 64:
+        blocks[-1] = nb + 3                                       # and one wholly past it
+    Q = torch.randn(128, 256, device="cuda", generator=g).half()
+    Pm = torch.rand(128, 64, device="cuda", generator=g).half()
+    S = torch.zeros(128, 64, device="cuda"); O = torch.zeros(128, 256, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    capi.check(capi.lib.cr_debug_umma_kv_step(kc.data_ptr(), vc.data_ptr(), kv_heads, rows, head, blocks.data_ptr(), Q.data_ptr(), Pm.data_ptr(),
+                                              S.data_ptr(), O.data_ptr(), status.data_ptr(), None))
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    pos = (blocks.long()[:, None] * 4 + torch.arange(4, device="cuda")[None]).reshape(-1)
+    live = pos < rows
+    kt = torch.zeros(64, 256, device="cuda", dtype=torch.float64); vt = torch.zeros(64, 256, device="cuda", dtype=torch.float64)
+    kt[live] = kc[pos[live], head].double(); vt[live] = vc[pos[live], head].double()
+    assert (S.double() - Q.double() @ kt.t()).abs().max().item() < 1e-3
+    assert (O.double() - Pm.double() @ vt).abs().max().item() < 1e-3
