@@ -9,7 +9,7 @@ OK, ERR_INVALID, ERR_CUDA, ERR_UNSUPPORTED, ERR_TIMEOUT = range(5)
 OUT_RAW_F32, OUT_RAW_BF16, OUT_EXL3_WHT = range(3)
 IN_F32, IN_BF16 = range(2)
 GDN_SERIAL_F32, GDN_CHUNK_TC = range(2)
-PEND_FLOATS, QSA_PART, QSA_SPLITS, SEL_BLOCKS = 258, 258, 32, 512
+PEND_FLOATS, QSA_PART, QSA_SPLITS, SEL_BLOCKS, MAX_STEP_ROWS = 258, 258, 32, 512, 13
 
 
 class CrError(RuntimeError):
