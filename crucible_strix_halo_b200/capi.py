@@ -41,6 +41,10 @@ class Span(C.Structure):
     _fields_ = [("ptr", P), ("bytes", C.c_size_t)]
 
 
+class ProjOut(C.Structure):
+    _fields_ = [("ptr", P), ("col0", C.c_int), ("cols", C.c_int), ("ld", C.c_int), ("f32", C.c_int)]
+
+
 class GdnArgs(C.Structure):
     _fields_ = [("qkv", P), ("z", P), ("x", P), ("ab", P), ("conv", P), ("A_log", P), ("dt_bias", P),
                 ("gamma", P), ("hist", P), ("state", P), ("suh_out", P), ("out", P), ("pend", P),
@@ -112,6 +116,7 @@ _protos = {
     "cr_qsa_merge_candidates": (C.c_int, [G, C.POINTER(QsaArgs), C.c_int, P, P, P]),
     "cr_qsa_shard_attn": (C.c_int, [G, C.POINTER(QsaArgs), C.c_int, C.c_int, P, P, C.c_size_t, P]),
     "cr_qsa_merge_partials": (C.c_int, [G, C.POINTER(QsaArgs), C.c_int, P, C.c_int, P]),
+    "cr_proj_gemm": (C.c_int, [P, P, C.c_int, C.c_int, C.c_int, C.POINTER(ProjOut), C.c_int, P]),
     "cr_spans_bytes": (C.c_size_t, [C.POINTER(Span), C.c_int]),
     "cr_state_save": (C.c_int, [C.POINTER(Span), C.c_int, P, C.c_size_t, P]),
     "cr_state_restore": (C.c_int, [C.POINTER(Span), C.c_int, P, C.c_size_t, P]),

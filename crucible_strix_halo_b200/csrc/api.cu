@@ -92,15 +92,15 @@ extern "C" cr_status cr_set_options(const cr_options* in) {
 
 extern "C" int cr_device_status(void) {
   return cr::gdn_scan_status_read() | (cr::qsa_score_status_read() << 1) | (cr::qsa_flash_status_read() << 2) |
-         (cr::debug_wait_status_read() << 3);
+         (cr::debug_wait_status_read() << 3) | (cr::proj_gemm_status_read() << 4);
 }
 
 extern "C" cr_status cr_device_check(void) {
   const int st = cr_device_status();
   if (st == 0) return CR_OK;
-  cr::set_error("a bounded device-side wait gave up (status word 0x%x:%s%s%s%s); the outputs of that launch are undefined",
+  cr::set_error("a bounded device-side wait gave up (status word 0x%x:%s%s%s%s%s); the outputs of that launch are undefined",
                 st, st & 1 ? " gdn_chunk_scan_tc_kernel" : "", st & 2 ? " qsa_score_tc_kernel" : "", st & 4 ? " qsa_flash_tc_kernel" : "",
-                st & 8 ? " debug_wait_kernel" : "");
+                st & 8 ? " debug_wait_kernel" : "", st & 16 ? " proj_gemm_kernel" : "");
   return CR_ERR_TIMEOUT;
 }
 
@@ -109,6 +109,7 @@ extern "C" cr_status cr_device_status_clear(void) {
   cr::qsa_score_status_clear();
   cr::qsa_flash_status_clear();
   cr::debug_wait_status_clear();
+  cr::proj_gemm_status_clear();
   CR_CUDA(cudaGetLastError());
   return CR_OK;
 }

@@ -96,6 +96,7 @@ int gdn_scan_status_read();   void gdn_scan_status_clear();
 int qsa_score_status_read();  void qsa_score_status_clear();
 int qsa_flash_status_read();  void qsa_flash_status_clear();
 int debug_wait_status_read(); void debug_wait_status_clear();
+int proj_gemm_status_read();  void proj_gemm_status_clear();
 
 // ---- device math ---------------------------------------------------------------------------------
 __device__ __forceinline__ float round_h(float v) { return __half2float(__float2half_rn(v)); }

@@ -202,3 +202,18 @@ class SlotCheckpoint:
 
     def restore(self):
         check(lib.cr_state_restore(self.spans, len(self.tensors), dptr(self.buffer), self.bytes, _stream()))
+
+
+def proj_gemm(x, w, outs):
+    """x [R, K] bf16, w [N, K] bf16 (out x in); outs: list of (tensor [R, cols] bf16 or fp32, contiguous rows) whose
+    widths add up to N.  One cr_proj_gemm launch (the input or output GEMM group of a prefill layer)."""
+    R, K = x.shape
+    N = w.shape[0]
+    arr = (capi.ProjOut * len(outs))()
+    col = 0
+    for i, o in enumerate(outs):
+        cols = o.shape[-1] if o.dim() == 2 else o[0].numel()
+        arr[i] = capi.ProjOut(o.data_ptr(), col, cols, cols, 1 if o.dtype == torch.float32 else 0)
+        col += cols
+    check(lib.cr_proj_gemm(dptr(x), dptr(w), R, K, N, arr, len(outs), _stream()))
+    return outs

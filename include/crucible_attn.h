@@ -311,7 +311,8 @@ int cr_version(void);
  * copies or tensor-core work, runs to its end, frees its tensor memory and returns: the context stays usable, the
  * outputs of that launch are undefined.  cr_device_status() synchronises the current device and returns the word
  * (0 = no wait has given up since the library was loaded or the word was cleared): bit 0 = tcgen05 GDN scan,
- * bit 1 = tcgen05 QSA scoring, bit 2 = tcgen05 QSA prefill attention, bit 3 = cr_debug_wait_timeout.
+ * bit 1 = tcgen05 QSA scoring, bit 2 = tcgen05 QSA prefill attention, bit 3 = cr_debug_wait_timeout,
+ * bit 4 = cr_proj_gemm.
  * cr_device_check() is the same read as a status code: CR_OK or CR_ERR_TIMEOUT (cr_last_error() names the kernel).
  * cr_device_status_clear() zeroes the word.  All three synchronise: call them outside stream capture, e.g. once per
  * forward pass.  No counterpart in the reference, whose waits spin without bound
@@ -332,6 +333,25 @@ typedef struct {
 } cr_options;
 cr_status cr_get_options(cr_options* out);
 cr_status cr_set_options(const cr_options* in);
+/* ---- projection GEMMs either side of the core ----------------------------------------------------------------
+ * One destination of a projection: columns [col0, col0 + cols) of the product go to ptr[row * ld + (col - col0)],
+ * as bf16 or, with f32 != 0, as fp32.  Outputs are listed in column order without gaps; cols is a multiple of 32. */
+typedef struct {
+  void* ptr;
+  int col0, cols, ld, f32;
+} cr_proj_out;
+
+/* Y[R][N] = X[R][K] W[N][K]^T, bf16 operands (X row-major, W as [out][in] row-major), fp32 accumulation on tcgen05
+ * tensor cores, the columns scattered into up to 6 outputs: the input GEMM group of a prefill layer writing the rows
+ * the core reads (GDN: qkv | z | a,b logits as bf16 for cr_gdn_prefill with CR_IN_BF16; QSA: q | k | v | idx as fp32)
+ * or the output GEMM writing hidden rows (PrefillLayer::input / ::output, engine/runtime/prefill_engine.inc:261-270,
+ * :362, for plain bf16 weights; the reference's EXL3 weight decoding is not part of this path, and its GEMM-epilogue
+ * form of the GDN q/k prep, engine/layers/kernels/prefill_gdn.h:431-492, lives in the chunk kernel of cr_gdn_prefill
+ * here).  K a multiple of 64, N >= 32.  Nothing is allocated; bit 4 of the device status word reports a bounded
+ * wait that gave up. */
+cr_status cr_proj_gemm(const void* x, const void* w, int R, int K, int N, const cr_proj_out* outs, int n_outs,
+                       void* stream);
+
 /* ---- state snapshot / restore --------------------------------------------------------------------------------------
  * A span of device memory in a snapshot list.  The lists themselves (which buffers, in which order) are the host's:
  * include/crucible_state.hpp builds them the way SequenceState::FixedSpans, SlotCheckpointIO::Spans and
