@@ -15,6 +15,7 @@ A step is one pass of the hot path over one batch of synthetic input.  Workloads
                       GDN with lazy commit, replay counts uniform 0..8
   prefill_262k_stack  long cold prefill of 262,144 tokens through a 3:1 stack of GDN:QSA layers (16,384-row launches, QSA in
                       2,048-row parts against the growing cache)
+  gdn_in_proj_32k     the input projection of a GDN layer over 32,768 tokens (hidden 2048 -> qkv | z | a,b), one GEMM launch
 With no --workload the line's headline is gdn_prefill_32k and a `workloads` object carries the figures of all of them
 (shorter runs).  Under torchrun (N > 1) every rank runs the headline on its own sequence (weak scaling, no data-path
 collective) and the `workloads` object carries qsa_prefill_262k_split_kv: ONE sequence whose KV positions are split
@@ -636,6 +637,60 @@ class PrefillStack262k:
                 "selections": "i.i.d. (random indexer)", "l2": "the K/V cache (0.5 GB) and the GDN inputs exceed the 126 MB L2"}
 
 
+class GdnInProj32k:
+    """The input projection of a GDN layer over 32,768 tokens (the caller's side of configs[1]): hidden rows
+    x [T, 2048] bf16 ~ N(0,1) times W [12,352, 2048] bf16 ~ N(0, 1/2048) -> qkv [T, 8192] | z [T, 4096] | a,b logits
+    [T, 64] as bf16 rows, the inputs cr_gdn_prefill takes.  One cr_proj_gemm launch per step."""
+    name = "gdn_in_proj_32k"
+    bound = "tensor"
+    T, K, WIDTHS = 32768, 2048, (8192, 4096, 64)
+    unit, metric, dtype = "tokens/s", "gdn_input_projection_tokens_per_s_at_32k", "bf16 operands / fp32 accumulate (tcgen05) / bf16 out"
+
+    def __init__(self, rank, algo):
+        import torch
+        from crucible_strix_halo_b200 import layers
+        self.torch, self.layers = torch, layers
+        gen = torch.Generator(device="cuda").manual_seed(7000 + rank)
+        T, K, N = self.T, self.K, sum(self.WIDTHS)
+        self.x = torch.randn(T, K, device="cuda", generator=gen).bfloat16()
+        self.w = (torch.randn(N, K, device="cuda", generator=gen) / K ** 0.5).bfloat16()
+        self.outs = [torch.empty(T, c, device="cuda", dtype=torch.bfloat16) for c in self.WIDTHS]
+        self.h_x = self.x.cpu().pin_memory()
+        self.h_out = [torch.empty(T, c, dtype=torch.bfloat16).pin_memory() for c in self.WIDTHS]
+        self.h2d, self.d2h = self.x.numel() * 2, T * N * 2
+        self.units_per_step = T
+        self.alg_flops = 2.0 * T * K * N
+        self.alg_bytes = (T * K + N * K + T * N) * 2
+        self.kernel_bytes = {}
+        # the library GEMM on the same operands, for context (not part of the step)
+        y = torch.empty(T, N, device="cuda", dtype=torch.bfloat16)
+        for _ in range(3):
+            torch.matmul(self.x, self.w.t(), out=y)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(5):
+            torch.matmul(self.x, self.w.t(), out=y)
+        e1.record()
+        torch.cuda.synchronize()
+        self.cublas_ms = e0.elapsed_time(e1) / 5
+        del y
+
+    def step(self):
+        return self.layers.proj_gemm(self.x, self.w, self.outs)
+
+    step_eager = step
+
+    def step_e2e(self):
+        self.x.copy_(self.h_x, non_blocking=True)
+        self.step()
+        for h, o in zip(self.h_out, self.outs):
+            h.copy_(o, non_blocking=True)
+
+    def config(self):
+        return {"workload": self.name, "tokens": self.T, "hidden": self.K, "columns": "qkv 8192 | z 4096 | a,b 64",
+                "library_gemm_ms_same_operands": self.cublas_ms, "l2": "x (134 MB) and the outputs (810 MB) exceed the 126 MB L2"}
+
+
 class SplitKvPrefill262k:
     """The QSA part of qsa_prefill_262k with the KV sequence split over the ranks (strong scaling: ONE sequence): rank g
     owns the cache positions of blocks [b0_g, b1_g) (its cache pointers are biased, so it stores only its share), scores
@@ -748,9 +803,11 @@ class SplitKvPrefill262k:
 
 
 WORKLOADS = {"gdn_prefill_32k": GdnPrefill32k, "decode_262k": Decode262k, "qsa_prefill_262k": QsaPrefill262k,
-             "qsa_attend_262k_drift": QsaAttendDrift, "verify_131k": Verify131k, "prefill_262k_stack": PrefillStack262k}
-SUB_WORKLOADS = ["decode_262k", "qsa_prefill_262k", "qsa_attend_262k_drift", "verify_131k", "prefill_262k_stack"]
-SUB_STEPS = {"decode_262k": (20, 5), "qsa_prefill_262k": (5, 3), "qsa_attend_262k_drift": (5, 3), "verify_131k": (20, 5), "prefill_262k_stack": (2, 1)}
+             "qsa_attend_262k_drift": QsaAttendDrift, "verify_131k": Verify131k, "prefill_262k_stack": PrefillStack262k,
+             "gdn_in_proj_32k": GdnInProj32k}
+SUB_WORKLOADS = ["decode_262k", "qsa_prefill_262k", "qsa_attend_262k_drift", "verify_131k", "prefill_262k_stack", "gdn_in_proj_32k"]
+SUB_STEPS = {"decode_262k": (20, 5), "qsa_prefill_262k": (5, 3), "qsa_attend_262k_drift": (5, 3), "verify_131k": (20, 5), "prefill_262k_stack": (2, 1),
+             "gdn_in_proj_32k": (5, 3)}
 BF16_PEAK_FALLBACK = 1590.0
 
 
@@ -820,6 +877,11 @@ def cpu_baseline(workload, seconds=6.0):
             for c in ctxs * 8:
                 row(c)
         return run(fn, 64, "64 tokens of the stack (3 x 64 GDN tokens + 64 QSA rows at contexts spread over the sequence)")
+    if workload == "gdn_in_proj_32k":
+        x, w = f32(rng.normal(size=(1024, 2048))), f32(rng.normal(size=(12352, 2048)))
+        res = run(lambda: x @ w.T, 1024, "1024 of the 32768 rows (numpy fp32 product, the host's BLAS threads)")
+        res["cores"] = len(os.sched_getaffinity(0))
+        return res
     raise ValueError(workload)
 
 
@@ -916,6 +978,11 @@ def measure(wl, steps, warmup, world, dist, sampler=None):
         tf = wl.alg_flops / (step_ms * 1e-3) / 1e12
         roof["tensor"] = {"useful_tflops": tf, "peak": tpeak, "frac": tf / tpeak, "peak_source": tpeak_kind + " (cuBLAS bf16, burst)",
                           "step_useful_flops": wl.alg_flops}
+        if getattr(wl, "bound", "hbm") == "tensor":          # a contraction: the tensor figure leads, the byte figure stays beside it
+            roof = {"bound": "tensor", "achieved": tf, "peak": tpeak, "unit": "TFLOP/s", "frac": tf / tpeak,
+                    "frac_is": "step: flops of the step / ms_per_step / peak", "peak_source": tpeak_kind + " (of measured cuBLAS bf16, burst)",
+                    "traffic": None, "step_flops": wl.alg_flops, "hbm": {k: roof[k] for k in ("achieved", "peak", "frac", "step_algorithmic_bytes")},
+                    "dominant_kernel": roof["dominant_kernel"], "kernels": roof["kernels"]}
     total_units = wl.units_per_step * world * steps
     return {"metric": wl.metric, "value": total_units / (ms * 1e-3), "unit": wl.unit, "steps": steps, "ms_per_step": step_ms,
             "dtype": wl.dtype, "config": wl.config(),
