@@ -7,6 +7,7 @@ A step is one pass of the hot path over one batch of synthetic input.  Workloads
   gdn_prefill_32k     one Gated DeltaNet layer, chunked prefill, batch 1, seq 32768, 16 QK x 128 / 32 V x 128 heads,
                       bf16 inputs, fp32 state (the headline: the config the metric is quoted on)
   decode_262k         QSA sparse attention decode + GDN recurrent update, 4 sessions x 262,144-token fp16 KV cache
+  decode_262k_x16     the same step with 16 sessions per GPU (the dependent kernels' latency amortised)
   qsa_prefill_262k    one QSA layer, the last 2,048-row part of a 262,144-token prefill (scores, top-512, attention),
                       selections from the random indexer (nearly independent per row)
   qsa_attend_262k_drift  the attention stage of the same part with injected selections that drift from row to row
@@ -332,7 +333,14 @@ class Decode262k:
     def config(self):
         return {"workload": self.name, "sessions_per_gpu": self.SESSIONS, "context": self.CTX, "qsa_heads": "16q/2kv x256",
                 "block": 4, "top_k_blocks": 512, "gdn_state": "32x128x128 fp32",
-                "l2": "per-step traffic (168 MB) exceeds the 126 MB L2"}
+                "l2": "per-step traffic (%d MB) exceeds the 126 MB L2" % (self.alg_bytes // 1000000)}
+
+
+class Decode262kX16(Decode262k):
+    """The same step with 16 sessions per GPU: the latency of the dependent kernels behind the pool scan is shared by
+    four times the bytes, which shows the HBM fraction the kernels reach once it is amortised."""
+    name = "decode_262k_x16"
+    SESSIONS = 16
 
 
 class QsaPrefill262k:
@@ -804,9 +812,9 @@ class SplitKvPrefill262k:
 
 WORKLOADS = {"gdn_prefill_32k": GdnPrefill32k, "decode_262k": Decode262k, "qsa_prefill_262k": QsaPrefill262k,
              "qsa_attend_262k_drift": QsaAttendDrift, "verify_131k": Verify131k, "prefill_262k_stack": PrefillStack262k,
-             "gdn_in_proj_32k": GdnInProj32k}
-SUB_WORKLOADS = ["decode_262k", "qsa_prefill_262k", "qsa_attend_262k_drift", "verify_131k", "prefill_262k_stack", "gdn_in_proj_32k"]
-SUB_STEPS = {"decode_262k": (20, 5), "qsa_prefill_262k": (5, 3), "qsa_attend_262k_drift": (5, 3), "verify_131k": (20, 5), "prefill_262k_stack": (2, 1),
+             "gdn_in_proj_32k": GdnInProj32k, "decode_262k_x16": Decode262kX16}
+SUB_WORKLOADS = ["decode_262k", "decode_262k_x16", "qsa_prefill_262k", "qsa_attend_262k_drift", "verify_131k", "prefill_262k_stack", "gdn_in_proj_32k"]
+SUB_STEPS = {"decode_262k": (20, 5), "decode_262k_x16": (20, 5), "qsa_prefill_262k": (5, 3), "qsa_attend_262k_drift": (5, 3), "verify_131k": (20, 5), "prefill_262k_stack": (2, 1),
              "gdn_in_proj_32k": (5, 3)}
 BF16_PEAK_FALLBACK = 1590.0
 
@@ -861,7 +869,7 @@ def cpu_baseline(workload, seconds=6.0):
         row = qsa_row(262144)
         what = "8 rows of the 2,048-row part at 262,144 context (score, top-512, attention)"
         return run(lambda: [row(262143 - i) for i in range(8)], 8, what)
-    if workload == "decode_262k":
+    if workload in ("decode_262k", "decode_262k_x16"):
         row, upd = qsa_row(262144), gdn_rows(1)
         return run(lambda: (row(), upd()), 1, "1 session-step at 262,144 context (QSA row + GDN update)")
     if workload == "verify_131k":

@@ -321,7 +321,7 @@ cr_status qsa_attn_launch(const cr_geometry* g, const cr_qsa_args* spans, int n_
           return CR_OK;
         })) return st;
     const dim3 grid(splits, Rmax * g->kv_heads, n);
-    if ((long long)grid.x * grid.y * grid.z > 1024)
+    if ((long long)grid.x * grid.y * grid.z > 600)          // more than two waves of the two-stage kernel (2 CTAs per SM)
       CR_CUDA(launch_pdl(qsa_attn_split_kernel<1>, grid, dim3(128), sizeof(SplitSmem<1>), stream, P, partials, splits, p0, p1));
     else
       CR_CUDA(launch_pdl(qsa_attn_split_kernel<2>, grid, dim3(128), sizeof(SplitSmem<2>), stream, P, partials, splits, p0, p1));
