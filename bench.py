@@ -20,7 +20,7 @@ A step is one pass of the hot path over one batch of synthetic input.  Workloads
 With no --workload the line's headline is gdn_prefill_32k and a `workloads` object carries the figures of all of them
 (shorter runs).  Under torchrun (N > 1) every rank runs the headline on its own sequence (weak scaling, no data-path
 collective) and the `workloads` object carries qsa_prefill_262k_split_kv: ONE sequence whose KV positions are split
-over the ranks, with all-gathers of candidates and partials over NCCL (strong scaling).  Time is the max over ranks.
+over the ranks, with all-to-alls of candidates and partials and all-gathers of selections and outputs over NCCL (strong scaling).  Time is the max over ranks.
 Prints ONE JSON line (rank 0).  --impl reference times the CPU restatement of the reference's algorithm
 (oracle/_build/liboracle.so) on the host cores, on a bounded sample of the same workload.
 """
@@ -701,9 +701,11 @@ class GdnInProj32k:
 
 class SplitKvPrefill262k:
     """The QSA part of qsa_prefill_262k with the KV sequence split over the ranks (strong scaling: ONE sequence): rank g
-    owns the cache positions of blocks [b0_g, b1_g) (its cache pointers are biased, so it stores only its share), scores
-    its own blocks, all-gathers 512 candidates per row, merges them into the global selection, attends its own
-    positions, all-gathers the (m, l, acc) partials and merges them (NCCL over NVLink)."""
+    owns the cache positions of blocks [b0_g, b1_g) (its cache pointers are biased, so it stores only its share) and the
+    merges of the rows [g R / N, (g + 1) R / N).  It scores its own blocks for every row, sends each rank the 512
+    candidates of that rank's rows (all-to-all), merges the candidates of its rows into the global selection, all-gathers
+    the selections, attends its own positions for every row, sends each rank the (m, l, acc) partials of that rank's rows
+    (all-to-all), merges its rows and all-gathers the output rows (NCCL over NVLink)."""
     name = "qsa_prefill_262k_split_kv"
     POS0, R = 262144 - 2048, 2048
     unit, metric, dtype = "tokens/s", "qsa_layer_prefill_tokens_per_s_at_262k_split_kv", "fp16 kv / fp32 q"
@@ -742,14 +744,28 @@ class SplitKvPrefill262k:
                                  capi.dptr(self.w.q_norm1), capi.dptr(self.w.k_norm1), capi.dptr(self.w.iq_norm1), capi.dptr(self.w.ik_norm1),
                                  cache, self.scores.data_ptr() - b0 * 4, score_stride, capi.dptr(self.sel), capi.dptr(self.nsel), None,
                                  capi.dptr(self.out), self.POS0, R, None, 0, 0, None, capi.dptr(self.w.rope))
+        assert R % world == 0, "the part's rows are dealt evenly to the ranks"
+        Rr = self.Rr = R // world
+        r0 = self.r0 = rank * Rr
         self.cs = torch.empty(R, 512, device="cuda"); self.ci = torch.empty(R, 512, device="cuda", dtype=torch.int32)
-        self.all_cs = torch.empty(world, R, 512, device="cuda"); self.all_ci = torch.empty(world, R, 512, device="cuda", dtype=torch.int32)
-        self.part = torch.empty(R, 16, 258, device="cuda"); self.all_part = torch.empty(world, R, 16, 258, device="cuda")
+        self.my_cs = torch.empty(world, Rr, 512, device="cuda"); self.my_ci = torch.empty(world, Rr, 512, device="cuda", dtype=torch.int32)
+        self.sel_mine = torch.zeros(Rr, 512, device="cuda", dtype=torch.int32); self.nsel_mine = torch.zeros(Rr, device="cuda", dtype=torch.int32)
+        self.part = torch.empty(R, 16, 258, device="cuda"); self.my_part = torch.empty(world, Rr, 16, 258, device="cuda")
+        self.out_mine = torch.empty(Rr, 4096, device="cuda", dtype=torch.bfloat16)
         self.scratch = torch.empty(R * 16 * 4 * 258 * 4, dtype=torch.uint8, device="cuda")
+        # the argument block of this rank's rows: same buffers, row pointers moved to row r0, selections and outputs of its own
+        mine = capi.QsaArgs.from_buffer_copy(self.args)
+        mine.q += r0 * 16 * 512 * 4; mine.idx += r0 * 640 * 4; mine.k += r0 * 512 * 4; mine.v += r0 * 512 * 4
+        mine.scores += r0 * score_stride * 4
+        mine.sel, mine.nsel, mine.out = self.sel_mine.data_ptr(), self.nsel_mine.data_ptr(), self.out_mine.data_ptr()
+        mine.pos0 += r0; mine.R = Rr
+        self.args_mine = mine
         self.units_per_step = R
-        self.wire_bytes = (world - 1) * (self.cs.numel() * 4 + self.ci.numel() * 4 + self.part.numel() * 4)   # received per rank per part
-        self.ev = [torch.cuda.Event(enable_timing=True) for _ in range(6)]
-        self.coll_ms = [0.0, 0.0]
+        f = (world - 1) / world                                              # share of a buffer that crosses the wire
+        self.wire_bytes = int(f * (self.cs.numel() * 8 + self.sel.numel() * 4 + self.nsel.numel() * 4 + self.part.numel() * 4 + self.out.numel() * 2))
+        self.ev = [torch.cuda.Event(enable_timing=True) for _ in range(9)]
+        self.stage_ms = [0.0, 0.0, 0.0, 0.0]
+        self.coll_ms = [0.0, 0.0, 0.0, 0.0]
         self.h_in = {n: t.cpu().pin_memory() for n, t in self.inp.items()}
         self.h_out = torch.empty(R, 4096, dtype=torch.bfloat16).pin_memory()
         self.h2d, self.d2h = sum(t.numel() * 4 for t in self.h_in.values()), self.h_out.numel() * 2
@@ -764,24 +780,38 @@ class SplitKvPrefill262k:
         st = C.c_void_p(self.torch.cuda.current_stream().cuda_stream)
         arr = (capi.QsaArgs * 1)(self.args)
         # the cache rows of the part belong to the last rank's positions and are part of the synthetic cache here
+        if timed: self.ev[8].record()
         self._prep()
+        mine = (capi.QsaArgs * 1)(self.args_mine)
         capi.check(capi.lib.cr_qsa_shard_select(C.byref(g), arr, self.b0, self.b1, self.cs.data_ptr(), self.ci.data_ptr(), st))
         if timed: self.ev[0].record()
         if self.world > 1:
-            dist.all_gather_into_tensor(self.all_cs, self.cs); dist.all_gather_into_tensor(self.all_ci, self.ci)
+            dist.all_to_all_single(self.my_cs.view(-1, 512), self.cs); dist.all_to_all_single(self.my_ci.view(-1, 512), self.ci)
         else:
-            self.all_cs.copy_(self.cs.unsqueeze(0)); self.all_ci.copy_(self.ci.unsqueeze(0))
+            self.my_cs.copy_(self.cs.unsqueeze(0)); self.my_ci.copy_(self.ci.unsqueeze(0))
         if timed: self.ev[1].record()
-        capi.check(capi.lib.cr_qsa_merge_candidates(C.byref(g), arr, self.world, self.all_cs.data_ptr(), self.all_ci.data_ptr(), st))
-        capi.check(capi.lib.cr_qsa_shard_attn(C.byref(g), arr, self.p0, self.p1 if self.rank < self.world - 1 else 2 ** 31 - 1,
-                                              self.part.data_ptr(), self.scratch.data_ptr(), self.scratch.numel(), st))
+        capi.check(capi.lib.cr_qsa_merge_candidates(C.byref(g), mine, self.world, self.my_cs.data_ptr(), self.my_ci.data_ptr(), st))
         if timed: self.ev[2].record()
         if self.world > 1:
-            dist.all_gather_into_tensor(self.all_part, self.part)
+            dist.all_gather_into_tensor(self.sel, self.sel_mine); dist.all_gather_into_tensor(self.nsel, self.nsel_mine)
         else:
-            self.all_part.copy_(self.part.unsqueeze(0))
+            self.sel.copy_(self.sel_mine); self.nsel.copy_(self.nsel_mine)
         if timed: self.ev[3].record()
-        capi.check(capi.lib.cr_qsa_merge_partials(C.byref(g), arr, self.world, self.all_part.data_ptr(), capi.OUT_RAW_BF16, st))
+        capi.check(capi.lib.cr_qsa_shard_attn(C.byref(g), arr, self.p0, self.p1 if self.rank < self.world - 1 else 2 ** 31 - 1,
+                                              self.part.data_ptr(), self.scratch.data_ptr(), self.scratch.numel(), st))
+        if timed: self.ev[4].record()
+        if self.world > 1:
+            dist.all_to_all_single(self.my_part.view(-1, 16, 258), self.part)
+        else:
+            self.my_part.copy_(self.part.unsqueeze(0))
+        if timed: self.ev[5].record()
+        capi.check(capi.lib.cr_qsa_merge_partials(C.byref(g), mine, self.world, self.my_part.data_ptr(), capi.OUT_RAW_BF16, st))
+        if timed: self.ev[6].record()
+        if self.world > 1:
+            dist.all_gather_into_tensor(self.out, self.out_mine)
+        else:
+            self.out.copy_(self.out_mine)
+        if timed: self.ev[7].record()
         return self.out
 
     def _fresh(self):
@@ -796,7 +826,9 @@ class SplitKvPrefill262k:
         self._fresh()
         out = self._run(timed=True)
         self.torch.cuda.synchronize()
-        self.coll_ms[0] += self.ev[0].elapsed_time(self.ev[1]); self.coll_ms[1] += self.ev[2].elapsed_time(self.ev[3])
+        for i in range(4):
+            self.coll_ms[i] += self.ev[2 * i].elapsed_time(self.ev[2 * i + 1])
+            self.stage_ms[i] += (self.ev[8] if i == 0 else self.ev[2 * i - 1]).elapsed_time(self.ev[2 * i])
         return out
 
     def step_e2e(self):
@@ -806,7 +838,7 @@ class SplitKvPrefill262k:
 
     def config(self):
         return {"workload": self.name, "context": self.POS0 + self.R, "part_rows": self.R, "ranks": self.world,
-                "split": "KV positions by whole blocks, the newest rows on the last rank", "collectives": "all-gather of candidates, all-gather of partials (NCCL)",
+                "split": "KV positions by whole blocks, the newest rows on the last rank", "collectives": "all-to-all of candidates, all-gather of selections, all-to-all of partials, all-gather of output rows (NCCL)",
                 "wire_bytes_received_per_rank_per_part": self.wire_bytes}
 
 
@@ -1027,13 +1059,16 @@ def measure_split_kv(rank, world, dist, steps=5, warmup=3):
         res[name] = float(ms.item()) / steps
     for _ in range(steps):
         wl.step_timed()
-    coll = torch.tensor(wl.coll_ms, device="cuda") / steps
+    coll = torch.tensor(wl.coll_ms + wl.stage_ms, device="cuda") / steps
     if world > 1:
         dist.all_reduce(coll, op=dist.ReduceOp.MAX)
     out = {"metric": wl.metric, "value": wl.R / (res["device"] * 1e-3), "unit": wl.unit, "ms_per_step": res["device"], "scaling": "strong",
            "steps": steps, "config": wl.config(),
            "e2e": {"value": wl.R / (res["e2e"] * 1e-3), "unit": wl.unit, "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h, "ms_per_step": res["e2e"]},
-           "collectives_ms_per_step": {"all_gather_candidates": float(coll[0]), "all_gather_partials": float(coll[1])},
+           "collectives_ms_per_step": {"all_to_all_candidates": float(coll[0]), "all_gather_selections": float(coll[1]),
+                                       "all_to_all_partials": float(coll[2]), "all_gather_outputs": float(coll[3])},
+           "stages_ms_per_step": {"prep_and_shard_select": float(coll[4]), "merge_candidates": float(coll[5]), "shard_attn": float(coll[6]),
+                                  "merge_partials": float(coll[7])},
            "wire_bytes_received_per_rank_per_step": wl.wire_bytes}
     del wl
     torch.cuda.empty_cache()

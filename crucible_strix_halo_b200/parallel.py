@@ -4,10 +4,15 @@ Natural shards need no exchange: sessions (decode / verify) and sequences (prefi
 heads are independent recurrences (GdnHeadShard).  One long sequence of the QSA layer is split over the KV positions:
 
     rank g owns positions [lo_g, hi_g)  (whole 4-token blocks; the newest rows belong to the last rank)
-    1. local scores + top-512 candidates over the owned blocks          cr_qsa_shard_select
-    2. all-gather candidates [ranks][rows][512] (score, id)             -> every rank: cr_qsa_merge_candidates
-    3. attention over the owned part of the attended positions          cr_qsa_shard_attn -> (m, l, acc[256])
-    4. all-gather partials [ranks][rows][heads][258]                    -> cr_qsa_merge_partials (LSE merge + gate)
+    and the merges of the rows [g R / W, (g + 1) R / W) of the part
+    1. local scores + top-512 candidates over the owned blocks, all rows    cr_qsa_shard_select
+    2. candidates of rows r go to the owner of r (all-to-all)               -> owner: cr_qsa_merge_candidates
+    3. all-gather of the selections [rows][512]
+    4. attention over the owned part of the attended positions, all rows    cr_qsa_shard_attn -> (m, l, acc[256])
+    5. partials of rows r go to the owner of r (all-to-all)                 -> owner: cr_qsa_merge_partials (LSE merge + gate)
+    6. all-gather of the output rows
+Per rank and part (2,048 rows, 16 heads) that is (W - 1) / W x (8 + 4 + 34 + 17) MB on the wire instead of
+(W - 1) x 42 MB when every rank gathers and merges everything (the form kept for row counts W does not divide).
 
 The record formats are the reference's own split-KV formats (engine/layers/qsa_long.h:228-234, :442-474), which is
 what makes the single-device merge kernels reusable across devices.  The compute steps go through a backend
@@ -71,9 +76,13 @@ class GdnHeadShard:
 
 class SplitKvQsa:
     """Runs the selection and attention of one QSA part (rows already prepared, caches holding the part) across the
-    ranks of `group`.  backend: object with shard_candidates(b0, b1) -> (scores [R,512] f32, ids [R,512] i32),
-    merge_candidates(all_scores [W,R,512], all_ids), shard_attn(p0, p1) -> partials [R,Hq,258],
-    merge_partials(all_partials [W,R,Hq,258]) -> output; tensors are torch tensors on the backend's device."""
+    ranks of `group`.  backend: object with `rows` and
+        shard_candidates(b0, b1)                  -> (scores [R,512] f32, ids [R,512] i32) over the rank's own blocks
+        merge_candidates(scores [W,n,512], ids, r0, r1) -> (sel [n,512] i32, nsel [n] i32) of the rows [r0, r1)
+        set_selection(sel [R,512], nsel [R])      the global selection every rank attends with
+        shard_attn(p0, p1)                        -> partials [R,Hq,258] over the rank's own positions
+        merge_partials(parts [W,n,Hq,258], r0, r1) -> output rows [n, ...] of the rows [r0, r1)
+    tensors are torch tensors on the backend's device."""
 
     def __init__(self, backend, group=None):
         import torch.distributed as dist
@@ -89,39 +98,81 @@ class SplitKvQsa:
         self.dist.all_gather(list(out.unbind(0)), t.contiguous(), group=self.group)   # rank-major [W, ...]
         return out
 
+    def _rows_to_owners(self, t, r0, r1):
+        """t [R, ...] on every rank -> [W, r1 - r0, ...]: what every rank holds for this rank's rows.  An all-to-all
+        where the backend has one (NCCL); elsewhere an all-gather of which the own rows are kept."""
+        import torch
+        if self.world == 1:
+            return t.unsqueeze(0)
+        if t.is_cuda:
+            out = torch.empty((self.world, r1 - r0) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
+            self.dist.all_to_all_single(out.view((-1,) + tuple(t.shape[1:])), t.contiguous(), group=self.group)
+            return out
+        return self._all_gather(t)[:, r0:r1].contiguous()
+
     def run(self, total_positions):
-        """total_positions = pos0 + R (positions in the cache after this part).  Returns the gated output rows."""
-        (b0, b1), (p0, p1) = kv_block_range(total_positions, self.world, self.rank)
-        cs, ci = self.backend.shard_candidates(b0, b1)
-        self.backend.merge_candidates(self._all_gather(cs), self._all_gather(ci))
-        parts = self.backend.shard_attn(p0, p1)
-        return self.backend.merge_partials(self._all_gather(parts))
+        """total_positions = pos0 + R (positions in the cache after this part).  Returns the gated output rows [R, ...]."""
+        b, W = self.backend, self.world
+        (b0, b1), (p0, p1) = kv_block_range(total_positions, W, self.rank)
+        cs, ci = b.shard_candidates(b0, b1)
+        R = b.rows
+        if R % W == 0:                                        # every rank merges its own rows
+            r0, r1 = shard_range(R, W, self.rank)
+            sel, nsel = b.merge_candidates(self._rows_to_owners(cs, r0, r1), self._rows_to_owners(ci, r0, r1), r0, r1)
+            b.set_selection(self._all_gather(sel).reshape(R, -1), self._all_gather(nsel).reshape(R))
+            out = b.merge_partials(self._rows_to_owners(b.shard_attn(p0, p1), r0, r1), r0, r1)
+            return self._all_gather(out).reshape((R,) + tuple(out.shape[1:]))
+        sel, nsel = b.merge_candidates(self._all_gather(cs), self._all_gather(ci), 0, R)      # every rank merges every row
+        b.set_selection(sel, nsel)
+        return b.merge_partials(self._all_gather(b.shard_attn(p0, p1)), 0, R)
 
 
 def run_emulated_ranks(backend, world, total_positions):
     """The exchange of SplitKvQsa.run with the ranks played one after the other by ONE process on one device (tests and
-    single-GPU checks): every rank's candidates, one merge, every rank's partials, one merge."""
+    single-GPU checks): every rank's candidates, the merges of every rank's rows, every rank's partials, the merges of
+    every rank's rows."""
     import torch
+    R = backend.rows
     ranges = [kv_block_range(total_positions, world, r) for r in range(world)]
+    rows = [shard_range(R, world, r) for r in range(world)]
     cands = [backend.shard_candidates(b0, b1) for (b0, b1), _ in ranges]
-    backend.merge_candidates(torch.stack([c[0] for c in cands]), torch.stack([c[1] for c in cands]))
-    parts = [backend.shard_attn(p0, p1).clone() for _, (p0, p1) in ranges]
-    return backend.merge_partials(torch.stack(parts))
+    cs, ci = torch.stack([c[0] for c in cands]), torch.stack([c[1] for c in cands])
+    merged = [backend.merge_candidates(cs[:, r0:r1].contiguous(), ci[:, r0:r1].contiguous(), r0, r1) for r0, r1 in rows if r1 > r0]
+    backend.set_selection(torch.cat([m[0] for m in merged]), torch.cat([m[1] for m in merged]))
+    parts = torch.stack([backend.shard_attn(p0, p1).clone() for _, (p0, p1) in ranges])
+    return torch.cat([backend.merge_partials(parts[:, r0:r1].contiguous(), r0, r1).clone() for r0, r1 in rows if r1 > r0])
 
 
 class CudaQsaBackend:
-    """The C-ABI calls behind SplitKvQsa for one prepared part: `args` is the cr_qsa_args of the part (scores
-    already computed for the owned blocks by cr_qsa_select or cr_qsa_prefill's score stage)."""
+    """The C-ABI calls behind SplitKvQsa for one prepared part: `args` is the cr_qsa_args of the part (queries
+    normalised, caches holding the part); `out` [rows, Hq * 256] receives the output rows."""
 
     def __init__(self, geometry, args, rows, fmt, out):
         import torch
         from . import capi
         self.capi, self.torch, self.g, self.rows, self.fmt, self.out = capi, torch, geometry, rows, fmt, out
+        self.args = args
         self.arr = (capi.QsaArgs * 1)(args)
         self.scratch = torch.empty(rows * geometry.q_heads * 32 * 258 * 4, dtype=torch.uint8, device="cuda")
+        self.sel = torch.zeros(rows, 512, device="cuda", dtype=torch.int32)        # the part's selection, wherever it was merged
+        self.nsel = torch.zeros(rows, device="cuda", dtype=torch.int32)
 
     def _stream(self):
         return C.c_void_p(self.torch.cuda.current_stream().cuda_stream)
+
+    def _rows_args(self, r0, r1):
+        """The argument block of the rows [r0, r1): the same buffers, row pointers moved to row r0."""
+        capi, g = self.capi, self.g
+        a = capi.QsaArgs.from_buffer_copy(self.args)
+        esz = self.out.element_size()
+        a.q += r0 * g.q_heads * 512 * 4; a.idx += r0 * 640 * 4
+        a.k += r0 * g.kv_heads * 256 * 4; a.v += r0 * g.kv_heads * 256 * 4
+        if a.scores:
+            a.scores += r0 * a.sstride * 4
+        a.sel, a.nsel = self.sel.data_ptr() + r0 * 512 * 4, self.nsel.data_ptr() + r0 * 4
+        a.out = self.out.data_ptr() + r0 * g.q_heads * 256 * esz
+        a.pos0 += r0; a.R = r1 - r0
+        return (capi.QsaArgs * 1)(a)
 
     def shard_candidates(self, b0, b1):
         """Scores of the rank's own blocks [b0, b1), then its best 512 per row."""
@@ -130,9 +181,20 @@ class CudaQsaBackend:
         self.capi.check(self.capi.lib.cr_qsa_shard_select(C.byref(self.g), self.arr, b0, b1, cs.data_ptr(), ci.data_ptr(), self._stream()))
         return cs, ci
 
-    def merge_candidates(self, all_scores, all_ids):
-        self.capi.check(self.capi.lib.cr_qsa_merge_candidates(C.byref(self.g), self.arr, all_scores.shape[0], all_scores.data_ptr(),
-                                                                all_ids.data_ptr(), self._stream()))
+    def merge_candidates(self, scores, ids, r0, r1):
+        self.capi.check(self.capi.lib.cr_qsa_merge_candidates(C.byref(self.g), self._rows_args(r0, r1), scores.shape[0], scores.data_ptr(),
+                                                                ids.data_ptr(), self._stream()))
+        return self.sel[r0:r1], self.nsel[r0:r1]
+
+    def set_selection(self, sel, nsel):
+        """The global selection into the buffers the part's argument block names."""
+        capi, t = self.capi, self.torch
+        if sel.data_ptr() != self.sel.data_ptr():
+            self.sel.copy_(sel); self.nsel.copy_(nsel)
+        a = capi.QsaArgs.from_buffer_copy(self.args)
+        a.sel, a.nsel = self.sel.data_ptr(), self.nsel.data_ptr()
+        self.args = a
+        self.arr = (capi.QsaArgs * 1)(a)
 
     def shard_attn(self, p0, p1):
         parts = self.torch.empty(self.rows, self.g.q_heads, 258, device="cuda")
@@ -140,7 +202,7 @@ class CudaQsaBackend:
                                                           self.scratch.data_ptr(), self.scratch.numel(), self._stream()))
         return parts
 
-    def merge_partials(self, all_parts):
-        self.capi.check(self.capi.lib.cr_qsa_merge_partials(C.byref(self.g), self.arr, all_parts.shape[0], all_parts.data_ptr(), self.fmt,
+    def merge_partials(self, parts, r0, r1):
+        self.capi.check(self.capi.lib.cr_qsa_merge_partials(C.byref(self.g), self._rows_args(r0, r1), parts.shape[0], parts.data_ptr(), self.fmt,
                                                               self._stream()))
-        return self.out
+        return self.out[r0:r1]

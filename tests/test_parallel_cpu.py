@@ -46,16 +46,23 @@ class OracleBackend:
             cs[r, :len(order)] = sc[order]; ci[r, :len(order)] = order + b0
         return torch.from_numpy(cs), torch.from_numpy(ci)
 
-    def merge_candidates(self, all_scores, all_ids):
-        s, i = all_scores.numpy(), all_ids.numpy()
-        for r in range(self.R):
+    rows = property(lambda self: self.R)
+
+    def merge_candidates(self, scores, ids, r0, r1):
+        s, i = scores.numpy(), ids.numpy()
+        sel = np.zeros((r1 - r0, 512), np.int32); nsel = np.full(r1 - r0, -1, np.int32)
+        for r in range(r0, r1):
             if (self.pos0 + r + 1) // 4 <= 512:
                 continue
-            sc, ids = s[:, r].ravel(), i[:, r].ravel()
-            keep = ids >= 0
-            sc, ids = sc[keep], ids[keep]
-            order = np.lexsort((ids, -sc.astype(np.float64)))[:512]
-            self.sel[r] = np.sort(ids[order]).astype(np.int32)
+            sc, idv = s[:, r - r0].ravel(), i[:, r - r0].ravel()
+            keep = idv >= 0
+            sc, idv = sc[keep], idv[keep]
+            order = np.lexsort((idv, -sc.astype(np.float64)))[:512]
+            sel[r - r0], nsel[r - r0] = np.sort(idv[order]), 512
+        return torch.from_numpy(sel), torch.from_numpy(nsel)
+
+    def set_selection(self, sel, nsel):
+        self.sel = [sel[r].numpy().astype(np.int32) if int(nsel[r]) > 0 else None for r in range(self.R)]
 
     def shard_attn(self, p0, p1):
         g = self.g
@@ -73,19 +80,19 @@ class OracleBackend:
                 out[r, h, 0], out[r, h, 1], out[r, h, 2:] = m, e.sum(), e @ V[:, h // g.gqa]
         return torch.from_numpy(out)
 
-    def merge_partials(self, all_parts):
-        p = all_parts.numpy().astype(np.float64)
-        out = np.zeros((self.R, self.g.q_heads, 256))
-        for r in range(self.R):
+    def merge_partials(self, parts, r0, r1):
+        p = parts.numpy().astype(np.float64)
+        out = np.zeros((r1 - r0, self.g.q_heads, 256))
+        for r in range(r1 - r0):
             for h in range(self.g.q_heads):
                 out[r, h] = ao.lse_merge([(p[w, r, h, 0], p[w, r, h, 1], p[w, r, h, 2:]) for w in range(p.shape[0])])
-        return out * ao.sigmoid(self.gate)
+        return torch.from_numpy(out * ao.sigmoid(self.gate[r0:r1]))
 
 
-def _problem():
+def _problem(R=6):
     g = ao.Geometry(q_heads=16, kv_heads=2)
     rng = np.random.default_rng(0)
-    ctx0, R = 2110, 6
+    ctx0 = 2110
     cache = ao.QsaCache(g, ctx0 + R)
     norms = [1 + 0.1 * rng.normal(size=s) for s in (256, 256, 128, 128)]
     ao.qsa_prep(rng.normal(size=(ctx0, 16, 512)), rng.normal(size=(ctx0, 512)), rng.normal(size=(ctx0, 512)), rng.normal(size=(ctx0, 640)),
@@ -94,31 +101,32 @@ def _problem():
     return g, cache, norms, rows, ctx0, R
 
 
-def _worker(rank, world, port, q):
+def _worker(rank, world, port, q, R):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
-    g, cache, norms, rows, ctx0, R = _problem()
+    g, cache, norms, rows, ctx0, R = _problem(R)
     qn, gate, iq = ao.qsa_prep(*rows, *norms, cache, ctx0, g)
     out = par.SplitKvQsa(OracleBackend(g, cache, qn, gate, iq, ctx0)).run(ctx0 + R)
     if rank == 0:
-        q.put(out)
+        q.put(out.numpy())
     dist.barrier()
     dist.destroy_process_group()
 
 
-def test_split_kv_two_ranks_equals_single_rank():
+@pytest.mark.parametrize("R", [6, 5])         # rows the ranks divide (every rank merges its own rows) and rows they do not
+def test_split_kv_two_ranks_equals_single_rank(R):
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q, R)) for r in range(2)]
     for p in procs:
         p.start()
     out = q.get(timeout=120)
     for p in procs:
         p.join(timeout=60)
         assert p.exitcode == 0
-    g, cache, norms, rows, ctx0, R = _problem()
+    g, cache, norms, rows, ctx0, R = _problem(R)
     ref = ao.qsa_rows(*rows, norms, cache, ctx0, g)
     np.testing.assert_allclose(out.reshape(R, -1), ref, rtol=1e-6, atol=1e-7)
 

@@ -461,9 +461,9 @@ def test_split_kv_emulated_ranks_match_the_single_device_path(world, pos0, R):
     backend = par.CudaQsaBackend(g, args, R, capi.OUT_RAW_F32, out)
     got = par.run_emulated_ranks(backend, world, pos0 + R).cpu().numpy()
     torch.cuda.synchronize()
-    np.testing.assert_array_equal(ses.nsel.cpu().numpy(), nsel_single)
+    np.testing.assert_array_equal(backend.nsel.cpu().numpy(), nsel_single)        # merged rank by rank over each rank's rows
     sparse = nsel_single > 0
-    np.testing.assert_array_equal(ses.sel.cpu().numpy()[sparse], sel_single[sparse])
+    np.testing.assert_array_equal(backend.sel.cpu().numpy()[sparse], sel_single[sparse])
     assert_close_attn(got, single, max_abs=2e-4, cos=0.999999, what="sharded vs single device")
     for o, r in enumerate(sample):
         if sels[o] is not None and not np.array_equal(sel_single[r], sels[o]):
