@@ -20,7 +20,7 @@ namespace cr {
 constexpr int kTile = 32;            // positions per shared-memory tile
 constexpr int kRowH = 264;           // padded row of 256 halves: 528 B keeps ldmatrix conflict-free
 constexpr int kPRowH = 40;           // padded row of the 16 x 32 probability tile (80 B)
-constexpr int kMaxSplitPos = 576;    // positions of one split: at most 65 tiles over >= 4 splits = 17 tiles = 544
+constexpr int kMaxSplitPos = 576;    // positions listed in shared memory at a time (18 tiles); a longer split walks its list in chunks
 
 // STAGES = 2: the next tile is gathered while the current one is multiplied (a step: few CTAs, latency counts).
 // STAGES = 1: 55 KB per CTA, four CTAs per SM keep more gathers in flight (a prefill part: thousands of CTAs).
@@ -94,14 +94,18 @@ __global__ void __launch_bounds__(128) qsa_attn_split_kernel(const __grid_consta
   // tiles of 32 attended indices are dealt evenly: the first (tiles % splits) splits take one more
   const int tiles = (n_win + kTile - 1) / kTile, tb = tiles / splits, trem = tiles % splits;
   const int begin = t_lo + (split * tb + min(split, trem)) * kTile, end = min(begin + (tb + (split < trem ? 1 : 0)) * kTile, t_hi);
-  const int cnt = min(max(end - begin, 0), kMaxSplitPos);     // n <= 2051 and splits >= 4: at most 17 tiles
-
-  for (int i = t; i < cnt; i += 128) {
-    int pos = qsa_position(sel, begin + i, ns, nb);
-    if (pos < p0 || pos >= p1) pos = -1;
-    sm.pos[i] = pos;
-  }
-  __syncthreads();
+  const int total = max(end - begin, 0);                  // positions of this split, walked in chunks of at most kMaxSplitPos
+  int cnt = 0, chunk0 = 0;
+  auto list_chunk = [&]() {                               // attended positions [begin + chunk0, + cnt) into shared memory
+    cnt = min(total - chunk0, kMaxSplitPos);
+    for (int i = t; i < cnt; i += 128) {
+      int pos = qsa_position(sel, begin + chunk0 + i, ns, nb);
+      if (pos < p0 || pos >= p1) pos = -1;
+      sm.pos[i] = pos;
+    }
+    __syncthreads();
+  };
+  list_chunk();
 
   const __half* kc = reinterpret_cast<const __half*>(a.c.k);
   const __half* vc = reinterpret_cast<const __half*>(a.c.v);
@@ -116,7 +120,7 @@ __global__ void __launch_bounds__(128) qsa_attn_split_kernel(const __grid_consta
     asm volatile("cp.async.commit_group;\n" ::);
   };
 
-  const int ntiles = (cnt + kTile - 1) / kTile;
+  int ntiles = (cnt + kTile - 1) / kTile;
   const int row0 = l >> 2, cq = (l & 3) * 2;              // this thread's rows row0, row0 + 8; columns cq, cq + 1 of an n-tile
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
   float O[8][4];
@@ -135,6 +139,7 @@ __global__ void __launch_bounds__(128) qsa_attn_split_kernel(const __grid_consta
     *reinterpret_cast<__half2*>(&sm.q[1][row][c]) = __floats2half2_rn(qv.x - b0.x, qv.y - b0.y);
     *reinterpret_cast<__half2*>(&sm.q[1][row][c + 2]) = __floats2half2_rn(qv.z - b1.x, qv.w - b1.y);
   }
+  for (;;) {
   for (int tile = 0; tile < ntiles; ++tile) {
     const int buf = STAGES == 2 ? (tile & 1) : 0;
     if (STAGES == 1) {
@@ -215,6 +220,13 @@ __global__ void __launch_bounds__(128) qsa_attn_split_kernel(const __grid_consta
         mma_f16(O[nt + 1], pl, vb[2], vb[3]);
       }
     }
+  }
+    chunk0 += kMaxSplitPos;                               // a split longer than one chunk (few splits over a long list)
+    if (chunk0 >= total) break;
+    __syncthreads();                                      // every warp is done with the chunk's positions and tiles
+    list_chunk();
+    ntiles = (cnt + kTile - 1) / kTile;
+    if (STAGES == 2) stage(0, 0);
   }
   // partial records of this split: rows row0 and row0 + 8 are heads g * gqa + row
 #pragma unroll
@@ -305,7 +317,7 @@ __global__ void __launch_bounds__(256) qsa_merge_kernel(const __grid_constant__ 
 cr_status qsa_attn_launch(const cr_geometry* g, const cr_qsa_args* spans, int n_spans, float* partials, int splits,
                           int p0, int p1, cudaStream_t stream, const QsaTileSplit* tiles) {
   use_stream(stream);
-  CR_REQUIRE(splits >= 4 && splits <= 32, "qsa attention: %d KV splits unsupported (4..32)", splits);
+  CR_REQUIRE(splits >= 1 && splits <= 32, "qsa attention: %d KV splits unsupported (1..32)", splits);
   int row_base = 0;
   for (int s0 = 0; s0 < n_spans; s0 += kMaxSpans) {
     const int n = n_spans - s0 < kMaxSpans ? n_spans - s0 : kMaxSpans;
@@ -404,7 +416,11 @@ extern "C" cr_status cr_qsa_shard_attn(const cr_geometry* g, const cr_qsa_args* 
   using namespace cr;
   if (cr_status s = qsa_validate(g, a, 1, CR_MAX_PREFILL_ROWS, "cr_qsa_shard_attn", 0)) return s;
   CR_REQUIRE(partials && p0 >= 0 && p1 >= p0, "cr_qsa_shard_attn: bad position window or null output");
-  const int splits = a->R <= CR_MAX_STEP_ROWS ? CR_QSA_SPLITS : 4;
+  // A part's rows take up to 4 splits each; a window that holds a fraction of the cache holds about that fraction of a
+  // row's 2,051 attended positions, so it takes fewer (a split whose list is longer than expected walks it in chunks).
+  const long long cache = (long long)a->pos0 + a->R, window = (p1 < cache ? p1 : cache) - p0;
+  const int part_splits = window <= 0 ? 1 : (int)((4 * window + cache - 1) / cache);
+  const int splits = a->R <= CR_MAX_STEP_ROWS ? CR_QSA_SPLITS : (part_splits < 1 ? 1 : part_splits > 4 ? 4 : part_splits);
   const size_t need = (size_t)a->R * g->q_heads * splits * CR_QSA_PART * sizeof(float);
   CR_REQUIRE(scratch && scratch_bytes >= need, "cr_qsa_shard_attn: scratch of %zu bytes needed, %zu given", need, scratch_bytes);
   if (cr_status s = qsa_attn_launch(g, a, 1, (float*)scratch, splits, p0, p1, (cudaStream_t)stream)) return s;
