@@ -30,6 +30,8 @@ cr_status qsa_prep_launch(const cr_geometry* g, const cr_qsa_args* spans, int n_
 cr_status qsa_score_launch(const cr_geometry* g, const cr_qsa_args* spans, int n_spans, cudaStream_t stream, int b_lo = 0, int b_hi = INT_MAX);
 // Prefill parts (many rows): the scores as four GEMMs on tcgen05 tensor cores.
 cr_status qsa_score_tc_launch(const QsaParams& P, int Rmax, int n, cudaStream_t stream);
+// Spans of 3..16 rows (verify passes): the scores as an HBM stream through mma.sync, every block of every row.
+cr_status qsa_score_mma_launch(const QsaParams& P, int tiles, int Rmax, int n, cudaStream_t stream);
 cr_status qsa_topk_launch(const cr_geometry* g, const cr_qsa_args* spans, int n_spans, cudaStream_t stream);
 cr_status qsa_select_launch(const cr_geometry* g, const cr_qsa_args* spans, int n_spans, cudaStream_t stream);
 // splits: KV splits per (row, KV head). p0/p1: position window (shard mode) or 0 / INT_MAX.

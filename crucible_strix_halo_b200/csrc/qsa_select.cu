@@ -195,7 +195,8 @@ cr_status qsa_score_launch(const cr_geometry* g, const cr_qsa_args* spans, int n
       CR_LAUNCH_CHECK("qsa_score_kernel");
       st = CR_OK;
     }
-    else if (Rmax >= 8 && !options().qsa_score_simt) st = qsa_score_tc_launch(P, Rmax, n, stream);   // verify spans of 8 rows and more, prefill parts
+    else if (Rmax <= 16 && !ranged && !options().qsa_score_simt) st = qsa_score_mma_launch(P, tiles, Rmax, n, stream);   // verify spans
+    else if (Rmax >= 8 && !options().qsa_score_simt) st = qsa_score_tc_launch(P, Rmax, n, stream);   // prefill parts (and a rank's range of a span)
     else if (Rmax <= 4) st = score_launch_t<4>(P, tiles, Rmax, n, ranged, stream);
     else st = score_launch_t<8>(P, tiles, Rmax, n, ranged, stream);
     if (st) return st;
