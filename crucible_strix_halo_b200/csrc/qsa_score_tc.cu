@@ -5,8 +5,8 @@
 //
 // is four GEMMs of shape [blocks x 128] x [128 x rows] with a ReLU between them and their sum.  One CTA owns 64
 // rows and a range of 128-block pool tiles.  M = 128 blocks (the pool tile is the A operand), N = 64 rows (the
-// query panel of all four heads stays in shared memory as the B operand), K = 128; the four heads accumulate in
-// four TMEM accumulators, two sets used in turn, so the epilogue of a tile (ReLU, sum over heads, scale, store)
+// query panel of all four heads stays in shared memory as the B operand: N = 4 heads x 64 rows = 256 columns of one
+// MMA), K = 128; the heads are the four 64-column quarters of a TMEM accumulator, two accumulators used in turn, so the epilogue of a tile (ReLU, sum over heads, scale, store)
 // runs while the next tile is multiplied.  Precision: both operands are split into an fp16 head and an fp16
 // remainder (22 mantissa bits together; the values are normalised rows, well inside the fp16 range) and three
 // products are accumulated in fp32 (head x head, head x remainder, remainder x head); the error of a score
@@ -24,7 +24,7 @@ CR_DEFINE_STATUS_WORD(qsa_score)
 constexpr int kScRows = 64;                 // query rows per CTA (N)
 constexpr int kScBlocks = 128;              // pool blocks per tile (M)
 constexpr int kScThreads = 32 * 13;         // 4 epilogue warps, 8 staging warps, 1 issuer warp
-constexpr int kQopBytes = 4 * 2 * 16 * kScRows * 16;      // [head][hi/lo][dim / 8][row][8 fp16]
+constexpr int kQopBytes = 2 * 16 * 4 * kScRows * 16;      // [hi/lo][dim / 8][head][row][8 fp16]: N = (head, row) = 256 columns
 constexpr int kPopBytes = 2 * 16 * kScBlocks * 16;        // [hi/lo][dim / 8][block][8 fp16]
 constexpr size_t kScoreSmem = kQopBytes + kPopBytes + 128;
 
@@ -92,8 +92,8 @@ __global__ void __launch_bounds__(kScThreads, 1) qsa_score_tc_kernel(const __gri
     }
     uint4 hi, lo;
     split8(x, hi, lo);
-    *reinterpret_cast<uint4*>(Qop + ((size_t)((h * 2 + 0) * 16 + dc) * kScRows + row) * 16) = hi;
-    *reinterpret_cast<uint4*>(Qop + ((size_t)((h * 2 + 1) * 16 + dc) * kScRows + row) * 16) = lo;
+    *reinterpret_cast<uint4*>(Qop + ((size_t)(dc * 4 + h) * kScRows + row) * 16) = hi;
+    *reinterpret_cast<uint4*>(Qop + kQopBytes / 2 + ((size_t)(dc * 4 + h) * kScRows + row) * 16) = lo;
   }
   umma::fence_async_smem();
   umma::fence_before_sync();
@@ -109,27 +109,25 @@ __global__ void __launch_bounds__(kScThreads, 1) qsa_score_tc_kernel(const __gri
   if (w == 12) {
     // ------------------------------------------------------------------ issuer
     if (l == 0) {
-      constexpr uint32_t idesc = idesc_f16(kScBlocks, kScRows);
+      // One MMA covers the four heads: N = 4 x 64 (head, row) columns, so the pool tile is read once per k-step and
+      // product instead of once per head (an MMA of N = 64 is bound by its 6 KB of shared-memory reads).
+      constexpr uint32_t idesc = idesc_f16(kScBlocks, 4 * kScRows);
       const uint64_t dPh = umma::smem_desc(Pop, kScBlocks * 16, 128), dPl = umma::smem_desc(Pop + kPopBytes / 2, kScBlocks * 16, 128);
+      const uint64_t dQh = umma::smem_desc(Qop, 4 * kScRows * 16, 128), dQl = umma::smem_desc(Qop + kQopBytes / 2, 4 * kScRows * 16, 128);
       for (int i = 0; i < t1 - t0; ++i) {
         const int buf = i & 1;
         wait(popFull, i & 1);
         if (i >= 2) wait(&accFree[buf], ((i >> 1) - 1) & 1);
         if (gave_up || dead) break;                        // no more tensor-core work once any wait has run out
         umma::fence_after_sync();
+        const uint32_t d = tm + buf * 256;
+        // a step of 16 along K is two 16-byte planes: 2 x 128 units of the pool tile, 2 x 256 of the query panel
 #pragma unroll
-        for (int h = 0; h < 4; ++h) {
-          const uint32_t d = tm + buf * 256 + h * 64;
-          const uint64_t dQh = umma::smem_desc(Qop + (size_t)(h * 2 + 0) * 16 * kScRows * 16, kScRows * 16, 128);
-          const uint64_t dQl = umma::smem_desc(Qop + (size_t)(h * 2 + 1) * 16 * kScRows * 16, kScRows * 16, 128);
-          // a step of 16 along K is two 16-byte planes: 2 x 128 units of the pool tile, 2 x 64 of the query panel
+        for (int ks = 0; ks < 8; ++ks) mma_f16_ss(d, dPh + (uint64_t)(ks * 256), dQh + (uint64_t)(ks * 512), idesc, ks > 0);
 #pragma unroll
-          for (int ks = 0; ks < 8; ++ks) mma_f16_ss(d, dPh + (uint64_t)(ks * 256), dQh + (uint64_t)(ks * 128), idesc, ks > 0);
+        for (int ks = 0; ks < 8; ++ks) mma_f16_ss(d, dPh + (uint64_t)(ks * 256), dQl + (uint64_t)(ks * 512), idesc, 1u);
 #pragma unroll
-          for (int ks = 0; ks < 8; ++ks) mma_f16_ss(d, dPh + (uint64_t)(ks * 256), dQl + (uint64_t)(ks * 128), idesc, 1u);
-#pragma unroll
-          for (int ks = 0; ks < 8; ++ks) mma_f16_ss(d, dPl + (uint64_t)(ks * 256), dQh + (uint64_t)(ks * 128), idesc, 1u);
-        }
+        for (int ks = 0; ks < 8; ++ks) mma_f16_ss(d, dPl + (uint64_t)(ks * 256), dQh + (uint64_t)(ks * 512), idesc, 1u);
         umma::commit(&mmaDone[buf]);
       }
     }
