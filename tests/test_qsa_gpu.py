@@ -534,3 +534,42 @@ def test_yarn_table_and_multimodal_positions_match_oracle(factor):
     arr = (capi.QsaArgs * 1)(layers.qsa_args(w, ses, *keep, plan.out, R, mrope=mro_d))
     capi.check(capi.lib.cr_qsa_step(C.byref(g), arr, 1, capi.dptr(sp.scratch), sp.scratch.numel(), capi.OUT_RAW_F32, None))
     assert_close_attn(plan.out[:1].cpu().numpy(), refd, max_abs=1e-3, cos=0.99999, what="decode row")
+
+
+@pytest.mark.parametrize("ctx,R", [(262144, 1), (131072, 9)])
+def test_decode_and_verify_rows_at_the_benchmark_depths(ctx, R):
+    """A decode row at 262,144 positions (65,536 blocks: the one-row score stream, the cluster top-512) and a 9-row verify
+    span at 131,072 (scores through mma.sync, one CTA per row in the top-512) against the oracle on the same caches:
+    scores to 2e-4, selections identical outside near ties, outputs within the decode tolerance."""
+    capi, layers, g, og, rng, norms, suh, w = _setup(16, seed=31)
+    pos0 = ctx - R
+    ses, oc = layers.QsaSession(g, ctx, max_rows=R), ao.QsaCache(og, ctx)
+    oc.k[:] = rng.standard_normal(oc.k.shape, dtype=np.float32).astype(np.float16)
+    oc.v[:] = rng.standard_normal(oc.v.shape, dtype=np.float32).astype(np.float16)
+    oc.ik_raw[:] = rng.standard_normal(oc.ik_raw.shape, dtype=np.float32)
+    oc.ik_pool[:] = rng.standard_normal(oc.ik_pool.shape, dtype=np.float32)
+    ses.k.copy_(torch.from_numpy(oc.k)); ses.v.copy_(torch.from_numpy(oc.v))
+    ses.ik_raw.copy_(torch.from_numpy(oc.ik_raw)); ses.ik_pool.copy_(torch.from_numpy(oc.ik_pool))
+    q, k, v, idx = _rows(rng, og, R)
+    # At these positions the rotation is sensitive to the last bit of a frequency (angle = position x frequency) and to the
+    # float32 rounding of the angle itself (2^-7 rad): the oracle takes the engine's arithmetic and the table the
+    # library built.
+    rope = w.rope.cpu().numpy()
+    ao.ROPE_F32_ANGLE = True
+    try:
+        ref, sels, scs, _, _ = ao.qsa_rows(q, k, v, idx, norms, oc, pos0, og, return_detail=True, table=(rope[:32], rope[32]))
+    finally:
+        ao.ROPE_F32_ANGLE = False
+    out = layers.QsaStepPlan(w, R).run([dict(session=ses, q=dev(q), k=dev(k), v=dev(v), idx=dev(idx), pos0=pos0)])[0].cpu().numpy()
+    assert capi.lib.cr_device_status() == 0
+    checked = 0
+    for r in range(R):
+        nb = (pos0 + r + 1) // 4
+        assert int(ses.nsel[r]) == 512
+        np.testing.assert_allclose(ses.scores[r, :nb].cpu().numpy(), scs[r], rtol=0, atol=2e-4)
+        got = ses.sel[r].cpu().numpy()
+        assert ao.selection_agrees(scs[r], got, sels[r]), "row %d: selection differs beyond near ties" % r
+        if np.array_equal(got, sels[r]):
+            assert_close_attn(out[r], ref[r], max_abs=1e-3, cos=0.99999, what="row %d" % r)
+            checked += 1
+    assert checked >= (R + 1) // 2, "too few rows with an identical selection to compare outputs"
