@@ -56,7 +56,7 @@ __device__ __forceinline__ void mma_f16(float (&d)[4], const unsigned (&a)[4], u
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// grid (splits, Rmax * Hkv, spans); 128 threads.
+// grid (splits, Rmax * Hkv, spans), or (Rmax * Hkv, splits, spans) for STAGES == 1; 128 threads.
 template <int STAGES>
 __global__ void __launch_bounds__(128) qsa_attn_split_kernel(const __grid_constant__ QsaParams P, float* partials,
                                                              int splits, int p0, int p1) {
@@ -65,11 +65,15 @@ __global__ void __launch_bounds__(128) qsa_attn_split_kernel(const __grid_consta
   pdl_release();
   pdl_wait();
   const cr_qsa_args& a = P.span[blockIdx.z];
-  const int r = blockIdx.y / P.Hkv, g = blockIdx.y % P.Hkv;
+  // STAGES == 1 (many rows): grid (rows x KV heads, splits), the split being the slow index.  Split s of every row
+  // covers about the s-th part of the context (attended positions ascend), so the CTAs in flight at any time read one
+  // region of the cache, which L2 can hold.  STAGES == 2 (steps): grid (splits, rows x KV heads).
+  const int rg = STAGES == 1 ? blockIdx.x : blockIdx.y;
+  const int r = rg / P.Hkv, g = rg % P.Hkv;
   if (r >= a.R || qsa_row_is_tiled(P, r)) return;
   const int gqa = P.Hq / P.Hkv;
   const int t = threadIdx.x, w = t >> 5, l = t & 31;
-  const int split = blockIdx.x;
+  const int split = STAGES == 1 ? blockIdx.y : blockIdx.x;
   const int p = a.pos0 + r, ns = a.nsel[r], nb = (p + 1) / 4;
   const int n = ns < 0 ? p + 1 : ns * 4 + (p + 1) % 4;
   const int* sel = a.sel + (size_t)r * CR_SEL_BLOCKS;
@@ -334,7 +338,7 @@ cr_status qsa_attn_launch(const cr_geometry* g, const cr_qsa_args* spans, int n_
         })) return st;
     const dim3 grid(splits, Rmax * g->kv_heads, n);
     if ((long long)grid.x * grid.y * grid.z > 600)          // more than two waves of the two-stage kernel (2 CTAs per SM)
-      CR_CUDA(launch_pdl(qsa_attn_split_kernel<1>, grid, dim3(128), sizeof(SplitSmem<1>), stream, P, partials, splits, p0, p1));
+      CR_CUDA(launch_pdl(qsa_attn_split_kernel<1>, dim3(grid.y, grid.x, grid.z), dim3(128), sizeof(SplitSmem<1>), stream, P, partials, splits, p0, p1));
     else
       CR_CUDA(launch_pdl(qsa_attn_split_kernel<2>, grid, dim3(128), sizeof(SplitSmem<2>), stream, P, partials, splits, p0, p1));
     CR_LAUNCH_CHECK("qsa_attn_split_kernel");
