@@ -385,6 +385,17 @@ static size_t total_rows(const cr_qsa_args* spans, int n) {
 
 }  // namespace cr
 
+// KV splits per (row, KV head) of a decode / verify pass: 32 for a few rows (latency: many short CTAs), fewer when the
+// pass holds many rows, so that the grid stays near two waves of CTAs and the per-CTA work (query staging, a partial
+// record per head) is shared by more positions.  A power of two between 4 and 32.
+constexpr long long kStepCtas = 1200;   // 600 and 2,400 measured 20 % and 6 % slower on 72 rows
+static int step_splits(const cr_geometry* g, const cr_qsa_args* spans, int n_spans) {
+  const long long units = (long long)cr::total_rows(spans, n_spans) * g->kv_heads;
+  int splits = CR_QSA_SPLITS;
+  while (splits > 4 && units * splits > kStepCtas) splits >>= 1;
+  return splits;
+}
+
 extern "C" size_t cr_qsa_scratch_bytes(const cr_geometry* g, int rows) {
   if (!g || rows < 1) return 0;
   return (size_t)rows * g->q_heads * CR_QSA_SPLITS * CR_QSA_PART * sizeof(float);
@@ -397,8 +408,9 @@ extern "C" cr_status cr_qsa_attn(const cr_geometry* g, const cr_qsa_args* spans,
   if (cr_status s = check_out(spans, n_spans, fmt, "cr_qsa_attn")) return s;
   const size_t need = cr_qsa_scratch_bytes(g, (int)total_rows(spans, n_spans));
   CR_REQUIRE(scratch && scratch_bytes >= need, "cr_qsa_attn: scratch of %zu bytes needed, %zu given", need, scratch_bytes);
-  if (cr_status s = qsa_attn_launch(g, spans, n_spans, (float*)scratch, CR_QSA_SPLITS, 0, INT_MAX, (cudaStream_t)stream)) return s;
-  return qsa_merge_launch(g, spans, n_spans, (const float*)scratch, CR_QSA_SPLITS, false, nullptr, fmt, (cudaStream_t)stream);
+  const int splits = step_splits(g, spans, n_spans);
+  if (cr_status s = qsa_attn_launch(g, spans, n_spans, (float*)scratch, splits, 0, INT_MAX, (cudaStream_t)stream)) return s;
+  return qsa_merge_launch(g, spans, n_spans, (const float*)scratch, splits, false, nullptr, fmt, (cudaStream_t)stream);
 }
 
 extern "C" cr_status cr_qsa_step(const cr_geometry* g, const cr_qsa_args* spans, int n_spans, void* scratch, size_t scratch_bytes,
@@ -411,8 +423,9 @@ extern "C" cr_status cr_qsa_step(const cr_geometry* g, const cr_qsa_args* spans,
   cudaStream_t st = (cudaStream_t)stream;
   if (cr_status s = qsa_prep_launch(g, spans, n_spans, 0, nullptr, 0, st)) return s;
   if (cr_status s = qsa_select_launch(g, spans, n_spans, st)) return s;
-  if (cr_status s = qsa_attn_launch(g, spans, n_spans, (float*)scratch, CR_QSA_SPLITS, 0, INT_MAX, st)) return s;
-  return qsa_merge_launch(g, spans, n_spans, (const float*)scratch, CR_QSA_SPLITS, false, nullptr, fmt, st);
+  const int splits = step_splits(g, spans, n_spans);
+  if (cr_status s = qsa_attn_launch(g, spans, n_spans, (float*)scratch, splits, 0, INT_MAX, st)) return s;
+  return qsa_merge_launch(g, spans, n_spans, (const float*)scratch, splits, false, nullptr, fmt, st);
 }
 
 extern "C" cr_status cr_qsa_shard_attn(const cr_geometry* g, const cr_qsa_args* a, int p0, int p1, float* partials, void* scratch,
