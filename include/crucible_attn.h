@@ -183,10 +183,11 @@ typedef struct {
 
 /* Scratch sizing (engine/layers/qsa_long.h:226, :396; engine/layers/ops.h:420;
  * engine/layers/cache_storage.h:40-46). */
-size_t cr_qsa_scratch_bytes(const cr_geometry* g, int rows);         /* split-KV partials: rows x Hq x 32 x 258 floats */
-size_t cr_qsa_select_scratch_bytes(const cr_geometry* g, int rows);  /* 0: the select kernels keep their histograms
-                                                                        on chip; kept so that QsaSelectScratchFloats
-                                                                        call sites compile */
+size_t cr_qsa_scratch_bytes(const cr_geometry* g, int rows);         /* split-KV partials: rows x Hq x 32 x 258 floats
+                                                                        (a pass of many rows uses fewer splits of it) */
+size_t cr_qsa_select_scratch_bytes(const cr_geometry* g, int rows);  /* 0: the select kernels keep their candidate
+                                                                        lists on chip; kept so that
+                                                                        QsaSelectScratchFloats call sites compile */
 size_t cr_qsa_pool_floats(int ctx);
 cr_status cr_qsa_cache_bytes(const cr_geometry* g, int ctx, int bounded, size_t out_bytes[4]);
 
